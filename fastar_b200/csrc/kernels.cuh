@@ -1,0 +1,96 @@
+// Launchers of the MLA kernels.  All pointers are device pointers; bf16 unless noted.
+#pragma once
+#include "common.cuh"
+
+namespace fst {
+
+// Strided-batched C[z][m, n] = sum_k A[z][m, k] * B[z][n, k]  (b_kn: B[z][k, n]).
+struct GemmArgs {
+  const bf16* A;
+  const bf16* B;
+  bf16* C;
+  int M, N, K;
+  int lda, ldb, ldc;
+  int batch;
+  long long a_bs, b_bs, c_bs;  // element strides between batch members
+  int b_kn;
+};
+void launch_gemm_simt(const GemmArgs& g, cudaStream_t st);
+// tcgen05 path: B in [N, K] layout only, K % 64 == 0, N % 128 == 0, 16-byte aligned rows.
+bool gemm_tc_supported(const GemmArgs& g);
+// Returns cudaSuccess or the error of building the tensor maps / launching.
+cudaError_t launch_gemm_tc(const GemmArgs& g, int* d_status, cudaStream_t st);
+
+// RMSNorm(q) -> qc; RMSNorm(latent) (+ RoPE on the key's rope dims) -> kv_new and the cache row.
+struct NormAppendArgs {
+  const bf16* cmp;      // [T, q_lora + row]
+  const bf16* q_norm;   // [q_lora] or null
+  const bf16* kv_norm;  // [kv_lora] or null
+  const float* lut;     // [T, rope] (cos, sin) pairs
+  const long long* dst_row;  // [T] element offset of the cache row in the pool, or -1
+  bf16* qc;             // [T, q_lora]
+  bf16* kv_new;         // [T, row]
+  bf16* pool;
+  int T, q_lora, kv_lora, row, rope;
+  float eps;
+};
+void launch_norm_append(const NormAppendArgs& a, cudaStream_t st);
+
+// BASELINE: rotate q_pe into q_eff[:, kv_lora:].  V4: per-head RMSNorm + tail RoPE -> q_eff.
+struct QPrepArgs {
+  const bf16* q_full;  // [T, H * q_head]
+  const float* lut;    // [T, rope]
+  bf16* q_eff;         // [T * H, d_qk]
+  int T, H, q_head, nope, rope, d_qk, v4;
+  float eps;
+};
+void launch_q_prep(const QPrepArgs& a, cudaStream_t st);
+
+struct AttnArgs {
+  const bf16* q_eff;        // [T * H, d_qk]
+  const bf16* pool;         // [n_pages * page_tokens, row]
+  const int32_t* tables;    // flat block tables
+  const int32_t* tok_table; // [T] offset of the token's sequence table in `tables`
+  const AttnSeg* segs;
+  const int32_t* cta_seg;   // [n_ctas + 1] segment ranges of the persistent CTAs
+  float* part_m;            // [P, H]
+  float* part_l;            // [P, H]
+  float* part_o;            // [P, H, d_v]
+  int* d_status;
+  int n_segs, n_ctas, H, d_qk, d_v, row, page_tokens;
+  long long q_rows;         // rows of q_eff (new tokens * H)
+  long long pool_rows;      // n_pages * page_tokens
+  float scale;
+};
+void launch_attn_simt(const AttnArgs& a, cudaStream_t st);
+bool attn_tc_supported(const AttnArgs& a);
+cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st);
+size_t attn_tc_smem_bytes(const AttnArgs& a);
+
+// Log-sum-exp merge of each token's partial slots [tok_part[t], tok_part[t+1]).
+struct MergeArgs {
+  const float* part_m;
+  const float* part_l;
+  const float* part_o;
+  const int32_t* tok_part;  // [T + 1]
+  const float* sinks;       // [H] or null
+  const float* lut;         // [T, rope]: inverse RoPE of the output tail when inv_rope
+  bf16* o_lat;              // [T * H, d_v]                 (mode 0)
+  float* rank_partial;      // [T * H, 2 + d_v] fp32        (mode 1, no sink)
+  int T, H, d_v, rope, inv_rope, mode;
+};
+void launch_merge(const MergeArgs& a, cudaStream_t st);
+
+// Merge of gathered per-GPU partials [n_parts][T * H, 2 + d_v] -> o_lat.
+struct MergeGatheredArgs {
+  const float* parts;
+  const float* sinks;
+  const float* lut;
+  bf16* o_lat;
+  int n_parts, T, H, d_v, rope, inv_rope;
+};
+void launch_merge_gathered(const MergeGatheredArgs& a, cudaStream_t st);
+
+void launch_zero_rows(bf16* pool, const long long* row_off, int n_rows, int row, cudaStream_t st);
+
+}  // namespace fst

@@ -1,0 +1,461 @@
+// CUDA-core kernels of the MLA path: the small fused stages (norms, RoPE, cache append,
+// log-sum-exp merge) and shape-agnostic GEMM / attention kernels used where the tcgen05
+// kernels do not apply (odd shapes, the [K,N] absorb operand) and for bisecting.
+#include "kernels.cuh"
+
+namespace fst {
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+// ---- GEMM, B in [N, K] (npu_gemm_mla_vec b_col_maj, reference src/fst_engine.cpp:477-484) ----
+// A warp owns a 8 x 4 output tile; its lanes split K in 16-byte pieces.
+template <bool VEC>
+__global__ void __launch_bounds__(128) k_gemm_nk(GemmArgs g) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bf16* A = g.A + (long long)blockIdx.z * g.a_bs;
+  const bf16* B = g.B + (long long)blockIdx.z * g.b_bs;
+  bf16* C = g.C + (long long)blockIdx.z * g.c_bs;
+  const int n0 = (blockIdx.x * 4 + warp) * 4, m0 = blockIdx.y * 8;
+  if (n0 >= g.N) return;
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+  if (VEC) {
+    for (int k = lane * 8; k < g.K; k += 256) {
+      float b[4][8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = min(n0 + j, g.N - 1);
+        unpack8(*reinterpret_cast<const uint4*>(B + (long long)n * g.ldb + k), b[j]);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int m = min(m0 + i, g.M - 1);
+        float a[8];
+        unpack8(*reinterpret_cast<const uint4*>(A + (long long)m * g.lda + k), a);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[i][j] = fmaf(a[e], b[j][e], acc[i][j]);
+      }
+    }
+  } else {
+    for (int k = lane; k < g.K; k += 32) {
+      float b[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = bf2f(B[(long long)min(n0 + j, g.N - 1) * g.ldb + k]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float a = bf2f(A[(long long)min(m0 + i, g.M - 1) * g.lda + k]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a, b[j], acc[i][j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float v = warp_sum(acc[i][j]);
+      if (lane == 0 && m0 + i < g.M && n0 + j < g.N) C[(long long)(m0 + i) * g.ldc + n0 + j] = f2bf(v);
+    }
+}
+
+// ---- GEMM, B in [K, N] (the b_row_maj operand, reference src/fst_engine.cpp:480) ----
+__global__ void __launch_bounds__(128) k_gemm_kn(GemmArgs g) {
+  const bf16* A = g.A + (long long)blockIdx.z * g.a_bs;
+  const bf16* B = g.B + (long long)blockIdx.z * g.b_bs;
+  bf16* C = g.C + (long long)blockIdx.z * g.c_bs;
+  const int n = blockIdx.x * 128 + threadIdx.x;
+  const int m0 = blockIdx.y * 8;
+  if (n >= g.N) return;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  for (int k = 0; k < g.K; ++k) {
+    const float b = bf2f(B[(long long)k * g.ldb + n]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      acc[i] = fmaf(bf2f(A[(long long)min(m0 + i, g.M - 1) * g.lda + k]), b, acc[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (m0 + i < g.M) C[(long long)(m0 + i) * g.ldc + n] = f2bf(acc[i]);
+}
+
+void launch_gemm_simt(const GemmArgs& g, cudaStream_t st) {
+  if (g.M <= 0 || g.N <= 0 || g.batch <= 0) return;
+  if (g.b_kn) {
+    dim3 grid((g.N + 127) / 128, (g.M + 7) / 8, g.batch);
+    k_gemm_kn<<<grid, 128, 0, st>>>(g);
+    return;
+  }
+  dim3 grid((g.N + 15) / 16, (g.M + 7) / 8, g.batch);
+  const bool vec = g.K % 8 == 0 && g.lda % 8 == 0 && g.ldb % 8 == 0 && g.a_bs % 8 == 0 &&
+                   g.b_bs % 8 == 0 && (reinterpret_cast<uintptr_t>(g.A) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(g.B) & 15) == 0;
+  if (vec)
+    k_gemm_nk<true><<<grid, 128, 0, st>>>(g);
+  else
+    k_gemm_nk<false><<<grid, 128, 0, st>>>(g);
+}
+
+// ---- q_norm / kv_norm / key RoPE / cache append -------------------------------------------
+// Reference src/fst_engine.cpp:3385-3394 (norms), 3504-3517 (RoPE on the key), 3534-3544
+// (cache push).  One block per new token.  RMSNorm follows rms_cpu (89-91).
+__global__ void __launch_bounds__(256) k_norm_append(NormAppendArgs a) {
+  extern __shared__ float s_row[];  // [row]
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const bf16* in = a.cmp + (long long)t * (a.q_lora + a.row);
+  // q_norm
+  float ss = 0.0f;
+  for (int j = threadIdx.x; j < a.q_lora; j += blockDim.x) {
+    const float x = bf2f(in[j]);
+    ss += x * x;
+  }
+  ss = block_sum(ss, scratch);
+  float r = 1.0f / sqrtf(ss / (float)a.q_lora + a.eps);
+  for (int j = threadIdx.x; j < a.q_lora; j += blockDim.x) {
+    const float x = bf2f(in[j]);
+    a.qc[(long long)t * a.q_lora + j] = f2bf(a.q_norm ? x * r * bf2f(a.q_norm[j]) : x);
+  }
+  // kv_norm over the kv_lora latent; trailing dims (BASELINE k_pe) pass through
+  const bf16* kin = in + a.q_lora;
+  ss = 0.0f;
+  for (int j = threadIdx.x; j < a.kv_lora; j += blockDim.x) {
+    const float x = bf2f(kin[j]);
+    ss += x * x;
+  }
+  ss = block_sum(ss, scratch);
+  r = 1.0f / sqrtf(ss / (float)a.kv_lora + a.eps);
+  for (int j = threadIdx.x; j < a.row; j += blockDim.x) {
+    const float x = bf2f(kin[j]);
+    s_row[j] = (j < a.kv_lora && a.kv_norm) ? rbf(x * r * bf2f(a.kv_norm[j])) : x;
+  }
+  __syncthreads();
+  // RoPE on the last `rope` dims of the row, interleaved pairs (ew_rope,
+  // reference kernels/fst_ew_unified_kernel.cc:200-217)
+  const float* lut = a.lut + (long long)t * a.rope;
+  for (int p = threadIdx.x; p < a.rope / 2; p += blockDim.x) {
+    const int j = a.row - a.rope + 2 * p;
+    const float c = lut[2 * p], s = lut[2 * p + 1], x0 = s_row[j], x1 = s_row[j + 1];
+    s_row[j] = x0 * c - x1 * s;
+    s_row[j + 1] = x0 * s + x1 * c;
+  }
+  __syncthreads();
+  const long long dst = a.dst_row[t];
+  for (int j = threadIdx.x; j < a.row; j += blockDim.x) {
+    const bf16 v = f2bf(s_row[j]);
+    a.kv_new[(long long)t * a.row + j] = v;
+    if (dst >= 0) a.pool[dst + j] = v;
+  }
+}
+
+void launch_norm_append(const NormAppendArgs& a, cudaStream_t st) {
+  if (a.T <= 0) return;
+  k_norm_append<<<a.T, 256, a.row * sizeof(float), st>>>(a);
+}
+
+// ---- query preparation -----------------------------------------------------------------------
+// BASELINE: rotate the rope dims of every head of q_full into q_eff[:, kv_lora:]
+// (rope_qpe_all_heads, reference src/fst_engine.cpp:2025-2058; the absorb GEMM fills the rest).
+// V4: per-head weightless RMSNorm (3487-3495), then the tail rotation (3503).
+__global__ void __launch_bounds__(128) k_q_prep(QPrepArgs a) {
+  __shared__ float scratch[32];
+  __shared__ float s_q[1024];
+  const int r = blockIdx.x, t = r / a.H;
+  const bf16* in = a.q_full + (long long)r * a.q_head;
+  bf16* out = a.q_eff + (long long)r * a.d_qk;
+  const float* lut = a.lut + (long long)t * a.rope;
+  if (a.v4) {
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < a.q_head; j += blockDim.x) {
+      const float x = bf2f(in[j]);
+      ss += x * x;
+    }
+    ss = block_sum(ss, scratch);
+    const float sc = 1.0f / sqrtf(ss / (float)a.q_head + a.eps);
+    for (int j = threadIdx.x; j < a.q_head; j += blockDim.x) s_q[j] = rbf(bf2f(in[j]) * sc);
+    __syncthreads();
+    for (int p = threadIdx.x; p < a.rope / 2; p += blockDim.x) {
+      const int j = a.nope + 2 * p;
+      const float c = lut[2 * p], s = lut[2 * p + 1], x0 = s_q[j], x1 = s_q[j + 1];
+      s_q[j] = x0 * c - x1 * s;
+      s_q[j + 1] = x0 * s + x1 * c;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < a.q_head; j += blockDim.x) out[j] = f2bf(s_q[j]);
+  } else {
+    for (int p = threadIdx.x; p < a.rope / 2; p += blockDim.x) {
+      const float c = lut[2 * p], s = lut[2 * p + 1];
+      const float x0 = bf2f(in[a.nope + 2 * p]), x1 = bf2f(in[a.nope + 2 * p + 1]);
+      out[a.d_qk - a.rope + 2 * p] = f2bf(x0 * c - x1 * s);
+      out[a.d_qk - a.rope + 2 * p + 1] = f2bf(x0 * s + x1 * c);
+    }
+  }
+}
+
+void launch_q_prep(const QPrepArgs& a, cudaStream_t st) {
+  if (a.T <= 0) return;
+  k_q_prep<<<a.T * a.H, 128, 0, st>>>(a);
+}
+
+// ---- split-KV attention on CUDA cores -----------------------------------------------------
+// QK (reference src/fst_engine.cpp:3573-3589), softmax (3614-3666), SV (3668-3683) fused with
+// an online softmax.  One block per schedule segment; 8 warps x 8 heads; 32-token tiles of
+// the paged cache staged in shared memory; lane = cached token for QK, lane = column pair
+// for SV.  Writes the un-normalised partial (max, sum, O).
+constexpr int SIMT_TILE = 32;
+constexpr int SIMT_HPW = 8;  // heads per warp
+
+__global__ void __launch_bounds__(256, 1) k_attn_simt(AttnArgs a) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int stride = a.row * 2 + 16;  // bytes; the 16-byte pad keeps 16-byte loads conflict free
+  bf16* s_q = reinterpret_cast<bf16*>(smem);  // [H, d_qk]
+  unsigned char* s_tile = smem + (size_t)a.H * a.d_qk * 2;
+  const AttnSeg seg = a.segs[blockIdx.x];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int32_t* table = a.tables + a.tok_table[seg.tok];
+
+  for (int h0 = 0; h0 < a.H; h0 += 8 * SIMT_HPW) {
+    __syncthreads();
+    {
+      const uint4* src = reinterpret_cast<const uint4*>(a.q_eff + (long long)seg.tok * a.H * a.d_qk);
+      uint4* dst = reinterpret_cast<uint4*>(s_q);
+      for (int i = threadIdx.x; i < a.H * a.d_qk / 8; i += blockDim.x) dst[i] = src[i];
+    }
+    float m[SIMT_HPW], l[SIMT_HPW], acc[SIMT_HPW][16];
+#pragma unroll
+    for (int u = 0; u < SIMT_HPW; ++u) {
+      m[u] = -INFINITY;
+      l[u] = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) acc[u][c] = 0.0f;
+    }
+    const int hbase = h0 + warp * SIMT_HPW;
+    for (int s0 = seg.kv_begin; s0 < seg.kv_end; s0 += SIMT_TILE) {
+      __syncthreads();
+      const int per_row = a.row / 8;  // 16-byte pieces per cache row
+      for (int i = threadIdx.x; i < SIMT_TILE * per_row; i += blockDim.x) {
+        const int rr = i / per_row, cc = i % per_row;
+        const int s = min(s0 + rr, seg.kv_end - 1);
+        const long long prow = (long long)table[s / a.page_tokens] * a.page_tokens + s % a.page_tokens;
+        *reinterpret_cast<uint4*>(s_tile + (size_t)rr * stride + cc * 16) =
+            *reinterpret_cast<const uint4*>(a.pool + prow * a.row + cc * 8);
+      }
+      __syncthreads();
+      // scores: lane = token of the tile
+      float sc[SIMT_HPW];
+#pragma unroll
+      for (int u = 0; u < SIMT_HPW; ++u) sc[u] = 0.0f;
+      const unsigned char* krow = s_tile + (size_t)lane * stride;
+      for (int c = 0; c < a.d_qk / 8; ++c) {
+        float kf[8];
+        unpack8(*reinterpret_cast<const uint4*>(krow + c * 16), kf);
+#pragma unroll
+        for (int u = 0; u < SIMT_HPW; ++u) {
+          if (hbase + u < a.H) {
+            float qf[8];
+            unpack8(*reinterpret_cast<const uint4*>(s_q + (size_t)(hbase + u) * a.d_qk + c * 8), qf);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sc[u] = fmaf(qf[e], kf[e], sc[u]);
+          }
+        }
+      }
+      const bool valid = s0 + lane < seg.kv_end;
+      float p[SIMT_HPW];
+#pragma unroll
+      for (int u = 0; u < SIMT_HPW; ++u) {
+        const float v = valid ? sc[u] * a.scale : -INFINITY;
+        const float mn = fmaxf(m[u], warp_max(v));  // finite: every tile has a valid token
+        const float alpha = expf(m[u] - mn);
+        const float e = valid ? expf(v - mn) : 0.0f;
+        l[u] = l[u] * alpha + warp_sum(e);
+        m[u] = mn;
+        p[u] = rbf(e);  // P is a bf16 operand of SV (reference 3651-3652)
+#pragma unroll
+        for (int c = 0; c < 16; ++c) acc[u][c] *= alpha;
+      }
+      // SV: lane owns columns lane*2 + 64*j (+1)
+      const int ntok = min(SIMT_TILE, seg.kv_end - s0);
+      for (int tk = 0; tk < ntok; ++tk) {
+        float vf[16];
+        const unsigned char* vrow = s_tile + (size_t)tk * stride;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j * 64 < a.d_v) {
+            const float2 t2 = __bfloat1622float2(
+                *reinterpret_cast<const __nv_bfloat162*>(vrow + (j * 64 + lane * 2) * 2));
+            vf[2 * j] = t2.x;
+            vf[2 * j + 1] = t2.y;
+          } else {
+            vf[2 * j] = vf[2 * j + 1] = 0.0f;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < SIMT_HPW; ++u) {
+          const float pt = __shfl_sync(0xffffffffu, p[u], tk);
+#pragma unroll
+          for (int c = 0; c < 16; ++c) acc[u][c] = fmaf(pt, vf[c], acc[u][c]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < SIMT_HPW; ++u) {
+      const int h = hbase + u;
+      if (h < a.H) {
+        if (lane == 0) {
+          a.part_m[(long long)seg.part * a.H + h] = m[u];
+          a.part_l[(long long)seg.part * a.H + h] = l[u];
+        }
+        float* o = a.part_o + ((long long)seg.part * a.H + h) * a.d_v;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j * 64 < a.d_v)
+            *reinterpret_cast<float2*>(o + j * 64 + lane * 2) = make_float2(acc[u][2 * j], acc[u][2 * j + 1]);
+      }
+    }
+  }
+}
+
+void launch_attn_simt(const AttnArgs& a, cudaStream_t st) {
+  if (a.n_segs <= 0) return;
+  const size_t smem = (size_t)a.H * a.d_qk * 2 + (size_t)SIMT_TILE * (a.row * 2 + 16);
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaFuncSetAttribute(k_attn_simt, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    configured = smem;
+  }
+  k_attn_simt<<<a.n_segs, 256, smem, st>>>(a);
+}
+
+// ---- log-sum-exp merge ---------------------------------------------------------------------
+// out = sum_p e^{m_p - M} O_p / (sum_p e^{m_p - M} l_p [+ e^{sink - M}] + 1e-12); the sink and
+// the 1e-12 guard are those of the reference softmax (src/fst_engine.cpp:3623, 3636, 3646).
+// V4 applies the inverse RoPE of 3716 to the rounded output tail.
+__device__ __forceinline__ void finish_row(float* s_out, bf16* o_row, const float* lut, int d_v,
+                                           int rope, int inv_rope) {
+  if (inv_rope) {
+    __syncthreads();
+    for (int p = threadIdx.x; p < rope / 2; p += blockDim.x) {
+      const int j = d_v - rope + 2 * p;
+      const float c = lut[2 * p], s = -lut[2 * p + 1], x0 = s_out[j], x1 = s_out[j + 1];
+      s_out[j] = x0 * c - x1 * s;
+      s_out[j + 1] = x0 * s + x1 * c;
+    }
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < d_v; j += blockDim.x) o_row[j] = f2bf(s_out[j]);
+}
+
+__global__ void __launch_bounds__(128) k_merge(MergeArgs a) {
+  __shared__ float s_out[1024];
+  const int r = blockIdx.x, t = r / a.H, h = r % a.H;
+  const int p0 = a.tok_part[t], p1 = a.tok_part[t + 1];
+  const bool sink = a.sinks != nullptr;
+  float M = sink ? a.sinks[h] : -INFINITY;
+  for (int p = p0; p < p1; ++p) M = fmaxf(M, a.part_m[(long long)p * a.H + h]);
+  float den = sink ? expf(a.sinks[h] - M) : 0.0f;
+  float acc[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
+  for (int p = p0; p < p1; ++p) {
+    const float mp = a.part_m[(long long)p * a.H + h];
+    if (mp == -INFINITY) continue;
+    const float w = expf(mp - M);
+    den += w * a.part_l[(long long)p * a.H + h];
+    const float* o = a.part_o + ((long long)p * a.H + h) * a.d_v;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int j = threadIdx.x + c * 128;
+      if (j < a.d_v) acc[c] = fmaf(w, o[j], acc[c]);
+    }
+  }
+  if (a.mode == 1) {
+    float* o = a.rank_partial + (long long)r * (2 + a.d_v);
+    if (threadIdx.x == 0) {
+      o[0] = M;
+      o[1] = den;
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int j = threadIdx.x + c * 128;
+      if (j < a.d_v) o[2 + j] = acc[c];
+    }
+    return;
+  }
+  const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int j = threadIdx.x + c * 128;
+    if (j < a.d_v) s_out[j] = rbf(acc[c] * inv);
+  }
+  finish_row(s_out, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope,
+             a.inv_rope);
+}
+
+void launch_merge(const MergeArgs& a, cudaStream_t st) {
+  if (a.T <= 0) return;
+  k_merge<<<a.T * a.H, 128, 0, st>>>(a);
+}
+
+__global__ void __launch_bounds__(128) k_merge_gathered(MergeGatheredArgs a) {
+  __shared__ float s_out[1024];
+  const int r = blockIdx.x, t = r / a.H, h = r % a.H;
+  const long long rows = (long long)a.T * a.H, w_row = 2 + a.d_v;
+  const bool sink = a.sinks != nullptr;
+  float M = sink ? a.sinks[h] : -INFINITY;
+  for (int p = 0; p < a.n_parts; ++p) M = fmaxf(M, a.parts[(p * rows + r) * w_row]);
+  float den = sink ? expf(a.sinks[h] - M) : 0.0f;
+  float acc[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
+  for (int p = 0; p < a.n_parts; ++p) {
+    const float* pr = a.parts + (p * rows + r) * w_row;
+    if (pr[0] == -INFINITY) continue;
+    const float w = expf(pr[0] - M);
+    den += w * pr[1];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int j = threadIdx.x + c * 128;
+      if (j < a.d_v) acc[c] = fmaf(w, pr[2 + j], acc[c]);
+    }
+  }
+  const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int j = threadIdx.x + c * 128;
+    if (j < a.d_v) s_out[j] = rbf(acc[c] * inv);
+  }
+  finish_row(s_out, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope,
+             a.inv_rope);
+}
+
+void launch_merge_gathered(const MergeGatheredArgs& a, cudaStream_t st) {
+  if (a.T <= 0) return;
+  k_merge_gathered<<<a.T * a.H, 128, 0, st>>>(a);
+}
+
+// Zero whole cache rows (speculative rollback, reference src/fst_engine.cpp:6132-6147).
+__global__ void k_zero_rows(bf16* pool, const long long* row_off, int row) {
+  bf16* p = pool + row_off[blockIdx.x];
+  for (int j = threadIdx.x; j < row; j += blockDim.x) p[j] = f2bf(0.0f);
+}
+
+void launch_zero_rows(bf16* pool, const long long* row_off, int n_rows, int row, cudaStream_t st) {
+  if (n_rows <= 0) return;
+  k_zero_rows<<<n_rows, 128, 0, st>>>(pool, row_off, row);
+}
+
+}  // namespace fst

@@ -1,0 +1,1050 @@
+// Context, paged-cache bookkeeping, split-KV planning and the C ABI of the MLA path.
+// Host-side logic only; the kernels live in kernels_simt.cu, gemm_tc.cu and attn_tc.cu.
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/fst_cuda_mla.h"
+#include "kernels.cuh"
+
+using namespace fst;
+
+namespace {
+
+thread_local std::string g_err;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+#define CU(call)                                                                           \
+  do {                                                                                     \
+    cudaError_t e_ = (call);                                                               \
+    if (e_ != cudaSuccess)                                                                 \
+      return fail(FST_MLA_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), \
+                  __FILE__, __LINE__);                                                     \
+  } while (0)
+
+struct Dims {
+  int H, hidden, q_lora, kv_lora, nope, rope, v_head, row, d_qk, d_v, q_head, low, cmp_n;
+  bool v4;
+};
+
+struct LayerW {
+  bf16 *w_cmp = nullptr, *wq_b = nullptr, *wkv_b = nullptr, *wo_a = nullptr, *wo_b = nullptr;
+  bf16 *q_norm = nullptr, *kv_norm = nullptr;
+  float* sinks = nullptr;
+  bool set = false;
+};
+
+constexpr int ATTN_TILE = 128;      // split boundaries are multiples of this many cached rows
+constexpr int MAX_EVENT_SETS = 256;
+
+struct EventSet {
+  cudaEvent_t ev[FST_MLA_K_COUNT + 1];
+  bool used[FST_MLA_K_COUNT + 1];
+};
+
+}  // namespace
+
+struct FstMlaCtx {
+  FstMlaConfig cfg;
+  Dims d;
+  int n_sm = 0;
+  cudaStream_t stream = nullptr;
+  std::vector<LayerW> layers;
+  std::vector<bf16*> pools;  // per layer [n_pages * page_tokens, row]
+
+  // paged-cache bookkeeping (host)
+  std::vector<int32_t> free_pages, free_seqs;
+  std::vector<std::vector<int32_t>> tables;
+  std::vector<int32_t> lens;
+  std::vector<char> live;
+
+  // workspaces
+  bf16 *d_h = nullptr, *d_cmp = nullptr, *d_qc = nullptr, *d_kvnew = nullptr, *d_qfull = nullptr;
+  bf16 *d_qeff = nullptr, *d_olat = nullptr, *d_low = nullptr, *d_out = nullptr;
+  float *d_part_m = nullptr, *d_part_l = nullptr, *d_part_o = nullptr;
+  int max_parts = 0;
+  uint16_t* h_pinned = nullptr;  // [max_tokens, hidden] staging for the host-buffer entry point
+  int* d_status = nullptr;
+
+  // plan (device)
+  float* d_lut = nullptr;
+  long long* d_dst = nullptr;
+  int32_t *d_tables = nullptr, *d_tok_table = nullptr, *d_cta_seg = nullptr, *d_tok_part = nullptr;
+  AttnSeg* d_segs = nullptr;
+  int tables_cap = 0, segs_cap = 0;
+  // plan (host)
+  bool planned = false;
+  int T = 0, n_segs = 0, n_parts = 0, n_ctas = 0;
+  long long kv_rows = 0;
+
+  int64_t launches = 0;
+  bool profiling = false;
+  std::vector<EventSet> ev_pool;
+  int ev_used = 0;
+  float k_ms[FST_MLA_K_COUNT] = {0};
+  int32_t k_n[FST_MLA_K_COUNT] = {0};
+  EventSet* cur = nullptr;
+};
+
+namespace {
+
+Dims dims_of(const FstMlaConfig& c) {
+  Dims d;
+  d.v4 = c.preset == FST_MLA_PRESET_FASTAR_V4;
+  d.H = c.n_heads;
+  d.hidden = c.hidden;
+  d.q_lora = c.q_lora;
+  d.kv_lora = c.kv_lora;
+  d.rope = c.qk_rope;
+  if (!d.v4) {
+    d.nope = c.qk_nope;
+    d.v_head = c.v_head;
+    d.row = c.kv_lora + c.qk_rope;
+    d.d_qk = d.row;
+    d.d_v = c.kv_lora;
+    d.q_head = c.qk_nope + c.qk_rope;
+    d.low = c.n_heads * c.v_head;
+  } else {
+    d.nope = c.kv_lora - c.qk_rope;
+    d.v_head = 0;
+    d.row = c.kv_lora;
+    d.d_qk = c.kv_lora;
+    d.d_v = c.kv_lora;
+    d.q_head = c.kv_lora;
+    d.low = c.o_groups * c.o_lora;
+  }
+  d.cmp_n = d.q_lora + d.row;
+  return d;
+}
+
+// RoPE table of one position, the recurrence of build_rope_lut (reference
+// src/fst_engine.cpp:1970-2023): theta_0 = pos, theta_{j+1} = theta_j * base^(-2/rope_dim) in
+// fp32; YaRN layers mix theta/16 and theta through the correction ramp (1995-2022).  The
+// table stays fp32 (the reference rounds it to bf16, 1988-1989).
+void rope_lut_row(float* lut, int pos, int rope_dim, float theta, bool yarn) {
+  const float freq_base = yarn ? 160000.0f : theta;
+  const float theta_scale = std::pow(freq_base, -2.0f / (float)rope_dim);
+  float th = (float)pos;
+  float corr0 = 0, corr1 = 0;
+  if (yarn) {
+    auto corr_dim = [&](float beta) {
+      return (float)rope_dim * std::log(65536.0f / (beta * 2.0f * (float)M_PI)) / (2.0f * std::log(freq_base));
+    };
+    corr0 = std::max(0.0f, std::floor(corr_dim(32.0f)));
+    corr1 = std::min((float)(rope_dim - 1), std::ceil(corr_dim(1.0f)));
+  }
+  for (int dd = 0; dd < rope_dim; dd += 2) {
+    float ang = th;
+    if (yarn) {
+      const float y = ((float)(dd / 2) - corr0) / std::max(0.001f, corr1 - corr0);
+      const float mix = 1.0f - std::min(1.0f, std::max(0.0f, y));
+      ang = (th / 16.0f) * (1.0f - mix) + th * mix;
+    }
+    lut[dd] = std::cos(ang);
+    lut[dd + 1] = std::sin(ang);
+    th *= theta_scale;
+  }
+}
+
+bool seq_ok(const FstMlaCtx* c, int32_t s) { return s >= 0 && s < c->cfg.max_seqs && c->live[s]; }
+
+int reserve_pages(FstMlaCtx* c, int32_t seq, int32_t n_tokens) {
+  const size_t need = ((size_t)n_tokens + c->cfg.page_tokens - 1) / c->cfg.page_tokens;
+  auto& t = c->tables[seq];
+  if (need > t.size() && need - t.size() > c->free_pages.size())
+    return fail(FST_MLA_ERR_PAGES, "page pool exhausted: sequence %d needs %zu more pages, %zu free", seq,
+                need - t.size(), c->free_pages.size());
+  while (t.size() < need) {
+    t.push_back(c->free_pages.back());
+    c->free_pages.pop_back();
+  }
+  c->lens[seq] = std::max(c->lens[seq], n_tokens);
+  return FST_MLA_OK;
+}
+
+long long row_offset(const FstMlaCtx* c, int32_t seq, int32_t pos) {
+  const int pt = c->cfg.page_tokens;
+  return ((long long)c->tables[seq][pos / pt] * pt + pos % pt) * c->d.row;
+}
+
+template <class T>
+int dev_alloc(T** p, size_t n) {
+  CU(cudaMalloc((void**)p, std::max<size_t>(n, 1) * sizeof(T)));
+  return FST_MLA_OK;
+}
+
+void prof_mark(FstMlaCtx* c, int k) {
+  if (!c->cur) return;
+  cudaEventRecord(c->cur->ev[k], c->stream);
+  c->cur->used[k] = true;
+}
+
+int prof_flush(FstMlaCtx* c) {
+  if (c->ev_used == 0) return FST_MLA_OK;
+  CU(cudaStreamSynchronize(c->stream));
+  for (int i = 0; i < c->ev_used; ++i) {
+    EventSet& es = c->ev_pool[i];
+    // a kernel's time runs from its own mark to the next mark that was recorded
+    for (int k = 0; k < FST_MLA_K_COUNT; ++k) {
+      if (!es.used[k]) continue;
+      int nx = k + 1;
+      while (nx <= FST_MLA_K_COUNT && !es.used[nx]) ++nx;
+      if (nx > FST_MLA_K_COUNT) continue;
+      float ms = 0;
+      if (cudaEventElapsedTime(&ms, es.ev[k], es.ev[nx]) == cudaSuccess) {
+        c->k_ms[k] += ms;
+        c->k_n[k] += 1;
+      }
+    }
+    memset(es.used, 0, sizeof(es.used));
+  }
+  c->ev_used = 0;
+  return FST_MLA_OK;
+}
+
+int prof_begin(FstMlaCtx* c) {
+  c->cur = nullptr;
+  if (!c->profiling) return FST_MLA_OK;
+  if (c->ev_used == MAX_EVENT_SETS) {
+    int rc = prof_flush(c);
+    if (rc) return rc;
+  }
+  if ((int)c->ev_pool.size() <= c->ev_used) {
+    EventSet es;
+    memset(es.used, 0, sizeof(es.used));
+    for (auto& e : es.ev) CU(cudaEventCreate(&e));
+    c->ev_pool.push_back(es);
+  }
+  c->cur = &c->ev_pool[c->ev_used++];
+  return FST_MLA_OK;
+}
+
+bool use_tc_gemm(const FstMlaCtx* c, const GemmArgs& g) {
+  if (c->cfg.gemm_impl == FST_MLA_IMPL_SIMT) return false;
+  return gemm_tc_supported(g);
+}
+
+int run_gemm(FstMlaCtx* c, const GemmArgs& g) {
+  if (c->cfg.gemm_impl == FST_MLA_IMPL_TENSOR && !gemm_tc_supported(g))
+    return fail(FST_MLA_ERR_ARG, "GEMM %dx%dx%d (b_kn=%d) has no tcgen05 path", g.M, g.N, g.K, g.b_kn);
+  if (use_tc_gemm(c, g)) {
+    cudaError_t e = launch_gemm_tc(g, c->d_status, c->stream);
+    if (e != cudaSuccess) return fail(FST_MLA_ERR_CUDA, "tcgen05 GEMM launch: %s", cudaGetErrorString(e));
+  } else {
+    launch_gemm_simt(g, c->stream);
+  }
+  c->launches += 1;
+  return FST_MLA_OK;
+}
+
+GemmArgs plain_gemm(const bf16* A, const bf16* B, bf16* C, int M, int N, int K) {
+  GemmArgs g;
+  g.A = A; g.B = B; g.C = C;
+  g.M = M; g.N = N; g.K = K;
+  g.lda = K; g.ldb = K; g.ldc = N;
+  g.batch = 1; g.a_bs = g.b_bs = g.c_bs = 0;
+  g.b_kn = 0;
+  return g;
+}
+
+AttnArgs attn_args(FstMlaCtx* c, int lid, const bf16* q_eff) {
+  AttnArgs a;
+  a.q_eff = q_eff;
+  a.pool = c->pools[lid];
+  a.tables = c->d_tables;
+  a.tok_table = c->d_tok_table;
+  a.segs = c->d_segs;
+  a.cta_seg = c->d_cta_seg;
+  a.part_m = c->d_part_m;
+  a.part_l = c->d_part_l;
+  a.part_o = c->d_part_o;
+  a.d_status = c->d_status;
+  a.n_segs = c->n_segs;
+  a.n_ctas = c->n_ctas;
+  a.H = c->d.H;
+  a.d_qk = c->d.d_qk;
+  a.d_v = c->d.d_v;
+  a.row = c->d.row;
+  a.page_tokens = c->cfg.page_tokens;
+  a.pool_rows = (long long)c->cfg.n_pages * c->cfg.page_tokens;
+  a.q_rows = (long long)c->T * c->d.H;
+  a.scale = c->cfg.softmax_scale;
+  return a;
+}
+
+int run_attention(FstMlaCtx* c, int lid, const bf16* q_eff) {
+  if (c->n_segs == 0) return FST_MLA_OK;
+  AttnArgs a = attn_args(c, lid, q_eff);
+  const bool tc_ok = attn_tc_supported(a);
+  if (c->cfg.attn_impl == FST_MLA_IMPL_TENSOR && !tc_ok)
+    return fail(FST_MLA_ERR_ARG, "this shape has no tcgen05 attention path");
+  if (c->cfg.attn_impl != FST_MLA_IMPL_SIMT && tc_ok) {
+    cudaError_t e = launch_attn_tc(a, c->stream);
+    if (e != cudaSuccess) return fail(FST_MLA_ERR_CUDA, "tcgen05 attention launch: %s", cudaGetErrorString(e));
+  } else {
+    launch_attn_simt(a, c->stream);
+  }
+  c->launches += 1;
+  return FST_MLA_OK;
+}
+
+// Stages before the attention: projections, norms, RoPE, cache append, absorbed query.
+int run_front(FstMlaCtx* c, int lid, const bf16* h_in) {
+  const Dims& d = c->d;
+  const LayerW& w = c->layers[lid];
+  const int T = c->T;
+  int rc;
+  prof_mark(c, FST_MLA_K_COMPRESS);
+  if ((rc = run_gemm(c, plain_gemm(h_in, w.w_cmp, c->d_cmp, T, d.cmp_n, d.hidden)))) return rc;
+  prof_mark(c, FST_MLA_K_NORM_APPEND);
+  NormAppendArgs na;
+  na.cmp = c->d_cmp; na.q_norm = w.q_norm; na.kv_norm = w.kv_norm; na.lut = c->d_lut;
+  na.dst_row = c->d_dst; na.qc = c->d_qc; na.kv_new = c->d_kvnew; na.pool = c->pools[lid];
+  na.T = T; na.q_lora = d.q_lora; na.kv_lora = d.kv_lora; na.row = d.row; na.rope = d.rope;
+  na.eps = c->cfg.rms_eps;
+  launch_norm_append(na, c->stream);
+  c->launches += 1;
+  prof_mark(c, FST_MLA_K_Q_EXPAND);
+  if ((rc = run_gemm(c, plain_gemm(c->d_qc, w.wq_b, c->d_qfull, T, d.H * d.q_head, d.q_lora)))) return rc;
+  prof_mark(c, FST_MLA_K_Q_ABSORB);
+  QPrepArgs qp;
+  qp.q_full = c->d_qfull; qp.lut = c->d_lut; qp.q_eff = c->d_qeff;
+  qp.T = T; qp.H = d.H; qp.q_head = d.q_head; qp.nope = d.nope; qp.rope = d.rope; qp.d_qk = d.d_qk;
+  qp.v4 = d.v4; qp.eps = c->cfg.rms_eps;
+  launch_q_prep(qp, c->stream);
+  c->launches += 1;
+  if (!d.v4) {
+    // q_lat[h] = q_nope[h] (128) * W_UK[h] ([128, 512], a [K, N] operand), one batch member per head
+    GemmArgs g;
+    g.A = c->d_qfull; g.B = w.wkv_b; g.C = c->d_qeff;
+    g.M = T; g.N = d.kv_lora; g.K = d.nope;
+    g.lda = d.H * d.q_head; g.ldb = d.kv_lora; g.ldc = d.H * d.d_qk;
+    g.batch = d.H; g.a_bs = d.q_head; g.b_bs = (long long)(d.nope + d.v_head) * d.kv_lora; g.c_bs = d.d_qk;
+    g.b_kn = 1;
+    if ((rc = run_gemm(c, g))) return rc;
+  }
+  return FST_MLA_OK;
+}
+
+// Output projections a and b.
+int run_back(FstMlaCtx* c, int lid, bf16* h_out) {
+  const Dims& d = c->d;
+  const LayerW& w = c->layers[lid];
+  const int T = c->T;
+  int rc;
+  prof_mark(c, FST_MLA_K_OPROJ_A);
+  GemmArgs g;
+  g.A = c->d_olat; g.C = c->d_low; g.M = T; g.b_kn = 0;
+  g.lda = d.H * d.d_v; g.ldc = d.low;
+  if (d.v4) {
+    // 8 groups: low[:, g*o_lora:] = heads[:, g*gk:(g+1)*gk] * wo_a[g]^T (reference 3736-3839)
+    const int gk = d.H * d.d_v / c->cfg.o_groups;
+    g.B = w.wo_a; g.N = c->cfg.o_lora; g.K = gk; g.ldb = gk;
+    g.batch = c->cfg.o_groups; g.a_bs = gk; g.b_bs = (long long)c->cfg.o_lora * gk; g.c_bs = c->cfg.o_lora;
+  } else {
+    // per-head W_UV: low[:, h*v_head:] = o_lat[:, h, :] * W_UV[h]^T
+    g.B = w.wkv_b + (long long)d.nope * d.kv_lora; g.N = d.v_head; g.K = d.d_v; g.ldb = d.kv_lora;
+    g.batch = d.H; g.a_bs = d.d_v; g.b_bs = (long long)(d.nope + d.v_head) * d.kv_lora; g.c_bs = d.v_head;
+  }
+  if ((rc = run_gemm(c, g))) return rc;
+  prof_mark(c, FST_MLA_K_OPROJ_B);
+  if ((rc = run_gemm(c, plain_gemm(c->d_low, w.wo_b, h_out, T, d.hidden, d.low)))) return rc;
+  prof_mark(c, FST_MLA_K_COUNT);
+  return FST_MLA_OK;
+}
+
+int run_merge_local(FstMlaCtx* c, int lid, int mode, float* rank_partial) {
+  const Dims& d = c->d;
+  MergeArgs m;
+  m.part_m = c->d_part_m; m.part_l = c->d_part_l; m.part_o = c->d_part_o; m.tok_part = c->d_tok_part;
+  m.sinks = (d.v4 && mode == 0) ? c->layers[lid].sinks : nullptr;
+  m.lut = c->d_lut; m.o_lat = c->d_olat; m.rank_partial = rank_partial;
+  m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope; m.inv_rope = d.v4 ? 1 : 0; m.mode = mode;
+  launch_merge(m, c->stream);
+  c->launches += 1;
+  return FST_MLA_OK;
+}
+
+int check_run(FstMlaCtx* c, int lid) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (lid < 0 || lid >= c->cfg.n_layers) return fail(FST_MLA_ERR_ARG, "layer %d out of range", lid);
+  if (!c->layers[lid].set) return fail(FST_MLA_ERR_STATE, "layer %d has no weights", lid);
+  if (!c->planned) return fail(FST_MLA_ERR_STATE, "no plan: call fst_cuda_mla_plan first");
+  return FST_MLA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* fst_cuda_mla_last_error(void) { return g_err.c_str(); }
+
+int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
+  if (!cfg || !out) return fail(FST_MLA_ERR_ARG, "null argument");
+  *out = nullptr;
+  FstMlaConfig c = *cfg;
+  if (c.preset != FST_MLA_PRESET_BASELINE && c.preset != FST_MLA_PRESET_FASTAR_V4)
+    return fail(FST_MLA_ERR_ARG, "unknown preset %d", c.preset);
+  if (c.hidden <= 0 || c.n_heads <= 0 || c.q_lora <= 0 || c.kv_lora <= 0 || c.qk_rope <= 0 ||
+      c.qk_rope % 2 || c.n_layers <= 0 || c.page_tokens <= 0 || c.n_pages <= 0 || c.max_seqs <= 0 ||
+      c.max_tokens <= 0)
+    return fail(FST_MLA_ERR_ARG, "non-positive dimension in FstMlaConfig");
+  if (c.preset == FST_MLA_PRESET_BASELINE && (c.qk_nope <= 0 || c.v_head <= 0))
+    return fail(FST_MLA_ERR_ARG, "BASELINE preset needs qk_nope and v_head");
+  if (c.preset == FST_MLA_PRESET_FASTAR_V4 &&
+      (c.o_groups <= 0 || c.o_lora <= 0 || (c.n_heads * c.kv_lora) % c.o_groups || c.qk_rope >= c.kv_lora))
+    return fail(FST_MLA_ERR_ARG, "V4 preset needs o_groups dividing n_heads*kv_lora and o_lora");
+  Dims d = dims_of(c);
+  if (d.row % 8 || d.d_qk % 8 || d.d_v % 64 || d.d_v > 512 || d.q_head > 1024 || d.row > 1024)
+    return fail(FST_MLA_ERR_ARG, "row width must be a multiple of 8 and d_v a multiple of 64 (<= 512)");
+  if (c.softmax_scale <= 0)
+    c.softmax_scale = 1.0f / std::sqrt((float)(d.v4 ? c.kv_lora : c.qk_nope + c.qk_rope));
+  if (c.rope_theta <= 0) c.rope_theta = 10000.0f;
+  if (c.rms_eps <= 0) c.rms_eps = 1e-6f;
+
+  int n_dev = 0;
+  if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0) {
+    cudaGetLastError();
+    return fail(FST_MLA_ERR_NO_DEVICE, "no CUDA device: this path has no CPU fallback");
+  }
+  if (c.device < 0 || c.device >= n_dev) return fail(FST_MLA_ERR_ARG, "device %d of %d", c.device, n_dev);
+  CU(cudaSetDevice(c.device));
+  cudaDeviceProp prop;
+  CU(cudaGetDeviceProperties(&prop, c.device));
+  if (prop.major != 10)
+    return fail(FST_MLA_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only",
+                c.device, prop.major, prop.minor);
+
+  FstMlaCtx* x = new FstMlaCtx;
+  x->cfg = c;
+  x->d = d;
+  x->n_sm = prop.multiProcessorCount;
+  x->layers.resize(c.n_layers);
+  x->pools.assign(c.n_layers, nullptr);
+  for (int i = c.n_pages - 1; i >= 0; --i) x->free_pages.push_back(i);
+  for (int i = c.max_seqs - 1; i >= 0; --i) x->free_seqs.push_back(i);
+  x->tables.resize(c.max_seqs);
+  x->lens.assign(c.max_seqs, 0);
+  x->live.assign(c.max_seqs, 0);
+  *out = x;  // from here on destroy() cleans up after a failure
+
+  const size_t pool_elems = (size_t)c.n_pages * c.page_tokens * d.row;
+  const size_t T = c.max_tokens;
+  int rc = FST_MLA_OK;
+  for (int l = 0; l < c.n_layers && !rc; ++l) {
+    rc = dev_alloc(&x->pools[l], pool_elems);
+    if (!rc && cudaMemset(x->pools[l], 0, pool_elems * sizeof(bf16)) != cudaSuccess)
+      rc = fail(FST_MLA_ERR_CUDA, "cudaMemset(pool) failed");
+  }
+  x->max_parts = x->n_sm + (int)T;
+  if (!rc) rc = dev_alloc(&x->d_h, T * d.hidden);
+  if (!rc) rc = dev_alloc(&x->d_cmp, T * d.cmp_n);
+  if (!rc) rc = dev_alloc(&x->d_qc, T * d.q_lora);
+  if (!rc) rc = dev_alloc(&x->d_kvnew, T * d.row);
+  if (!rc) rc = dev_alloc(&x->d_qfull, T * d.H * d.q_head);
+  if (!rc) rc = dev_alloc(&x->d_qeff, T * d.H * d.d_qk);
+  if (!rc) rc = dev_alloc(&x->d_olat, T * d.H * d.d_v);
+  if (!rc) rc = dev_alloc(&x->d_low, T * d.low);
+  if (!rc) rc = dev_alloc(&x->d_out, T * d.hidden);
+  if (!rc) rc = dev_alloc(&x->d_part_m, (size_t)x->max_parts * d.H);
+  if (!rc) rc = dev_alloc(&x->d_part_l, (size_t)x->max_parts * d.H);
+  if (!rc) rc = dev_alloc(&x->d_part_o, (size_t)x->max_parts * d.H * d.d_v);
+  if (!rc) rc = dev_alloc(&x->d_lut, T * d.rope);
+  if (!rc) rc = dev_alloc(&x->d_dst, T);
+  if (!rc) rc = dev_alloc(&x->d_tok_table, T);
+  if (!rc) rc = dev_alloc(&x->d_tok_part, T + 1);
+  if (!rc) rc = dev_alloc(&x->d_cta_seg, (size_t)x->n_sm + 1);
+  x->segs_cap = x->max_parts;
+  if (!rc) rc = dev_alloc(&x->d_segs, (size_t)x->segs_cap);
+  x->tables_cap = c.n_pages + c.max_seqs;
+  if (!rc) rc = dev_alloc(&x->d_tables, (size_t)x->tables_cap);
+  if (!rc) rc = dev_alloc(&x->d_status, 1);
+  if (!rc && cudaMemset(x->d_status, 0, sizeof(int)) != cudaSuccess) rc = fail(FST_MLA_ERR_CUDA, "cudaMemset failed");
+  if (!rc && cudaHostAlloc((void**)&x->h_pinned, T * d.hidden * sizeof(uint16_t), cudaHostAllocDefault) != cudaSuccess)
+    rc = fail(FST_MLA_ERR_CUDA, "cudaHostAlloc failed");
+  if (rc) {
+    std::string keep = g_err;
+    fst_cuda_mla_destroy(x);
+    *out = nullptr;
+    g_err = keep;
+    return rc;
+  }
+  return FST_MLA_OK;
+}
+
+void fst_cuda_mla_destroy(FstMlaCtx* c) {
+  if (!c) return;
+  cudaSetDevice(c->cfg.device);
+  cudaDeviceSynchronize();
+  for (auto& l : c->layers) {
+    cudaFree(l.w_cmp); cudaFree(l.wq_b); cudaFree(l.wkv_b); cudaFree(l.wo_a); cudaFree(l.wo_b);
+    cudaFree(l.q_norm); cudaFree(l.kv_norm); cudaFree(l.sinks);
+  }
+  for (auto p : c->pools) cudaFree(p);
+  cudaFree(c->d_h); cudaFree(c->d_cmp); cudaFree(c->d_qc); cudaFree(c->d_kvnew); cudaFree(c->d_qfull);
+  cudaFree(c->d_qeff); cudaFree(c->d_olat); cudaFree(c->d_low); cudaFree(c->d_out);
+  cudaFree(c->d_part_m); cudaFree(c->d_part_l); cudaFree(c->d_part_o);
+  cudaFree(c->d_lut); cudaFree(c->d_dst); cudaFree(c->d_tables); cudaFree(c->d_tok_table);
+  cudaFree(c->d_cta_seg); cudaFree(c->d_tok_part); cudaFree(c->d_segs); cudaFree(c->d_status);
+  if (c->h_pinned) cudaFreeHost(c->h_pinned);
+  for (auto& es : c->ev_pool)
+    for (auto& e : es.ev) cudaEventDestroy(e);
+  delete c;
+}
+
+int fst_cuda_mla_set_stream(FstMlaCtx* c, void* s) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  CU(cudaStreamSynchronize(c->stream));
+  c->stream = (cudaStream_t)s;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_sync(FstMlaCtx* c) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  CU(cudaStreamSynchronize(c->stream));
+  int st = 0;
+  CU(cudaMemcpy(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (st != 0) {
+    cudaMemset(c->d_status, 0, sizeof(int));
+    return fail(FST_MLA_ERR_DEVICE_CHECK, "a kernel gave up a bounded wait (status %d)", st);
+  }
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_set_layer_weights(FstMlaCtx* c, int lid, const FstMlaWeights* w) {
+  if (!c || !w) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (lid < 0 || lid >= c->cfg.n_layers) return fail(FST_MLA_ERR_ARG, "layer %d out of range", lid);
+  const Dims& d = c->d;
+  const bool need_b = !d.v4;
+  if (!w->wq_a || !w->wq_b || !w->wkv_a || !w->wo_b || (need_b && !w->wkv_b) || (d.v4 && !w->wo_a))
+    return fail(FST_MLA_ERR_ARG, "a weight matrix this preset needs is NULL");
+  CU(cudaSetDevice(c->cfg.device));
+  LayerW& L = c->layers[lid];
+  auto up = [&](bf16** dst, const uint16_t* src, size_t n) -> int {
+    if (!*dst) {
+      int rc = dev_alloc(dst, n);
+      if (rc) return rc;
+    }
+    CU(cudaMemcpy(*dst, src, n * sizeof(bf16), cudaMemcpyHostToDevice));
+    return FST_MLA_OK;
+  };
+  int rc;
+  // [wq_a; wkv_a] stacked so that both compressions are one GEMM over h
+  if (!L.w_cmp && (rc = dev_alloc(&L.w_cmp, (size_t)d.cmp_n * d.hidden))) return rc;
+  CU(cudaMemcpy(L.w_cmp, w->wq_a, (size_t)d.q_lora * d.hidden * 2, cudaMemcpyHostToDevice));
+  CU(cudaMemcpy(L.w_cmp + (size_t)d.q_lora * d.hidden, w->wkv_a, (size_t)d.row * d.hidden * 2, cudaMemcpyHostToDevice));
+  if ((rc = up(&L.wq_b, w->wq_b, (size_t)d.H * d.q_head * d.q_lora))) return rc;
+  if (need_b && (rc = up(&L.wkv_b, w->wkv_b, (size_t)d.H * (d.nope + d.v_head) * d.kv_lora))) return rc;
+  if (d.v4 && (rc = up(&L.wo_a, w->wo_a, (size_t)d.low * (d.H * d.d_v / c->cfg.o_groups)))) return rc;
+  if ((rc = up(&L.wo_b, w->wo_b, (size_t)d.hidden * d.low))) return rc;
+  if (w->q_norm) {
+    if ((rc = up(&L.q_norm, w->q_norm, d.q_lora))) return rc;
+  } else if (L.q_norm) {
+    cudaFree(L.q_norm);
+    L.q_norm = nullptr;
+  }
+  if (w->kv_norm) {
+    if ((rc = up(&L.kv_norm, w->kv_norm, d.kv_lora))) return rc;
+  } else if (L.kv_norm) {
+    cudaFree(L.kv_norm);
+    L.kv_norm = nullptr;
+  }
+  if (d.v4) {
+    if (!L.sinks && (rc = dev_alloc(&L.sinks, (size_t)d.H))) return rc;
+    if (w->attn_sinks)
+      CU(cudaMemcpy(L.sinks, w->attn_sinks, d.H * sizeof(float), cudaMemcpyHostToDevice));
+    else
+      CU(cudaMemset(L.sinks, 0, d.H * sizeof(float)));  // empty sinks: logit 0 (reference 3623)
+  }
+  L.set = true;
+  return FST_MLA_OK;
+}
+
+/* ---- paged cache ---------------------------------------------------------------------- */
+int fst_cuda_mla_seq_alloc(FstMlaCtx* c, int32_t* seq_out) {
+  if (!c || !seq_out) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (c->free_seqs.empty()) return fail(FST_MLA_ERR_CAPACITY, "all %d sequence slots are in use", c->cfg.max_seqs);
+  int s = c->free_seqs.back();
+  c->free_seqs.pop_back();
+  c->live[s] = 1;
+  c->lens[s] = 0;
+  c->tables[s].clear();
+  *seq_out = s;
+  c->planned = false;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_seq_truncate(FstMlaCtx* c, int32_t seq, int32_t n_tokens) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (!seq_ok(c, seq)) return fail(FST_MLA_ERR_ARG, "sequence %d is not allocated", seq);
+  if (n_tokens < 0 || n_tokens > c->lens[seq])
+    return fail(FST_MLA_ERR_ARG, "truncate to %d outside [0, %d]", n_tokens, c->lens[seq]);
+  CU(cudaSetDevice(c->cfg.device));
+  // zero the dropped rows in every layer, as the reference rollback does (6132-6147)
+  const int n_drop = c->lens[seq] - n_tokens;
+  if (n_drop > 0) {
+    std::vector<long long> offs(n_drop);
+    for (int i = 0; i < n_drop; ++i) offs[i] = row_offset(c, seq, n_tokens + i);
+    long long* d_offs = nullptr;
+    CU(cudaMalloc((void**)&d_offs, n_drop * sizeof(long long)));
+    cudaError_t e = cudaMemcpyAsync(d_offs, offs.data(), n_drop * sizeof(long long), cudaMemcpyHostToDevice, c->stream);
+    for (int l = 0; l < c->cfg.n_layers && e == cudaSuccess; ++l) {
+      launch_zero_rows(c->pools[l], d_offs, n_drop, c->d.row, c->stream);
+      c->launches += 1;
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    cudaFree(d_offs);
+    if (e != cudaSuccess) return fail(FST_MLA_ERR_CUDA, "rollback failed: %s", cudaGetErrorString(e));
+  }
+  const size_t keep = ((size_t)n_tokens + c->cfg.page_tokens - 1) / c->cfg.page_tokens;
+  auto& t = c->tables[seq];
+  while (t.size() > keep) {
+    c->free_pages.push_back(t.back());
+    t.pop_back();
+  }
+  c->lens[seq] = n_tokens;
+  c->planned = false;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_seq_free(FstMlaCtx* c, int32_t seq) {
+  int rc = fst_cuda_mla_seq_truncate(c, seq, 0);
+  if (rc) return rc;
+  c->live[seq] = 0;
+  c->free_seqs.push_back(seq);
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_seq_reserve(FstMlaCtx* c, int32_t seq, int32_t n_tokens) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (!seq_ok(c, seq)) return fail(FST_MLA_ERR_ARG, "sequence %d is not allocated", seq);
+  if (n_tokens < 0) return fail(FST_MLA_ERR_ARG, "negative length");
+  c->planned = false;
+  return reserve_pages(c, seq, n_tokens);
+}
+
+int fst_cuda_mla_seq_len(FstMlaCtx* c, int32_t seq, int32_t* len_out) {
+  if (!c || !len_out) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (!seq_ok(c, seq)) return fail(FST_MLA_ERR_ARG, "sequence %d is not allocated", seq);
+  *len_out = c->lens[seq];
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_reset(FstMlaCtx* c) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  CU(cudaSetDevice(c->cfg.device));
+  CU(cudaStreamSynchronize(c->stream));
+  c->free_pages.clear();
+  c->free_seqs.clear();
+  for (int i = c->cfg.n_pages - 1; i >= 0; --i) c->free_pages.push_back(i);
+  for (int i = c->cfg.max_seqs - 1; i >= 0; --i) c->free_seqs.push_back(i);
+  for (auto& t : c->tables) t.clear();
+  std::fill(c->lens.begin(), c->lens.end(), 0);
+  std::fill(c->live.begin(), c->live.end(), 0);
+  const size_t bytes = (size_t)c->cfg.n_pages * c->cfg.page_tokens * c->d.row * sizeof(bf16);
+  for (auto p : c->pools) CU(cudaMemsetAsync(p, 0, bytes, c->stream));
+  CU(cudaStreamSynchronize(c->stream));
+  c->planned = false;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_block_table(FstMlaCtx* c, int32_t seq, int32_t* out, int32_t cap, int32_t* n_out) {
+  if (!c || !n_out) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (!seq_ok(c, seq)) return fail(FST_MLA_ERR_ARG, "sequence %d is not allocated", seq);
+  const auto& t = c->tables[seq];
+  for (size_t i = 0; i < t.size() && (int)i < cap && out; ++i) out[i] = t[i];
+  *n_out = (int32_t)t.size();
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_free_pages(FstMlaCtx* c, int32_t* n_out) {
+  if (!c || !n_out) return fail(FST_MLA_ERR_ARG, "null argument");
+  *n_out = (int32_t)c->free_pages.size();
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_row_offset(FstMlaCtx* c, int32_t seq, int32_t pos, int64_t* off_out) {
+  if (!c || !off_out) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (!seq_ok(c, seq)) return fail(FST_MLA_ERR_ARG, "sequence %d is not allocated", seq);
+  if (pos < 0 || (size_t)pos >= c->tables[seq].size() * c->cfg.page_tokens)
+    return fail(FST_MLA_ERR_ARG, "row %d has no page", pos);
+  *off_out = row_offset(c, seq, pos);
+  return FST_MLA_OK;
+}
+
+static int cache_copy(FstMlaCtx* c, int lid, int32_t seq, int32_t pos0, int32_t n, uint16_t* rows, bool write) {
+  if (!c || (!rows && n > 0)) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (lid < 0 || lid >= c->cfg.n_layers) return fail(FST_MLA_ERR_ARG, "layer %d out of range", lid);
+  if (!seq_ok(c, seq)) return fail(FST_MLA_ERR_ARG, "sequence %d is not allocated", seq);
+  if (pos0 < 0 || n < 0) return fail(FST_MLA_ERR_ARG, "negative row range");
+  CU(cudaSetDevice(c->cfg.device));
+  if (write) {
+    int rc = reserve_pages(c, seq, pos0 + n);
+    if (rc) return rc;
+    c->planned = false;
+  } else if (pos0 + n > c->lens[seq]) {
+    return fail(FST_MLA_ERR_ARG, "rows [%d, %d) beyond the sequence length %d", pos0, pos0 + n, c->lens[seq]);
+  }
+  const int pt = c->cfg.page_tokens, row = c->d.row;
+  int done = 0;
+  while (done < n) {  // one copy per page-contiguous run
+    const int pos = pos0 + done, run = std::min(n - done, pt - pos % pt);
+    bf16* dev = c->pools[lid] + row_offset(c, seq, pos);
+    uint16_t* host = rows + (size_t)done * row;
+    if (write)
+      CU(cudaMemcpyAsync(dev, host, (size_t)run * row * 2, cudaMemcpyHostToDevice, c->stream));
+    else
+      CU(cudaMemcpyAsync(host, dev, (size_t)run * row * 2, cudaMemcpyDeviceToHost, c->stream));
+    done += run;
+  }
+  CU(cudaStreamSynchronize(c->stream));
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_cache_write(FstMlaCtx* c, int lid, int32_t seq, int32_t pos0, int32_t n, const uint16_t* rows) {
+  return cache_copy(c, lid, seq, pos0, n, const_cast<uint16_t*>(rows), true);
+}
+int fst_cuda_mla_cache_read(FstMlaCtx* c, int lid, int32_t seq, int32_t pos0, int32_t n, uint16_t* rows) {
+  return cache_copy(c, lid, seq, pos0, n, rows, false);
+}
+
+int fst_cuda_mla_pool_read(FstMlaCtx* c, int lid, uint16_t* out, size_t bytes) {
+  if (!c || !out) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (lid < 0 || lid >= c->cfg.n_layers) return fail(FST_MLA_ERR_ARG, "layer %d out of range", lid);
+  const size_t full = (size_t)c->cfg.n_pages * c->cfg.page_tokens * c->d.row * 2;
+  if (bytes > full) return fail(FST_MLA_ERR_ARG, "pool holds %zu bytes", full);
+  CU(cudaSetDevice(c->cfg.device));
+  CU(cudaStreamSynchronize(c->stream));
+  CU(cudaMemcpy(out, c->pools[lid], bytes, cudaMemcpyDeviceToHost));
+  return FST_MLA_OK;
+}
+
+/* ---- planning ------------------------------------------------------------------------- */
+int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, int32_t causal) {
+  if (!c || (!steps && n_seqs > 0)) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (n_seqs < 0) return fail(FST_MLA_ERR_ARG, "negative sequence count");
+  const Dims& d = c->d;
+  const int pt = c->cfg.page_tokens;
+  c->planned = false;
+  long long T = 0;
+  for (int b = 0; b < n_seqs; ++b) {
+    const FstMlaSeqStep& s = steps[b];
+    if (!seq_ok(c, s.seq)) return fail(FST_MLA_ERR_ARG, "step %d: sequence %d is not allocated", b, s.seq);
+    if (s.pos0 < 0 || s.q_len < 0) return fail(FST_MLA_ERR_ARG, "step %d: negative position or length", b);
+    for (int b2 = 0; b2 < b; ++b2)
+      if (steps[b2].seq == s.seq) return fail(FST_MLA_ERR_ARG, "sequence %d appears twice", s.seq);
+    T += s.q_len;
+  }
+  if (T > c->cfg.max_tokens)
+    return fail(FST_MLA_ERR_CAPACITY, "%lld new tokens exceed max_tokens %d", T, c->cfg.max_tokens);
+  CU(cudaSetDevice(c->cfg.device));
+  // reserve pages first so that a failure leaves no half-built plan (the reference asserts
+  // seq_pos_ + M <= max_seq, src/fst_engine.cpp:3327)
+  for (int b = 0; b < n_seqs; ++b) {
+    const FstMlaSeqStep& s = steps[b];
+    const int need = s.append ? s.pos0 + s.q_len : s.pos0;
+    if (!s.append && need > c->lens[s.seq])
+      return fail(FST_MLA_ERR_ARG, "step %d: rows [0, %d) are not all cached (length %d)", b, need, c->lens[s.seq]);
+    if (s.append) {
+      int rc = reserve_pages(c, s.seq, need);
+      if (rc) return rc;
+    }
+  }
+
+  std::vector<float> lut((size_t)T * d.rope);
+  std::vector<long long> dst(T);
+  std::vector<int32_t> tok_table(T), tables, kvlen(T), tok_part(T + 1);
+  int t = 0;
+  for (int b = 0; b < n_seqs; ++b) {
+    const FstMlaSeqStep& s = steps[b];
+    const int toff = (int)tables.size();
+    tables.insert(tables.end(), c->tables[s.seq].begin(), c->tables[s.seq].end());
+    const int rp0 = s.rope_pos0 >= 0 ? s.rope_pos0 : s.pos0;
+    for (int i = 0; i < s.q_len; ++i, ++t) {
+      rope_lut_row(&lut[(size_t)t * d.rope], rp0 + i, d.rope, c->cfg.rope_theta, c->cfg.rope_yarn != 0);
+      dst[t] = s.append ? row_offset(c, s.seq, s.pos0 + i) : -1;
+      tok_table[t] = toff;
+      int len = s.append ? s.pos0 + s.q_len : s.pos0;
+      if (causal && s.append) len = std::min(len, s.pos0 + i + 1);  // drop s > seq_pos_ + m (3626)
+      kvlen[t] = len;
+    }
+  }
+  if ((int)tables.size() > c->tables_cap) return fail(FST_MLA_ERR_CAPACITY, "block tables overflow");
+
+  // split-KV schedule: the concatenated ATTN_TILE-row tiles of all query tokens are cut into
+  // n_ctas contiguous, equally long runs; a run that crosses a token boundary yields one
+  // segment (and one partial) per token it touches.
+  long long total_tiles = 0, kv_rows = 0;
+  for (int i = 0; i < T; ++i) {
+    total_tiles += (kvlen[i] + ATTN_TILE - 1) / ATTN_TILE;
+    kv_rows += kvlen[i];
+  }
+  const int n_ctas = (int)std::min<long long>(c->n_sm, std::max<long long>(total_tiles, 1));
+  std::vector<AttnSeg> segs;
+  std::vector<int32_t> cta_seg(n_ctas + 1, 0);
+  {
+    int tok = 0, tile_in_tok = 0, part = 0;
+    tok_part[0] = 0;
+    auto tiles_of = [&](int i) { return (kvlen[i] + ATTN_TILE - 1) / ATTN_TILE; };
+    auto skip_empty = [&]() {
+      while (tok < T && tile_in_tok >= tiles_of(tok)) {
+        ++tok;
+        tile_in_tok = 0;
+        if (tok <= T) tok_part[tok] = part;
+      }
+    };
+    skip_empty();
+    long long given = 0;
+    for (int k = 0; k < n_ctas; ++k) {
+      cta_seg[k] = (int)segs.size();
+      long long quota = (total_tiles * (k + 1)) / n_ctas - given;
+      given += quota;
+      while (quota > 0 && tok < T) {
+        const int take = (int)std::min<long long>(quota, tiles_of(tok) - tile_in_tok);
+        AttnSeg sg;
+        sg.tok = tok;
+        sg.kv_begin = tile_in_tok * ATTN_TILE;
+        sg.kv_end = std::min(kvlen[tok], (tile_in_tok + take) * ATTN_TILE);
+        sg.part = part++;
+        segs.push_back(sg);
+        tile_in_tok += take;
+        quota -= take;
+        skip_empty();
+      }
+    }
+    cta_seg[n_ctas] = (int)segs.size();
+    while (tok < T) {
+      ++tok;
+      tok_part[tok] = part;
+    }
+  }
+  if ((int)segs.size() > c->segs_cap || (int)segs.size() > c->max_parts)
+    return fail(FST_MLA_ERR_CAPACITY, "split schedule overflow");
+
+  cudaStream_t st = c->stream;
+  if (T > 0) {
+    CU(cudaMemcpyAsync(c->d_lut, lut.data(), lut.size() * sizeof(float), cudaMemcpyHostToDevice, st));
+    CU(cudaMemcpyAsync(c->d_dst, dst.data(), T * sizeof(long long), cudaMemcpyHostToDevice, st));
+    CU(cudaMemcpyAsync(c->d_tok_table, tok_table.data(), T * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  }
+  CU(cudaMemcpyAsync(c->d_tok_part, tok_part.data(), (T + 1) * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  if (!tables.empty())
+    CU(cudaMemcpyAsync(c->d_tables, tables.data(), tables.size() * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  if (!segs.empty())
+    CU(cudaMemcpyAsync(c->d_segs, segs.data(), segs.size() * sizeof(AttnSeg), cudaMemcpyHostToDevice, st));
+  CU(cudaMemcpyAsync(c->d_cta_seg, cta_seg.data(), cta_seg.size() * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  CU(cudaStreamSynchronize(st));  // the host vectors go out of scope
+  c->T = (int)T;
+  c->n_segs = (int)segs.size();
+  c->n_parts = (int)segs.size();
+  c->n_ctas = n_ctas;
+  c->kv_rows = kv_rows;
+  c->planned = true;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_plan_tokens(FstMlaCtx* c, int32_t* t_out) {
+  if (!c || !t_out) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (!c->planned) return fail(FST_MLA_ERR_STATE, "no plan");
+  *t_out = c->T;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_plan_info(FstMlaCtx* c, int32_t* n_partials, int32_t* n_ctas, int64_t* kv_rows) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (!c->planned) return fail(FST_MLA_ERR_STATE, "no plan");
+  if (n_partials) *n_partials = c->n_parts;
+  if (n_ctas) *n_ctas = c->n_ctas;
+  if (kv_rows) *kv_rows = c->kv_rows;
+  return FST_MLA_OK;
+}
+
+/* ---- running -------------------------------------------------------------------------- */
+int fst_cuda_mla_run_device(FstMlaCtx* c, int lid, const void* d_h_in, void* d_h_out) {
+  int rc = check_run(c, lid);
+  if (rc) return rc;
+  if (!d_h_in || !d_h_out) return fail(FST_MLA_ERR_ARG, "null device pointer");
+  if (c->T == 0) return FST_MLA_OK;
+  CU(cudaSetDevice(c->cfg.device));
+  if ((rc = prof_begin(c))) return rc;
+  if ((rc = run_front(c, lid, (const bf16*)d_h_in))) return rc;
+  prof_mark(c, FST_MLA_K_ATTN);
+  if ((rc = run_attention(c, lid, c->d_qeff))) return rc;
+  prof_mark(c, FST_MLA_K_MERGE);
+  if ((rc = run_merge_local(c, lid, 0, nullptr))) return rc;
+  if ((rc = run_back(c, lid, (bf16*)d_h_out))) return rc;
+  c->cur = nullptr;
+  CU(cudaGetLastError());
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* h_out, const int32_t* seq_ids,
+                         const int32_t* pos0, const int32_t* q_lens, int32_t n_seqs, int32_t causal) {
+  if (!c || !h_in || !h_out || !seq_ids || !pos0 || !q_lens) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (n_seqs < 0) return fail(FST_MLA_ERR_ARG, "negative sequence count");
+  std::vector<FstMlaSeqStep> steps(n_seqs);
+  for (int b = 0; b < n_seqs; ++b) steps[b] = FstMlaSeqStep{seq_ids[b], pos0[b], q_lens[b], -1, 1};
+  int rc = fst_cuda_mla_plan(c, steps.data(), n_seqs, causal);
+  if (rc) return rc;
+  if ((rc = check_run(c, lid))) return rc;
+  if (c->T == 0) return FST_MLA_OK;
+  const size_t bytes = (size_t)c->T * c->d.hidden * sizeof(uint16_t);
+  memcpy(c->h_pinned, h_in, bytes);
+  CU(cudaMemcpyAsync(c->d_h, c->h_pinned, bytes, cudaMemcpyHostToDevice, c->stream));
+  if ((rc = fst_cuda_mla_run_device(c, lid, c->d_h, c->d_out))) return rc;
+  CU(cudaMemcpyAsync(c->h_pinned, c->d_out, bytes, cudaMemcpyDeviceToHost, c->stream));
+  if ((rc = fst_cuda_mla_sync(c))) return rc;
+  memcpy(h_out, c->h_pinned, bytes);
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_attention_only(FstMlaCtx* c, int lid, const uint16_t* q_eff, uint16_t* o_lat) {
+  int rc = check_run(c, lid);
+  if (rc) return rc;
+  if (!q_eff || !o_lat) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (c->T == 0) return FST_MLA_OK;
+  CU(cudaSetDevice(c->cfg.device));
+  const Dims& d = c->d;
+  CU(cudaMemcpyAsync(c->d_qeff, q_eff, (size_t)c->T * d.H * d.d_qk * 2, cudaMemcpyHostToDevice, c->stream));
+  if ((rc = prof_begin(c))) return rc;
+  prof_mark(c, FST_MLA_K_ATTN);
+  if ((rc = run_attention(c, lid, c->d_qeff))) return rc;
+  prof_mark(c, FST_MLA_K_MERGE);
+  if ((rc = run_merge_local(c, lid, 0, nullptr))) return rc;
+  prof_mark(c, FST_MLA_K_OPROJ_A);
+  c->cur = nullptr;
+  CU(cudaMemcpyAsync(o_lat, c->d_olat, (size_t)c->T * d.H * d.d_v * 2, cudaMemcpyDeviceToHost, c->stream));
+  return fst_cuda_mla_sync(c);
+}
+
+int fst_cuda_mla_run_partial_device(FstMlaCtx* c, int lid, const void* d_h_in, void* d_partial) {
+  int rc = check_run(c, lid);
+  if (rc) return rc;
+  if (!d_h_in || !d_partial) return fail(FST_MLA_ERR_ARG, "null device pointer");
+  if (c->T == 0) return FST_MLA_OK;
+  CU(cudaSetDevice(c->cfg.device));
+  if ((rc = prof_begin(c))) return rc;
+  if ((rc = run_front(c, lid, (const bf16*)d_h_in))) return rc;
+  prof_mark(c, FST_MLA_K_ATTN);
+  if ((rc = run_attention(c, lid, c->d_qeff))) return rc;
+  prof_mark(c, FST_MLA_K_MERGE);
+  if ((rc = run_merge_local(c, lid, 1, (float*)d_partial))) return rc;
+  prof_mark(c, FST_MLA_K_OPROJ_A);
+  c->cur = nullptr;
+  CU(cudaGetLastError());
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_run_merge_device(FstMlaCtx* c, int lid, const void* d_partials, int32_t n_parts, void* d_h_out) {
+  int rc = check_run(c, lid);
+  if (rc) return rc;
+  if (!d_partials || !d_h_out || n_parts <= 0) return fail(FST_MLA_ERR_ARG, "bad partial buffer");
+  if (c->T == 0) return FST_MLA_OK;
+  CU(cudaSetDevice(c->cfg.device));
+  const Dims& d = c->d;
+  if ((rc = prof_begin(c))) return rc;
+  prof_mark(c, FST_MLA_K_MERGE);
+  MergeGatheredArgs m;
+  m.parts = (const float*)d_partials; m.sinks = d.v4 ? c->layers[lid].sinks : nullptr; m.lut = c->d_lut;
+  m.o_lat = c->d_olat; m.n_parts = n_parts; m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope;
+  m.inv_rope = d.v4 ? 1 : 0;
+  launch_merge_gathered(m, c->stream);
+  c->launches += 1;
+  if ((rc = run_back(c, lid, (bf16*)d_h_out))) return rc;
+  c->cur = nullptr;
+  CU(cudaGetLastError());
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_get_stage(FstMlaCtx* c, int stage, uint16_t* host_out, size_t bytes) {
+  if (!c || !host_out) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (!c->planned) return fail(FST_MLA_ERR_STATE, "no plan");
+  const Dims& d = c->d;
+  const bf16* src = nullptr;
+  size_t n = 0;
+  switch (stage) {
+    case FST_MLA_STAGE_QC: src = c->d_qc; n = (size_t)c->T * d.q_lora; break;
+    case FST_MLA_STAGE_KV: src = c->d_kvnew; n = (size_t)c->T * d.row; break;
+    case FST_MLA_STAGE_QEFF: src = c->d_qeff; n = (size_t)c->T * d.H * d.d_qk; break;
+    case FST_MLA_STAGE_OLAT: src = c->d_olat; n = (size_t)c->T * d.H * d.d_v; break;
+    case FST_MLA_STAGE_LOW: src = c->d_low; n = (size_t)c->T * d.low; break;
+    case FST_MLA_STAGE_OUT: src = c->d_out; n = (size_t)c->T * d.hidden; break;
+    default: return fail(FST_MLA_ERR_ARG, "unknown stage %d", stage);
+  }
+  if (bytes != n * 2) return fail(FST_MLA_ERR_ARG, "stage %d holds %zu bytes, caller asked for %zu", stage, n * 2, bytes);
+  CU(cudaSetDevice(c->cfg.device));
+  CU(cudaStreamSynchronize(c->stream));
+  CU(cudaMemcpy(host_out, src, bytes, cudaMemcpyDeviceToHost));
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_gemm(FstMlaCtx* c, uint16_t* C, const uint16_t* A, const uint16_t* B, int M, int N, int K, int b_kn) {
+  if (!c || !C || !A || !B) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(FST_MLA_ERR_ARG, "non-positive GEMM size");
+  CU(cudaSetDevice(c->cfg.device));
+  bf16 *dA = nullptr, *dB = nullptr, *dC = nullptr;
+  int rc = dev_alloc(&dA, (size_t)M * K);
+  if (!rc) rc = dev_alloc(&dB, (size_t)N * K);
+  if (!rc) rc = dev_alloc(&dC, (size_t)M * N);
+  cudaError_t e = cudaSuccess;
+  if (!rc) {
+    e = cudaMemcpyAsync(dA, A, (size_t)M * K * 2, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dB, B, (size_t)N * K * 2, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) {
+      GemmArgs g = plain_gemm(dA, dB, dC, M, N, K);
+      if (b_kn) {
+        g.b_kn = 1;
+        g.ldb = N;
+      }
+      rc = run_gemm(c, g);
+    }
+    if (e == cudaSuccess && !rc) e = cudaMemcpyAsync(C, dC, (size_t)M * N * 2, cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess && !rc) rc = fst_cuda_mla_sync(c);
+  }
+  cudaStreamSynchronize(c->stream);
+  cudaFree(dA); cudaFree(dB); cudaFree(dC);
+  if (e != cudaSuccess) return fail(FST_MLA_ERR_CUDA, "GEMM copy failed: %s", cudaGetErrorString(e));
+  return rc;
+}
+
+/* ---- measurement ---------------------------------------------------------------------- */
+int fst_cuda_mla_launch_count(FstMlaCtx* c, int64_t* n_out) {
+  if (!c || !n_out) return fail(FST_MLA_ERR_ARG, "null argument");
+  *n_out = c->launches;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_set_profiling(FstMlaCtx* c, int on) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  c->profiling = on != 0;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_kernel_times(FstMlaCtx* c, float* ms_out, int32_t* n_out) {
+  if (!c || !ms_out || !n_out) return fail(FST_MLA_ERR_ARG, "null argument");
+  CU(cudaSetDevice(c->cfg.device));
+  int rc = prof_flush(c);
+  if (rc) return rc;
+  for (int k = 0; k < FST_MLA_K_COUNT; ++k) {
+    ms_out[k] = c->k_ms[k];
+    n_out[k] = c->k_n[k];
+    c->k_ms[k] = 0;
+    c->k_n[k] = 0;
+  }
+  return FST_MLA_OK;
+}
+
+}  // extern "C"

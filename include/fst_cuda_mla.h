@@ -1,0 +1,219 @@
+/* C ABI of the B200 (sm_100a) Multi-head Latent Attention path of the FaStar engine.
+ *
+ * This is the boundary FSTEngine::process_mla (reference src/fst_engine.cpp:3320-3890,
+ * declared include/fst_engine.h:309) crosses instead of the NPU dispatch helpers
+ * (npu_gemm_mla_vec 465-575, npu_rmsnorm_weighted 882-934, npu_rope 815-856) and the XRT
+ * buffer objects bo_mla_* / KVCacheEntry (include/fst_engine.h:108-113, 533-557).
+ *
+ * Plain C: pointers and sizes only.  Every function returns FST_MLA_OK (0) or a negative
+ * FST_MLA_ERR_* code and never throws; fst_cuda_mla_last_error() describes the last
+ * failure of the calling thread.  The engine's wrapper turns a non-zero code into the
+ * std::runtime_error the reference raises (src/fst_engine.cpp:200-223).
+ *
+ * Threading: one context per GPU, calls serialised by the caller (the reference is single
+ * threaded, src/fst_main.cpp:461,506).  All work of a context runs on one CUDA stream.
+ *
+ * bf16 values cross the boundary as uint16_t bit patterns (bf16_t of include/fst_engine.h:16).
+ * Weight matrices are [N_out, K_in] row-major, consumed as C = A * B^T, exactly as the
+ * reference holds them (src/fst_engine.cpp:1611-1615).
+ */
+#ifndef FST_CUDA_MLA_H
+#define FST_CUDA_MLA_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FST_MLA_OK 0
+#define FST_MLA_ERR_ARG (-1)          /* bad argument */
+#define FST_MLA_ERR_PAGES (-2)        /* the page pool is exhausted */
+#define FST_MLA_ERR_CAPACITY (-3)     /* too many sequences / tokens for this context */
+#define FST_MLA_ERR_CUDA (-4)         /* a CUDA call failed */
+#define FST_MLA_ERR_DEVICE_CHECK (-5) /* a kernel gave up a bounded wait or failed a check */
+#define FST_MLA_ERR_STATE (-6)        /* call order: no weights, no plan */
+#define FST_MLA_ERR_NO_DEVICE (-7)    /* no CUDA device: there is no CPU fallback */
+
+#define FST_MLA_PRESET_BASELINE 0  /* 576-wide rows [512 latent | 64 k_pe], W_UK absorb, per-head W_UV */
+#define FST_MLA_PRESET_FASTAR_V4 1 /* live engine: 512-wide rows, RoPE tail, sink, grouped wo_a */
+
+/* Kernel selection (for bisecting; AUTO is what the engine uses). */
+#define FST_MLA_IMPL_AUTO 0
+#define FST_MLA_IMPL_TENSOR 1 /* tcgen05 / TMEM / TMA kernels */
+#define FST_MLA_IMPL_SIMT 2   /* CUDA-core kernels (any shape) */
+
+typedef struct FstMlaCtx FstMlaCtx;
+
+/* Shape constants mirror include/fst_engine.h:92-95 (MLA_Q_LORA, MLA_KV_LORA, MLA_N_HEADS,
+ * MLA_HEAD_DIM, MLA_ROPE_DIM) and ModelConfig (127-139). */
+typedef struct FstMlaConfig {
+  int32_t preset;
+  int32_t hidden;    /* 4096 */
+  int32_t n_heads;   /* 64 */
+  int32_t q_lora;    /* 1024 */
+  int32_t kv_lora;   /* 512 */
+  int32_t qk_nope;   /* BASELINE 128 (V4: ignored, kv_lora - qk_rope) */
+  int32_t qk_rope;   /* 64 */
+  int32_t v_head;    /* BASELINE 128 */
+  int32_t o_groups;  /* V4: 8 */
+  int32_t o_lora;    /* V4: 1024 */
+  float softmax_scale; /* <= 0: preset default (1/sqrt(nope+rope) or 1/sqrt(kv_lora)) */
+  float rope_theta;    /* 10000 */
+  float rms_eps;       /* 1e-6 */
+  int32_t rope_yarn;   /* V4 compressed layers: YaRN tables (src/fst_engine.cpp:1995-2022) */
+  int32_t n_layers;
+  int32_t page_tokens; /* 64 */
+  int32_t n_pages;     /* pages per layer in the pool */
+  int32_t max_seqs;
+  int32_t max_tokens;  /* most new tokens (sum of q_len) in one call */
+  int32_t device;      /* CUDA ordinal */
+  int32_t attn_impl;   /* FST_MLA_IMPL_* */
+  int32_t gemm_impl;   /* FST_MLA_IMPL_* */
+} FstMlaConfig;
+
+/* Host pointers, copied to the device once (replaces preload_all_layers,
+ * src/fst_engine.cpp:1152-1197).  Members a preset does not use may be NULL.
+ * BASELINE: wq_a[q_lora,hidden] wq_b[H*(nope+rope),q_lora] wkv_a[kv_lora+rope,hidden]
+ *           wkv_b[H*(nope+v_head),kv_lora] (per head: W_UK rows then W_UV rows)
+ *           wo_b[hidden,H*v_head] q_norm[q_lora] kv_norm[kv_lora]
+ * V4 (LayerWeightsC, include/fst_engine.h:165-188): wq_a wq_b[H*512,q_lora] wkv_a = wkv[512,hidden]
+ *           wo_a[o_groups*o_lora, H*512/o_groups] wo_b[hidden,o_groups*o_lora]
+ *           q_norm kv_norm attn_sinks[H] (NULL: sink logit 0, src/fst_engine.cpp:3623) */
+typedef struct FstMlaWeights {
+  const uint16_t* wq_a;
+  const uint16_t* wq_b;
+  const uint16_t* wkv_a;
+  const uint16_t* wkv_b;
+  const uint16_t* wo_a;
+  const uint16_t* wo_b;
+  const uint16_t* q_norm;
+  const uint16_t* kv_norm;
+  const float* attn_sinks;
+} FstMlaWeights;
+
+/* One sequence's share of a layer call.  The reference passes this implicitly as
+ * seq_pos_ / M / is_prefill_ (src/fst_engine.cpp:3327, 3345, 3626). */
+typedef struct FstMlaSeqStep {
+  int32_t seq;       /* id from fst_cuda_mla_seq_alloc */
+  int32_t pos0;      /* cache row of the first new token (seq_pos_) */
+  int32_t q_len;     /* new tokens (M) */
+  int32_t rope_pos0; /* RoPE position of the first new token; < 0: same as pos0 */
+  int32_t append;    /* 1: write the new rows and attend to [0, pos0+q_len);
+                        0: attend to [0, pos0) only (a KV slice that does not own them) */
+} FstMlaSeqStep;
+
+/* Intermediate buffers of the last run, the stage list of FST_MLA_TRACE
+ * (src/fst_engine.cpp:3396-3407, 3521-3532, 3685-3695, 3841-3851). */
+#define FST_MLA_STAGE_QC 0    /* [T, q_lora]      after wq_a + q_norm */
+#define FST_MLA_STAGE_KV 1    /* [T, row]         new cache rows (normed latent, rotated k_pe) */
+#define FST_MLA_STAGE_QEFF 2  /* [T*H, d_qk]      query in latent space, RoPE applied */
+#define FST_MLA_STAGE_OLAT 3  /* [T*H, d_v]       attention output (V4: after inverse RoPE) */
+#define FST_MLA_STAGE_LOW 4   /* [T, 8192]        after O-proj a */
+#define FST_MLA_STAGE_OUT 5   /* [T, hidden]      after O-proj b */
+
+/* Kernels whose device time fst_cuda_mla_kernel_times reports, in launch order. */
+#define FST_MLA_K_COMPRESS 0 /* h * [wq_a; wkv_a]^T */
+#define FST_MLA_K_NORM_APPEND 1
+#define FST_MLA_K_Q_EXPAND 2
+#define FST_MLA_K_Q_ABSORB 3 /* RoPE(q_pe) + W_UK absorb (V4: head RMSNorm + RoPE) */
+#define FST_MLA_K_ATTN 4     /* split-KV QK / online softmax / SV over the paged cache */
+#define FST_MLA_K_MERGE 5    /* log-sum-exp merge of the split partials */
+#define FST_MLA_K_OPROJ_A 6
+#define FST_MLA_K_OPROJ_B 7
+#define FST_MLA_K_COUNT 8
+
+/* ---- lifetime ------------------------------------------------------------------------- */
+/* Replaces device probe + buffer allocation of FSTEngine::FSTEngine (src/fst_engine.cpp:
+ * 1250-1270, 1419-1474).  Fails with FST_MLA_ERR_NO_DEVICE when there is no GPU. */
+int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out);
+void fst_cuda_mla_destroy(FstMlaCtx* ctx);
+const char* fst_cuda_mla_last_error(void);
+/* Stream all later work is enqueued on (a cudaStream_t; NULL = the default stream). */
+int fst_cuda_mla_set_stream(FstMlaCtx* ctx, void* cuda_stream);
+/* Blocks until the stream is idle; reports a pending device-side check (npu_run_wait /
+ * flush_pending_runs, src/fst_engine.cpp:200-223). */
+int fst_cuda_mla_sync(FstMlaCtx* ctx);
+
+/* ---- weights -------------------------------------------------------------------------- */
+int fst_cuda_mla_set_layer_weights(FstMlaCtx* ctx, int lid, const FstMlaWeights* w);
+
+/* ---- paged latent cache --------------------------------------------------------------- */
+/* The reference cache is one flat [max_seq, 512] bf16 buffer per layer indexed by seq_pos_
+ * (include/fst_engine.h:108-113; alloc src/fst_engine.cpp:1469-1474).  Here token t of a
+ * sequence lives in page table[t / page_tokens], slot t % page_tokens, of every layer's
+ * pool; pages come from a LIFO free list that initially hands out 0, 1, 2, ... */
+int fst_cuda_mla_seq_alloc(FstMlaCtx* ctx, int32_t* seq_out);
+int fst_cuda_mla_seq_free(FstMlaCtx* ctx, int32_t seq);
+/* Grow the table to hold n_tokens (no-op if it already does). */
+int fst_cuda_mla_seq_reserve(FstMlaCtx* ctx, int32_t seq, int32_t n_tokens);
+/* Speculative-decoding rollback (src/fst_engine.cpp:6132-6147): drop rows >= n_tokens,
+ * zero them in every layer as the reference does, return whole pages to the pool. */
+int fst_cuda_mla_seq_truncate(FstMlaCtx* ctx, int32_t seq, int32_t n_tokens);
+int fst_cuda_mla_seq_len(FstMlaCtx* ctx, int32_t seq, int32_t* len_out);
+/* reset_session (src/fst_engine.cpp:2992-3012): free every sequence, zero the pools. */
+int fst_cuda_mla_reset(FstMlaCtx* ctx);
+int fst_cuda_mla_block_table(FstMlaCtx* ctx, int32_t seq, int32_t* out, int32_t cap, int32_t* n_out);
+int fst_cuda_mla_free_pages(FstMlaCtx* ctx, int32_t* n_out);
+/* Element offset of row `pos` of `seq` inside a layer's pool (page * page_tokens + slot) * row. */
+int fst_cuda_mla_row_offset(FstMlaCtx* ctx, int32_t seq, int32_t pos, int64_t* off_out);
+/* Copy n rows [n, row] starting at row pos0 from / to host memory (reserves pages on write). */
+int fst_cuda_mla_cache_write(FstMlaCtx* ctx, int lid, int32_t seq, int32_t pos0, int32_t n,
+                             const uint16_t* rows);
+int fst_cuda_mla_cache_read(FstMlaCtx* ctx, int lid, int32_t seq, int32_t pos0, int32_t n,
+                            uint16_t* rows);
+/* Raw pool of a layer [n_pages * page_tokens, row] to host. */
+int fst_cuda_mla_pool_read(FstMlaCtx* ctx, int lid, uint16_t* out, size_t bytes);
+
+/* ---- the layer ------------------------------------------------------------------------ */
+/* Host-side preparation of one call shape: reserves pages, builds block tables, RoPE tables
+ * and the split-KV schedule, and uploads them.  A plan stays valid for every layer of the
+ * same step (process_layer calls process_mla once per layer with the same seq_pos_). */
+int fst_cuda_mla_plan(FstMlaCtx* ctx, const FstMlaSeqStep* steps, int32_t n_seqs, int32_t causal);
+/* Enqueue the layer for the current plan; h_in / h_out are device bf16 [T, hidden]
+ * (may alias).  No host synchronisation. */
+int fst_cuda_mla_run_device(FstMlaCtx* ctx, int lid, const void* d_h_in, void* d_h_out);
+/* process_mla with host buffers, as the engine calls it: plan + H2D + run + D2H + sync.
+ * h_in / h_out are host bf16 [sum q_lens, hidden] (may alias: the reference works in place,
+ * src/fst_engine.cpp:3889).  Rows are written at pos0[b] .. pos0[b]+q_lens[b]-1. */
+int fst_cuda_mla_forward(FstMlaCtx* ctx, int lid, const uint16_t* h_in, uint16_t* h_out,
+                         const int32_t* seq_ids, const int32_t* pos0, const int32_t* q_lens,
+                         int32_t n_seqs, int32_t causal);
+/* QK / softmax / SV alone on caller-supplied queries (the qksv dispatches,
+ * src/fst_engine.cpp:3588, 3682): host q_eff [T*H, d_qk] -> host o_lat [T*H, d_v], over the
+ * cache as it stands, for the current plan (nothing is appended). */
+int fst_cuda_mla_attention_only(FstMlaCtx* ctx, int lid, const uint16_t* q_eff, uint16_t* o_lat);
+/* Split-KV across GPUs: run the layer up to the merged per-GPU partial.  d_partial is device
+ * fp32 [T*H, 2 + d_v] holding (max, sum, un-normalised O) per query row. */
+int fst_cuda_mla_run_partial_device(FstMlaCtx* ctx, int lid, const void* d_h_in, void* d_partial);
+/* Merge n_parts gathered partials [n_parts][T*H, 2 + d_v] by log-sum-exp, then run the
+ * output projections into d_h_out. */
+int fst_cuda_mla_run_merge_device(FstMlaCtx* ctx, int lid, const void* d_partials, int32_t n_parts,
+                                  void* d_h_out);
+/* Number of new tokens T of the current plan. */
+int fst_cuda_mla_plan_tokens(FstMlaCtx* ctx, int32_t* t_out);
+int fst_cuda_mla_get_stage(FstMlaCtx* ctx, int stage, uint16_t* host_out, size_t bytes);
+
+/* ---- GEMM tile engine alone ----------------------------------------------------------- */
+/* npu_gemm_mla_vec (src/fst_engine.cpp:465-575): C[M,N] = A[M,K] * B[N,K]^T (b_kn = 0, the
+ * b_col_maj kernels) or A[M,K] * B[K,N] (b_kn = 1, the b_row_maj qksv kernel); host bf16
+ * buffers, fp32 accumulation.  The random-matrix probe of randmat_test (586-685) runs
+ * through this. */
+int fst_cuda_mla_gemm(FstMlaCtx* ctx, uint16_t* C, const uint16_t* A, const uint16_t* B, int M,
+                      int N, int K, int b_kn);
+
+/* ---- measurement ---------------------------------------------------------------------- */
+/* Kernels launched by this context so far. */
+int fst_cuda_mla_launch_count(FstMlaCtx* ctx, int64_t* n_out);
+/* on != 0: bracket every kernel of a run with CUDA events on the context's stream. */
+int fst_cuda_mla_set_profiling(FstMlaCtx* ctx, int on);
+/* Synchronises, then returns the summed device time (ms) and launch count per
+ * FST_MLA_K_* since the last call; ms_out / n_out have FST_MLA_K_COUNT entries. */
+int fst_cuda_mla_kernel_times(FstMlaCtx* ctx, float* ms_out, int32_t* n_out);
+/* Schedule of the current plan: partial count, CTAs of the attention kernel, cached rows read. */
+int fst_cuda_mla_plan_info(FstMlaCtx* ctx, int32_t* n_partials, int32_t* n_ctas, int64_t* kv_rows);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,96 @@
+"""CPU-side checks: the C-ABI library loads and exports every symbol its header declares, and
+refuses to run without a GPU (no CPU fallback); host-side sharding logic."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from fastar_b200 import mla, parallel, synth
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = []
+    for fn in sorted(os.listdir(os.path.join(ROOT, "include"))):
+        text = open(os.path.join(ROOT, "include", fn)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names += re.findall(r"\b(fst_cuda_\w+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(mla.LIB_PATH)
+    names = declared_symbols()
+    assert len(names) >= 30
+    for n in names:
+        assert hasattr(lib, n), n
+
+
+def test_no_gpu_means_no_context():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(mla.MlaError) as e:
+        mla.MlaContext(mla.make_config())
+    assert e.value.code == mla.ERR_NO_DEVICE
+    assert "no CPU fallback" in str(e.value)
+
+
+def test_bad_config_is_rejected():
+    lib = mla.load_library()
+    h = ctypes.c_void_p()
+    for kw in ({"n_pages": 0}, {"qk_rope": 63}, {"n_layers": 0}, {"preset": 5}):
+        cfg = mla.make_config(**kw)
+        assert lib.fst_cuda_mla_create(ctypes.byref(cfg), ctypes.byref(h)) == mla.ERR_ARG
+        assert not h.value
+    assert lib.fst_cuda_mla_create(None, ctypes.byref(h)) == mla.ERR_ARG
+    assert lib.fst_cuda_mla_sync(None) == mla.ERR_ARG
+    assert b"null" in lib.fst_cuda_mla_last_error()
+
+
+def test_bf16_helpers_round_to_nearest_even():
+    from oracle import oracle as O
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(1000).astype(np.float32),
+                        np.array([1.00390625, 1.01171875, -1.00390625, 0.0, 65504.0], np.float32)])
+    assert np.array_equal(synth.to_bf16_bits(x), O.to_bf16_bits(x))
+    assert np.array_equal(synth.from_bf16_bits(synth.to_bf16_bits(x)), O.bf16_round(x))
+    # ties go to the even mantissa
+    assert synth.to_bf16_bits(np.array([1.00390625], np.float32))[0] == 0x3F80
+    assert synth.to_bf16_bits(np.array([1.01171875], np.float32))[0] == 0x3F82
+
+
+def test_synthetic_inputs_do_not_depend_on_sharding():
+    cfg = mla.make_config()
+    a = synth.cache_rows_f32(cfg, 0, 5, 100)
+    b = synth.cache_rows_f32(cfg, 0, 5, 100)
+    c = synth.cache_rows_f32(cfg, 0, 6, 100)
+    assert np.array_equal(a, b) and not np.array_equal(a, c)
+    assert abs(float(a.std()) - 1.0) < 0.02
+    w = synth.normal_f32(0, "wq_a", (256, 256), 0.02, (0,))
+    assert abs(float(w.std()) - 0.02) < 0.001
+
+
+def test_shard_sequences_balances_rows():
+    lens = synth.context_lengths(0, 64, 1024, 8192)
+    assert lens.min() >= 1024 and lens.max() <= 8192
+    for world in (1, 2, 4, 8):
+        sh = parallel.shard_sequences(lens, world)
+        assert sorted(i for s in sh for i in s) == list(range(64))
+        loads = [int(sum(lens[i] for i in s)) for s in sh]
+        assert max(loads) - min(loads) <= 8192
+
+
+def test_kv_slices_are_page_aligned_and_cover():
+    for n, world in ((131072, 8), (131072, 2), (1000, 4), (64, 8), (1, 2), (0, 4)):
+        sl = parallel.kv_slices(n, world)
+        assert sl[0][0] == 0 and sl[-1][1] == n
+        for (a, b), (c, d) in zip(sl, sl[1:]):
+            assert b == c and a <= b
+        for a, b in sl[:-1]:
+            assert a % 64 == 0 and b % 64 == 0
+    assert parallel.owner_of_row(131072, 131072, 8) == 7
+    assert parallel.owner_of_row(0, 131072, 8) == 0

@@ -1,0 +1,107 @@
+"""The whole MLA layer through fst_cuda_mla_forward (process_mla with host buffers) against
+the CPU oracle on identical seeded inputs: stage by stage (the FST_MLA_TRACE stage list,
+src/fst_engine.cpp:3396-3407, 3521-3532, 3685-3695, 3841-3851) and end to end."""
+import numpy as np
+import pytest
+
+from fastar_b200 import mla, synth
+from oracle import oracle as O
+from tests.helpers import check_close, oracle_cfg
+
+pytestmark = pytest.mark.gpu
+
+IMPLS = [("simt", mla.IMPL_SIMT, mla.IMPL_SIMT), ("tensor", mla.IMPL_TENSOR, mla.IMPL_AUTO)]
+_W = {}
+
+
+def weights_for(preset):
+    """Seed-0 weights of the preset at full size, as bits (GPU) and rounded fp32 (oracle)."""
+    if preset not in _W:
+        cfg = mla.make_config(preset)
+        w = synth.layer_weights_f32(cfg, 0, 0)
+        _W[preset] = (synth.weights_to_bits(w), synth.weights_rounded(w))
+    return _W[preset]
+
+
+def run_layer(preset, impl, lens, q_len, causal, seed=0, steps=1):
+    """`steps` consecutive layer calls (each appends q_len tokens per sequence); every call is
+    compared with the oracle, and so is the cache content afterwards."""
+    attn_impl, gemm_impl = impl[1], impl[2]
+    B = len(lens)
+    n_pages = sum((L + q_len * steps + 63) // 64 for L in lens) + 4
+    cfg = mla.make_config(preset, n_pages=n_pages, max_tokens=B * q_len, max_seqs=B, attn_impl=attn_impl,
+                          gemm_impl=gemm_impl)
+    bits, rounded = weights_for(preset)
+    ocfg = oracle_cfg(cfg)
+    d = mla.dims_of(cfg)
+    H = cfg.n_heads
+    with mla.MlaContext(cfg) as ctx:
+        ctx.set_layer_weights(0, bits)
+        seqs, caches = [], []
+        for b, L in enumerate(lens):
+            s = ctx.seq_alloc()
+            rows = synth.to_bf16_bits(synth.cache_rows_f32(cfg, seed, b, L))
+            if L:
+                ctx.cache_write(0, s, 0, rows)
+            seqs.append(s)
+            cache = np.zeros((L + q_len * steps, d["row"]), np.float32)
+            cache[:L] = synth.from_bf16_bits(rows)
+            caches.append(cache)
+        pos = list(lens)
+        for step in range(steps):
+            h = synth.to_bf16_bits(synth.hidden_f32(cfg, seed, B * q_len, (step,)))
+            out = ctx.forward(0, h, seqs, pos, [q_len] * B, causal=causal)
+            stages = {k: ctx.get_stage(v) for k, v in (("qc", mla.STAGE_QC), ("kv", mla.STAGE_KV),
+                                                      ("q_eff", mla.STAGE_QEFF), ("o_lat", mla.STAGE_OLAT),
+                                                      ("low", mla.STAGE_LOW))}
+            hf = synth.from_bf16_bits(h)
+            for b in range(B):
+                r = O.mla_forward(ocfg, rounded, hf[b * q_len:(b + 1) * q_len], pos[b], caches[b], causal=causal)
+                sl = slice(b * q_len, (b + 1) * q_len)
+                slh = slice(b * q_len * H, (b + 1) * q_len * H)
+                check_close(stages["qc"][sl], r.trace["qc"], f"step {step} seq {b} qc", max_abs=6e-2)
+                check_close(stages["kv"][sl], r.trace["kv"], f"step {step} seq {b} kv", max_abs=6e-2)
+                check_close(stages["q_eff"][slh], r.trace["q_eff"], f"step {step} seq {b} q_eff", max_abs=6e-2)
+                check_close(stages["o_lat"][slh], r.trace["o_lat"], f"step {step} seq {b} o_lat")
+                check_close(stages["low"][sl], r.trace["low"], f"step {step} seq {b} low")
+                check_close(out[sl], r.out, f"step {step} seq {b} out")
+                # cache push: the appended rows are the kv stage rows, bit for bit, at the rows
+                # the block table names
+                got_rows = ctx.cache_read(0, seqs[b], pos[b], q_len)
+                assert np.array_equal(got_rows, stages["kv"][sl])
+                pos[b] += q_len
+        # the history itself is untouched
+        for b, L in enumerate(lens):
+            if L:
+                assert np.array_equal(ctx.cache_read(0, seqs[b], 0, L),
+                                      synth.to_bf16_bits(caches[b][:L]))
+
+
+@pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
+def test_decode_batch1_config1(impl):
+    # "decode at batch 1 over a 4096-token cache"
+    run_layer(mla.PRESET_BASELINE, impl, [4096], 1, False)
+
+
+@pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
+def test_decode_ragged_batch(impl):
+    # batched decode, ragged context lengths, two consecutive steps
+    run_layer(mla.PRESET_BASELINE, impl, [1030, 64, 1, 700, 0, 129, 2047, 333], 1, False, seed=1, steps=2)
+
+
+@pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
+def test_verify_block_causal(impl):
+    # 16 query tokens per sequence, causal among themselves, appended at L .. L+15
+    run_layer(mla.PRESET_BASELINE, impl, [200, 64], 16, True, seed=2)
+
+
+@pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
+def test_prefill_from_empty(impl):
+    # the reference's own regime: 16-token chunks from position 0 (prefill_tiled, 2957-2984)
+    run_layer(mla.PRESET_BASELINE, impl, [0], 16, True, seed=3, steps=2)
+
+
+@pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
+def test_fastar_v4_preset(impl):
+    # the live engine's form: 512-wide rows, per-head q norm, sink, inverse RoPE, grouped wo_a
+    run_layer(mla.PRESET_FASTAR_V4, impl, [100, 0, 129], 2, True, seed=4, steps=2)
