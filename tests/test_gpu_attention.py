@@ -29,7 +29,7 @@ def dummy_weights(cfg, sinks=None):
     return w
 
 
-def run_case(preset, impl, lens, q_len=1, causal=False, seed=0, q_std=1.0, shuffle_pages=True):
+def run_case(preset, impl, lens, q_len=1, causal=False, seed=0, q_std=1.0, shuffle_pages=True, ulps=0):
     n_pages = sum((L + q_len + 63) // 64 for L in lens) + 8
     B = len(lens)
     cfg, ctx = setup_ctx(preset, impl, n_pages, B * q_len, max_seqs=B + 8)
@@ -63,7 +63,11 @@ def run_case(preset, impl, lens, q_len=1, causal=False, seed=0, q_std=1.0, shuff
             kv_len = L + q_len if causal else L
             want = O.attention(ocfg, qf[b * q_len * H:(b + 1) * q_len * H], caches[b], kv_len, q_len, pos0=L,
                                causal=causal, sinks=sinks)
-            check_close(got[b * q_len * H:(b + 1) * q_len * H], want, f"seq {b} (L={L})")
+            if preset == mla.PRESET_FASTAR_V4:
+                # the V4 output stage carries the inverse RoPE of the tail (src/fst_engine.cpp:3716)
+                for r in range(q_len * H):
+                    want[r, -64:] = O.rope_apply(want[r, -64:], L + r // H, inverse=True, round_bf16=True)
+            check_close(got[b * q_len * H:(b + 1) * q_len * H], want, f"seq {b} (L={L})", ulps=ulps)
     finally:
         ctx.close()
 
@@ -72,7 +76,7 @@ def run_case(preset, impl, lens, q_len=1, causal=False, seed=0, q_std=1.0, shuff
 @pytest.mark.parametrize("preset", PRESETS, ids=[p[0] for p in PRESETS])
 def test_decode_ragged_lengths(preset, impl):
     # one token, one page, page boundary -1/0/+1, tile boundary -1/0/+1, several tiles
-    run_case(preset[1], impl[1], [1, 2, 63, 64, 65, 127, 128, 129, 191, 200, 257, 700])
+    run_case(preset[1], impl[1], [1, 2, 63, 64, 65, 127, 128, 129, 191, 200, 257, 700], ulps=1)
 
 
 @pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
@@ -84,7 +88,8 @@ def test_decode_config1_shape(impl):
 @pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
 def test_decode_sharp_softmax(impl):
     # large query norm: scores spread over hundreds of units, the running maximum moves often
-    run_case(mla.PRESET_BASELINE, impl[1], [300, 1000, 129], seed=2, q_std=6.0)
+    # (outputs reach several units here: the bound is one bf16 step at that magnitude)
+    run_case(mla.PRESET_BASELINE, impl[1], [300, 1000, 129], seed=2, q_std=6.0, ulps=1)
 
 
 @pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
@@ -92,7 +97,7 @@ def test_decode_sharp_softmax(impl):
 def test_causal_verify_block(preset, impl):
     # 16 query tokens, causal among themselves (the speculative-verify block, 6005-6014):
     # token i sees rows <= pos0 + i (mask at 3626)
-    run_case(preset[1], impl[1], [100, 128, 250], q_len=16, causal=True, seed=3)
+    run_case(preset[1], impl[1], [100, 128, 250], q_len=16, causal=True, seed=3, ulps=1)
 
 
 def test_empty_batch_and_zero_context():

@@ -23,7 +23,7 @@ def weights_for(preset):
     return _W[preset]
 
 
-def run_layer(preset, impl, lens, q_len, causal, seed=0, steps=1):
+def run_layer(preset, impl, lens, q_len, causal, seed=0, steps=1, ulps=0):
     """`steps` consecutive layer calls (each appends q_len tokens per sequence); every call is
     compared with the oracle, and so is the cache content afterwards."""
     attn_impl, gemm_impl = impl[1], impl[2]
@@ -59,12 +59,13 @@ def run_layer(preset, impl, lens, q_len, causal, seed=0, steps=1):
                 r = O.mla_forward(ocfg, rounded, hf[b * q_len:(b + 1) * q_len], pos[b], caches[b], causal=causal)
                 sl = slice(b * q_len, (b + 1) * q_len)
                 slh = slice(b * q_len * H, (b + 1) * q_len * H)
-                check_close(stages["qc"][sl], r.trace["qc"], f"step {step} seq {b} qc", max_abs=6e-2)
-                check_close(stages["kv"][sl], r.trace["kv"], f"step {step} seq {b} kv", max_abs=6e-2)
-                check_close(stages["q_eff"][slh], r.trace["q_eff"], f"step {step} seq {b} q_eff", max_abs=6e-2)
-                check_close(stages["o_lat"][slh], r.trace["o_lat"], f"step {step} seq {b} o_lat")
-                check_close(stages["low"][sl], r.trace["low"], f"step {step} seq {b} low")
-                check_close(out[sl], r.out, f"step {step} seq {b} out")
+                # normed intermediates are O(1..8): one or two bf16 steps there exceed 2e-2
+                check_close(stages["qc"][sl], r.trace["qc"], f"step {step} seq {b} qc", ulps=2)
+                check_close(stages["kv"][sl], r.trace["kv"], f"step {step} seq {b} kv", ulps=2)
+                check_close(stages["q_eff"][slh], r.trace["q_eff"], f"step {step} seq {b} q_eff", ulps=2)
+                check_close(stages["o_lat"][slh], r.trace["o_lat"], f"step {step} seq {b} o_lat", ulps=ulps)
+                check_close(stages["low"][sl], r.trace["low"], f"step {step} seq {b} low", ulps=ulps)
+                check_close(out[sl], r.out, f"step {step} seq {b} out", ulps=ulps)
                 # cache push: the appended rows are the kv stage rows, bit for bit, at the rows
                 # the block table names
                 got_rows = ctx.cache_read(0, seqs[b], pos[b], q_len)
@@ -104,4 +105,5 @@ def test_prefill_from_empty(impl):
 @pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
 def test_fastar_v4_preset(impl):
     # the live engine's form: 512-wide rows, per-head q norm, sink, inverse RoPE, grouped wo_a
-    run_layer(mla.PRESET_FASTAR_V4, impl, [100, 0, 129], 2, True, seed=4, steps=2)
+    # (its outputs reach several units: the absolute bound is two bf16 steps at that magnitude)
+    run_layer(mla.PRESET_FASTAR_V4, impl, [100, 0, 129], 2, True, seed=4, steps=2, ulps=2)
