@@ -2,12 +2,13 @@
 // process_mla (reference src/fst_engine.cpp:3573-3683) fused with an online softmax over the
 // paged bf16 cache, for 64 heads sharing every cached row.
 //
-// Orientation.  With one query token the natural M dimension (64 heads) would leave half of a
-// 128-row tcgen05.mma idle, so both products are transposed and the CACHED TOKENS are M:
-//   S^T[128 tok, 64 heads] = K[128 tok, d_qk] * Q^T          (A = cache tile, K-major;
-//                                                             B = Q_eff, K-major)
-//   O^T[512, 64 heads]    += V^T[512, 128 tok] * P^T          (A = the same cache bytes read
-//                                                             MN-major; B = P, MN-major)
+// Orientation.  The score product is transposed so that the CACHED TOKENS are the MMA M
+// dimension (a 128-row tcgen05.mma even with one query token), the value product is not, so
+// that its N dimension is 256 latent columns wide:
+//   S^T[128 tok, 64 heads] = K[128 tok, d_qk] * Q^T    (A = cache tile, K-major; B = Q_eff, K-major)
+//   O[64 heads, 512]      += P[64 heads, 128 tok] * V  (A = P^T as written by the softmax threads,
+//                                                       read MN-major; B = the same cache bytes,
+//                                                       read MN-major, two halves of 256 columns)
 // A cached row is fetched from HBM once and serves as key and as value.
 //
 // One persistent CTA per SM walks its run of schedule segments.  Shared memory holds Q_eff
@@ -17,9 +18,12 @@
 // QK MMAs of the next tile start on the chunks that have landed.  With 576-wide rows the
 // rope chunk is dead after QK, so P^T is written over it.
 //
-// Warp roles: warp 0 lane 0 issues TMA; warp 1 lane 0 issues tcgen05.mma (warp 1 owns the TMEM
-// allocation); warps 2-5 are the softmax / epilogue threads, one cached token (TMEM lane) each.
-// TMEM: S^T in columns [0, 64), O^T in 4 x 64 columns from 64.
+// Warp roles: warp 0 lane 0 issues TMA (and prefetches the next tile into L2, so that the
+// refill of a freed chunk is an L2 hit); warp 1 lane 0 issues tcgen05.mma (warp 1 owns the TMEM
+// allocation); warps 2-9 are the softmax / epilogue threads: two per cached token (TMEM lane),
+// 32 heads each.  TMEM: S^T in columns [0, 64).  O is two 64-row accumulators [64, 256] in
+// columns [64, 320): a 64-row accumulator occupies lanes 0-15 of each 32-lane quadrant (head h
+// in lane 32*(h/16) + h%16), so the second one sits at lane offset 16 in the same columns.
 #include "kernels.cuh"
 #include "tc_common.cuh"
 
@@ -32,7 +36,8 @@ constexpr int HEADS = 64;
 constexpr int D_V = 512;
 constexpr int Q_CHUNK = HEADS * 128;   // bytes of one [64 x 64] bf16 chunk of Q
 constexpr int KV_CHUNK = TILE * 128;   // bytes of one [128 x 64] bf16 chunk of the tile
-constexpr int ATTN_THREADS = 192;
+constexpr int ATTN_THREADS = 320;
+constexpr int SOFTMAX_THREADS = 256;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_O = 64;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units: O is rescaled only when the max grows by > 2^8
@@ -49,6 +54,14 @@ struct AttnTcParams {
   int pool_rows;   // first row index outside the pool: TMA fills zeros there
   float scale_log2;
 };
+
+#ifdef FST_ATTN_TRACE
+// Phase timestamps (SM clock) of CTA 0, for tuning builds only: [tile][event].
+__device__ long long g_attn_trace[64 * 16];
+#define TRACE(tile, ev) do { if (blockIdx.x == 0 && (tile) < 64) g_attn_trace[(tile) * 16 + (ev)] = clock64(); } while (0)
+#else
+#define TRACE(tile, ev) do { } while (0)
+#endif
 
 template <int NCH>
 struct Smem {
@@ -82,15 +95,20 @@ __device__ __forceinline__ float redux_max(float v) {
   asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
   return r;
 }
-__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-// Barrier of the 128 softmax threads that also ANDs a flag, so that a wait given up by one
+__device__ __forceinline__ float ex2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// Barrier of the 256 softmax threads that also ANDs a flag, so that a wait given up by one
 // warp ends the loop of all four and nobody is left waiting at a later barrier.
 __device__ __forceinline__ bool softmax_bar_and(bool v) {
   uint32_t out;
   asm volatile(
       "{\n\t.reg .pred q, r;\n\t"
       "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.and.pred r, 1, 128, q;\n\t"
+      "bar.red.and.pred r, 1, 256, q;\n\t"
       "selp.u32 %0, 1, 0, r;\n\t}"
       : "=r"(out)
       : "r"((uint32_t)v)
@@ -120,7 +138,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       tc::mbar_init(&mi->kv_empty[c], 1);
     }
     tc::mbar_init(&mi->s_full, 1);
-    tc::mbar_init(&mi->p_full, 128);
+    tc::mbar_init(&mi->p_full, SOFTMAX_THREADS);
     tc::mbar_init(&mi->o_done, 1);
     mi->abort_flag = 0;
     mi->rescale = 0;
@@ -147,11 +165,22 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
           const int base = sg.kv_begin + t * TILE;
           const int row0 = table[base >> 6] * 64;
           const int row1 = base + 64 < sg.kv_end ? table[(base >> 6) + 1] * 64 : p.pool_rows;
+          // start the HBM reads of the NEXT tile of this segment now; its TMA loads, issued as
+          // chunks are freed, then hit L2
+          if (base + TILE < sg.kv_end) {
+            const int nrow0 = table[(base >> 6) + 2] * 64;
+            const int nrow1 = base + TILE + 64 < sg.kv_end ? table[(base >> 6) + 3] * 64 : -1;
+            for (int c = 0; c < NCH; ++c) {
+              tc::tma_prefetch_3d(&tmKV, c * 64, nrow0, 0);
+              if (nrow1 >= 0) tc::tma_prefetch_3d(&tmKV, c * 64, nrow1, 0);
+            }
+          }
           for (int c = 0; c < NCH; ++c) {
             if (g > 0) {
               ok = tc::mbar_wait(&mi->kv_empty[c], (g - 1) & 1, abort_flag, p.d_status, ST_TMA_TIMEOUT);
               if (!ok) break;
             }
+            if (c == 0) TRACE(g, 0);
             if (t == 0 && c == 0) {
               // the QK MMAs of the previous segment have retired (they precede the SV MMAs
               // that freed chunk 0), so Q_eff may be replaced
@@ -162,6 +191,7 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
             tc::mbar_expect_tx(&mi->kv_full[c], KV_CHUNK);
             tc::tma_load_3d(s_kv + c * KV_CHUNK, &tmKV, &mi->kv_full[c], c * 64, row0, 0);
             tc::tma_load_3d(s_kv + c * KV_CHUNK + KV_CHUNK / 2, &tmKV, &mi->kv_full[c], c * 64, row1, 0);
+            if (c == NCH - 1) TRACE(g, 1);
           }
         }
       }
@@ -170,8 +200,12 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc_qk = tc::umma_idesc_bf16(TILE, HEADS, 0, 0);
-      constexpr uint32_t idesc_sv = tc::umma_idesc_bf16(128, HEADS, 1, 1);
-      const uint32_t q_addr = tc::smem_u32(s_q), kv_addr = tc::smem_u32(s_kv), p_addr = tc::smem_u32(s_p);
+      constexpr uint32_t idesc_sv = tc::umma_idesc_bf16(HEADS, 256, 1, 1);
+      // descriptors differ only in their start-address field (16-byte units): the rest is constant
+      const uint64_t k_major = tc::umma_desc_sw128(0, 16, 1024);
+      const uint64_t vt_desc = tc::umma_desc_sw128(0, KV_CHUNK, 1024);
+      const uint32_t q16 = (tc::smem_u32(s_q) & 0x3FFFFu) >> 4, kv16 = (tc::smem_u32(s_kv) & 0x3FFFFu) >> 4,
+                     p16 = (tc::smem_u32(s_p) & 0x3FFFFu) >> 4;
       int g = 0, sidx = 0;
       bool ok = true;
       for (int si = seg0; si < seg1 && ok; ++si, ++sidx) {
@@ -180,74 +214,92 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         ok = tc::mbar_wait(&mi->q_full, sidx & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
         for (int t = 0; t < n_tiles && ok; ++t, ++g) {
           // S^T = K * Q^T, chunk by chunk as the tile lands
-          for (int c = 0; c < NCH && ok; ++c) {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
             ok = tc::mbar_wait(&mi->kv_full[c], g & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
             if (!ok) break;
+            if (c == 0) TRACE(g, 2);
+            if (c == NCH - 1) TRACE(g, 3);
             tc::tc_fence_after();
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-              const uint64_t da = tc::umma_desc_sw128(kv_addr + c * KV_CHUNK + k * 32, 16, 1024);
-              const uint64_t db = tc::umma_desc_sw128(q_addr + c * Q_CHUNK + k * 32, 16, 1024);
+              const uint64_t da = k_major | (uint64_t)(kv16 + c * (KV_CHUNK / 16) + k * 2);
+              const uint64_t db = k_major | (uint64_t)(q16 + c * (Q_CHUNK / 16) + k * 2);
               tc::umma_bf16(tmem + COL_S, da, db, idesc_qk, (c > 0 || k > 0) ? 1u : 0u);
             }
           }
           if (!ok) break;
           tc::umma_commit(&mi->s_full);
+          TRACE(g, 4);
+#ifdef FST_ATTN_TRACE
+          tc::mbar_wait(&mi->s_full, g & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
+          TRACE(g, 14);  // QK MMAs retired
+#endif
           // O^T += V^T * P^T once the softmax threads have written P^T
           ok = tc::mbar_wait(&mi->p_full, g & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
           if (!ok) break;
+          TRACE(g, 5);
           tc::tc_fence_after();
 #pragma unroll
-          for (int mt = 0; mt < 4; ++mt) {
+          for (int nh = 0; nh < 2; ++nh) {
 #pragma unroll
             for (int k = 0; k < TILE / 16; ++k) {
-              // A: d rows 128*mt .. +127 (chunks 2mt, 2mt+1: LBO = chunk stride), tokens 16k .. +15
-              const uint64_t da = tc::umma_desc_sw128(kv_addr + 2 * mt * KV_CHUNK + k * 2048, KV_CHUNK, 1024);
-              const uint64_t db = tc::umma_desc_sw128(p_addr + k * 2048, 16, 1024);
-              tc::umma_bf16(tmem + COL_O + mt * HEADS, da, db, idesc_sv, (t > 0 || k > 0) ? 1u : 0u);
+              // A: P^T rows (tokens) 16k .. +15, all 64 heads.  B: the same tokens of latent
+              // columns 256*nh .. +255 (chunks 4nh .. 4nh+3: LBO = chunk stride)
+              const uint64_t da = k_major | (uint64_t)(p16 + k * 128);
+              const uint64_t db = vt_desc | (uint64_t)(kv16 + 4 * nh * (KV_CHUNK / 16) + k * 128);
+              tc::umma_bf16(tmem + COL_O + ((uint32_t)(nh * 16) << 16), da, db, idesc_sv, (t > 0 || k > 0) ? 1u : 0u);
             }
-            tc::umma_commit(&mi->kv_empty[2 * mt]);
-            tc::umma_commit(&mi->kv_empty[2 * mt + 1]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tc::umma_commit(&mi->kv_empty[4 * nh + c]);
           }
           if (NCH == 9) tc::umma_commit(&mi->kv_empty[8]);
           tc::umma_commit(&mi->o_done);
+          TRACE(g, 6);
+#ifdef FST_ATTN_TRACE
+          tc::mbar_wait(&mi->o_done, g & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
+          TRACE(g, 7);  // SV MMAs retired
+#endif
         }
       }
     }
   } else {
-    // ---------------- softmax / epilogue: thread = one cached token of the tile ----------------
-    const int quad = warp & 3;
+    // ---------------- softmax / epilogue ----------------
+    // thread = one cached token of the tile (TMEM lane) and one half of the heads (32 columns)
+    const int quad = warp & 3;            // TMEM lane quadrant this warp may touch
+    const int half = (warp - 2) >> 2;     // heads 32*half .. 32*half+31
     const int tok_in_tile = quad * 32 + lane;
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-    const int sm_tid = threadIdx.x - 64;  // 0..127
+    const int sm_tid = threadIdx.x - 64;  // 0..255
+    const int h0 = half * 32;
     int g = 0;
     bool ok = true;
     for (int si = seg0; si < seg1 && ok; ++si) {
       const AttnSeg sg = p.segs[si];
       const int n_tiles = (sg.kv_end - sg.kv_begin + TILE - 1) / TILE;
-      float l[HEADS];
+      float l[32];
 #pragma unroll
-      for (int h = 0; h < HEADS; ++h) l[h] = 0.0f;
+      for (int j = 0; j < 32; ++j) l[j] = 0.0f;
       if (sm_tid < HEADS) mi->m_used[sm_tid] = -INFINITY;
       softmax_bar();
       for (int t = 0; t < n_tiles && ok; ++t, ++g) {
         ok = tc::mbar_wait(&mi->s_full, g & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
+        if (sm_tid == 0) TRACE(g, 8);
         tc::tc_fence_after();
         const bool valid = sg.kv_begin + t * TILE + tok_in_tile < sg.kv_end;
-        // pass 1: per-warp maxima over the warp's 32 tokens, for every head
+        float s[32];
+        tc::tmem_ld32(lane_addr + COL_S + h0, s);
+        // pass 1: maxima over the warp's 32 tokens for its 32 heads
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float s[32];
-          tc::tmem_ld32(lane_addr + COL_S + half * 32, s);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float v = valid ? s[j] * p.scale_log2 : -INFINITY;
-            const float r = redux_max(v);
-            if (lane == j) mi->wmax[quad][half * 32 + j] = r;
-          }
+        for (int j = 0; j < 32; ++j) {
+          s[j] = valid ? s[j] * p.scale_log2 : -INFINITY;
+          const float r = redux_max(s[j]);
+          if (lane == j) mi->wmax[quad][h0 + j] = r;
         }
+        if (sm_tid == 0) TRACE(g, 9);
         ok = softmax_bar_and(ok);
         if (!ok) break;
+        if (sm_tid == 0) TRACE(g, 10);
         // one thread per head decides whether the reference maximum moves
         if (sm_tid < HEADS) {
           const float tm = fmaxf(fmaxf(mi->wmax[0][sm_tid], mi->wmax[1][sm_tid]),
@@ -255,33 +307,39 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
           const float mo = mi->m_used[sm_tid];
           float a = 1.0f;
           if (tm > mo + RESCALE_THRESHOLD) {  // also the first tile (mo = -inf)
-            a = exp2f(mo - tm);
+            a = ex2(mo - tm);
             mi->m_used[sm_tid] = tm;
             if (t > 0) mi->rescale = 1;
           }
           mi->alpha[sm_tid] = a;
         }
         softmax_bar();
+        if (sm_tid == 0) TRACE(g, 11);
         const bool rescale = mi->rescale != 0;
         // pass 2: P = exp2(s - m), row sums, P^T into shared memory (MN-major, 128-byte swizzle)
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float s[32];
-          tc::tmem_ld32(lane_addr + COL_S + half * 32, s);
+        {
           uint32_t packed[16];
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const int h = half * 32 + j;
-            const float p0 = valid ? exp2f(s[j] * p.scale_log2 - mi->m_used[h]) : 0.0f;
-            const float p1 = valid ? exp2f(s[j + 1] * p.scale_log2 - mi->m_used[h + 1]) : 0.0f;
+          for (int j4 = 0; j4 < 32; j4 += 4) {
+            const float4 m4 = *reinterpret_cast<const float4*>(&mi->m_used[h0 + j4]);
+            float pv[4];
+            pv[0] = ex2(s[j4] - m4.x);      // masked tokens: ex2(-inf) = 0
+            pv[1] = ex2(s[j4 + 1] - m4.y);
+            pv[2] = ex2(s[j4 + 2] - m4.z);
+            pv[3] = ex2(s[j4 + 3] - m4.w);
             if (rescale) {
-              l[h] *= mi->alpha[h];
-              l[h + 1] *= mi->alpha[h + 1];
+              const float4 a4 = *reinterpret_cast<const float4*>(&mi->alpha[h0 + j4]);
+              l[j4] *= a4.x;
+              l[j4 + 1] *= a4.y;
+              l[j4 + 2] *= a4.z;
+              l[j4 + 3] *= a4.w;
             }
-            l[h] += p0;
-            l[h + 1] += p1;
-            __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-            packed[j / 2] = *reinterpret_cast<uint32_t*>(&b);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) l[j4 + e] += pv[e];
+            __nv_bfloat162 b0 = __floats2bfloat162_rn(pv[0], pv[1]);
+            __nv_bfloat162 b1 = __floats2bfloat162_rn(pv[2], pv[3]);
+            packed[j4 / 2] = *reinterpret_cast<uint32_t*>(&b0);
+            packed[j4 / 2 + 1] = *reinterpret_cast<uint32_t*>(&b1);
           }
           unsigned char* prow = s_p + tok_in_tile * 128;
 #pragma unroll
@@ -291,22 +349,27 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                 make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
           }
         }
-        // the reference maximum moved: rescale O^T (thread = one row of each 128-row block).
+        // the reference maximum moved: rescale O.  A 32-lane TMEM load hands lanes 0-15 the
+        // rows of the first accumulator and lanes 16-31 those of the second, so thread = one
+        // head, one half of the latent columns; the two warps of a quadrant split the columns.
         // s_full of this tile implies that the SV MMAs of the previous tile have retired.
         if (rescale) {
+          const float a = mi->alpha[quad * 16 + (lane & 15)];
 #pragma unroll 1
-          for (int blk = 0; blk < 8; ++blk) {
+          for (int c = 0; c < 4; ++c) {
             float o[32];
-            const uint32_t addr = lane_addr + COL_O + blk * 32;
+            const uint32_t addr = lane_addr + COL_O + half * 128 + c * 32;
             tc::tmem_ld32(addr, o);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] *= mi->alpha[(blk & 1) * 32 + j];
+            for (int j = 0; j < 32; ++j) o[j] *= a;
             tc::tmem_st32(addr, o);
           }
         }
+        if (sm_tid == 0) TRACE(g, 12);
         tc::fence_proxy_async();
         tc::tc_fence_before();
         softmax_bar();  // every thread has read alpha / rescale before they are reset
+        if (sm_tid == 0) TRACE(g, 13);
         if (sm_tid == 0) mi->rescale = 0;
         tc::mbar_arrive(&mi->p_full);
       }
@@ -315,9 +378,9 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       ok = tc::mbar_wait(&mi->o_done, (g - 1) & 1, abort_flag, p.d_status, ST_EPI_TIMEOUT);
       tc::tc_fence_after();
 #pragma unroll
-      for (int h = 0; h < HEADS; ++h) {
-        const float v = warp_sum(l[h]);
-        if (lane == (h & 31)) mi->wmax[quad][h] = v;
+      for (int j = 0; j < 32; ++j) {
+        const float v = warp_sum(l[j]);
+        if (lane == j) mi->wmax[quad][h0 + j] = v;
       }
       ok = softmax_bar_and(ok);
       if (!ok) break;
@@ -326,14 +389,17 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         p.part_l[(long long)sg.part * HEADS + sm_tid] = sum;
         p.part_m[(long long)sg.part * HEADS + sm_tid] = mi->m_used[sm_tid] * 0.6931471805599453f;  // back to ln units
       }
-      float* po = p.part_o + (long long)sg.part * HEADS * D_V;
+      {
+        const int head = quad * 16 + (lane & 15);
+        float* po = p.part_o + ((long long)sg.part * HEADS + head) * D_V + (lane >> 4) * 256 + half * 128;
 #pragma unroll 1
-      for (int blk = 0; blk < 8; ++blk) {
-        float o[32];
-        tc::tmem_ld32(lane_addr + COL_O + blk * 32, o);
-        const int d = (blk >> 1) * 128 + tok_in_tile;  // row of O^T
+        for (int c = 0; c < 4; ++c) {
+          float o[32];
+          tc::tmem_ld32(lane_addr + COL_O + half * 128 + c * 32, o);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) po[(long long)((blk & 1) * 32 + j) * D_V + d] = o[j];
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(po + c * 32 + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+        }
       }
       tc::tc_fence_before();
       softmax_bar();  // wmax / m_used are reused by the next segment
@@ -352,6 +418,12 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 }
 
 }  // namespace
+
+#ifdef FST_ATTN_TRACE
+extern "C" int fst_debug_read_attn_trace(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(long long) * 64 * 16);
+}
+#endif
 
 bool attn_tc_supported(const AttnArgs& a) {
   return a.H == HEADS && a.d_v == D_V && a.page_tokens == 64 && a.row == a.d_qk &&

@@ -1,13 +1,17 @@
-// Skinny bf16 GEMM on the 5th-generation tensor cores: C[M, N] = A[M, K] * W[N, K]^T with the
-// weight rows as the MMA M dimension (128 per CTA) and the tokens as the MMA N dimension, so a
-// handful of tokens still fills a full-rate 128-row tcgen05.mma.  This is the tile engine the
-// reference calls npu_gemm_mla_vec (src/fst_engine.cpp:465-575): weights stay in their native
-// [N, K] layout and are streamed from HBM exactly once.
+// Skinny bf16 GEMM on the 5th-generation tensor cores: C[M, N] = A[M, K] * W^T with the weight
+// rows as the MMA M dimension (128 per CTA) and the tokens as the MMA N dimension, so a handful
+// of tokens still fills a 128-row tcgen05.mma.  This is the tile engine the reference calls
+// npu_gemm_mla_vec (src/fst_engine.cpp:465-575): weights stay in their native layout -- [N, K]
+// (the b_col_maj kernels) or [K, N] (the b_row_maj kernel, 480) -- and are streamed from HBM
+// exactly once.
 //
-// One CTA = one (128-row weight tile, token tile, K split).  Warp 0 streams both operands with
-// TMA through a ring of 128-byte-swizzled stages; one lane of warp 1 issues tcgen05.mma into
-// a TMEM accumulator; warps 2-5 drain TMEM.  When K is split the CTAs leave fp32 partials and
-// the last one to finish a tile adds them in split order (deterministic) and writes bf16.
+// One CTA = one (128-row weight tile, token tile, K slice).  Warp 0 streams both operands with
+// TMA through a ring of 128-byte-swizzled stages; one lane of warp 1 issues tcgen05.mma into a
+// TMEM accumulator; warps 2-5 drain TMEM.  The K slices of one output tile form a thread-block
+// cluster: every CTA parks its fp32 partial in its own shared memory and then reduces one
+// column slice of the tile over all peers through distributed shared memory, in rank order
+// (deterministic), without a round trip through global memory.
+#include <algorithm>
 #include <mutex>
 #include <unordered_map>
 
@@ -18,15 +22,14 @@ namespace fst {
 
 namespace {
 
-constexpr int BK = 64;          // K elements per stage: one 128-byte swizzle span
-constexpr int W_TILE = 128;     // weight rows per CTA
+constexpr int BK = 64;       // K elements per stage: one 128-byte swizzle span
+constexpr int W_TILE = 128;  // weight rows per CTA
 constexpr int W_BYTES = W_TILE * BK * 2;
 constexpr int GEMM_THREADS = 192;
+constexpr int MAX_SPLITS = 8;  // portable cluster size
 
 struct GemmTcParams {
   bf16* C;
-  float* ws;           // [batch][splits][M][N] fp32 partials (splits > 1)
-  unsigned* counters;  // one per output tile, all zero between launches
   int* d_status;
   int M, N, K, ldc;
   long long c_bs;
@@ -34,20 +37,44 @@ struct GemmTcParams {
   int w_swap, a_swap;  // the batch index is the middle tensor-map coordinate (its stride is the smaller one)
 };
 
-template <int NT>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 16 bytes from the same shared-memory offset of the cluster's CTA `rank`.
+__device__ __forceinline__ float4 ld_peer_f32x4(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(remote)
+               : "memory");
+  return v;
+}
+
+// NT: token tile (MMA N).  W_KN: the weight operand is stored [K, N] (N contiguous) and is read
+// as an MN-major UMMA operand; otherwise [N, K], K-major.
+template <int NT, bool W_KN>
+__global__ void __launch_bounds__(GEMM_THREADS, 2)
 k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA, GemmTcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   constexpr int A_BYTES = NT * BK * 2;
   constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
   constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
+  constexpr int RED_BYTES = NT * W_TILE * 4;  // fp32 partial tile, parked over the ring
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)p.stages * STAGE_BYTES);
-  uint64_t* empty = full + p.stages;
-  uint64_t* acc_bar = empty + p.stages;
+  const int ring = p.stages * STAGE_BYTES;
+  unsigned char* misc = smem + ((p.splits == 1 || ring > RED_BYTES) ? ring : RED_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(misc);
+  uint64_t* empty = full + 8;
+  uint64_t* acc_bar = empty + 8;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* last_flag = const_cast<int*>(abort_flag) + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * W_TILE;
@@ -65,7 +92,6 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     }
     tc::mbar_init(acc_bar, 1);
     *abort_flag = 0;
-    *last_flag = 0;
     tc::fence_barrier_init();
   }
   if (warp == 1) tc::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -83,26 +109,39 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
         if (i >= p.stages && !tc::mbar_wait(&empty[s], ((i / p.stages) - 1) & 1, abort_flag, p.d_status, ST_TMA_TIMEOUT))
           break;
         unsigned char* st = smem + (size_t)s * STAGE_BYTES;
+        const int k0 = (kc0 + i) * BK;
         tc::mbar_expect_tx(&full[s], STAGE_BYTES);
-        tc::tma_load_3d(st, &tmW, &full[s], (kc0 + i) * BK, p.w_swap ? z : n0, p.w_swap ? n0 : z);
-        tc::tma_load_3d(st + W_BYTES, &tmA, &full[s], (kc0 + i) * BK, p.a_swap ? z : m0, p.a_swap ? m0 : z);
+        if (W_KN) {
+          // two boxes of [64 k rows x 64 n]: n is the innermost coordinate
+          tc::tma_load_3d(st, &tmW, &full[s], n0, k0, z);
+          tc::tma_load_3d(st + W_BYTES / 2, &tmW, &full[s], n0 + 64, k0, z);
+        } else {
+          tc::tma_load_3d(st, &tmW, &full[s], k0, p.w_swap ? z : n0, p.w_swap ? n0 : z);
+        }
+        tc::tma_load_3d(st + W_BYTES, &tmA, &full[s], k0, p.a_swap ? z : m0, p.a_swap ? m0 : z);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = tc::umma_idesc_bf16(W_TILE, NT, 0, 0);
+      constexpr uint32_t idesc = tc::umma_idesc_bf16(W_TILE, NT, W_KN ? 1 : 0, 0);
+      // descriptors differ only in the start-address field: keep the rest in registers
+      const uint64_t w_tmpl = W_KN ? tc::umma_desc_sw128(0, W_BYTES / 2, 1024) : tc::umma_desc_sw128(0, 16, 1024);
+      const uint64_t a_tmpl = tc::umma_desc_sw128(0, 16, 1024);
+      // 14-bit start-address field: inside a cluster the shared-window address of a CTA carries
+      // its rank in high bits, which must not leak into the neighbouring descriptor fields
+      const uint32_t base = tc::smem_u32(smem) & 0x3FFFFu;
       bool ok = true;
       for (int i = 0; i < n_kc && ok; ++i) {
         const int s = i % p.stages;
         ok = tc::mbar_wait(&full[s], (i / p.stages) & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
         if (!ok) break;
         tc::tc_fence_after();
-        const uint32_t w_addr = tc::smem_u32(smem + (size_t)s * STAGE_BYTES);
-        const uint32_t a_addr = w_addr + W_BYTES;
+        const uint32_t w16 = (base + s * STAGE_BYTES) >> 4, a16 = w16 + (W_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k) {
-          const uint64_t da = tc::umma_desc_sw128(w_addr + k * 32, 16, 1024);
-          const uint64_t db = tc::umma_desc_sw128(a_addr + k * 32, 16, 1024);
+          // K-major: 16 k = 32 bytes along the row; MN-major: 16 k rows of 128 bytes
+          const uint64_t da = w_tmpl | (uint64_t)(w16 + (W_KN ? k * 128 : k * 2));
+          const uint64_t db = a_tmpl | (uint64_t)(a16 + k * 2);
           tc::umma_bf16(tmem, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
         }
         tc::umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
@@ -110,14 +149,17 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
       if (ok) tc::umma_commit(acc_bar);
     }
   } else {
-    // epilogue warps: TMEM lane quadrant = warp % 4
+    // epilogue warps: TMEM lane quadrant = warp % 4; thread = one weight row n
     const int quad = warp & 3;
-    const bool ok = n_kc == 0 || tc::mbar_wait(acc_bar, 0, abort_flag, p.d_status, ST_EPI_TIMEOUT);
+    bool ok = n_kc == 0 || tc::mbar_wait(acc_bar, 0, abort_flag, p.d_status, ST_EPI_TIMEOUT);
+    ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
     tc::tc_fence_after();
-    const int n = n0 + quad * 32 + lane;
+    const int row = quad * 32 + lane;
+    const int n = n0 + row;
     if (ok) {
+      float* red = reinterpret_cast<float*>(smem);  // [NT][128]: the ring is idle once acc_bar fired
       for (int c0 = 0; c0 < NT; c0 += 32) {
-        if (m0 + c0 >= p.M) break;
+        if (p.splits == 1 && m0 + c0 >= p.M) break;
         float v[32];
         if (n_kc > 0) {
           tc::tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + c0, v);
@@ -125,48 +167,52 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.0f;
         }
-        if (n < p.N) {
-          if (p.splits == 1) {
+        if (p.splits == 1) {
+          if (n < p.N) {
             bf16* c = p.C + z * p.c_bs + n;
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (j < NT - c0 && m0 + c0 + j < p.M) c[(long long)(m0 + c0 + j) * p.ldc] = f2bf(v[j]);
-          } else {
-            float* w = p.ws + (((long long)z * p.splits + split) * p.M) * p.N + n;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < NT - c0 && m0 + c0 + j < p.M) w[(long long)(m0 + c0 + j) * p.N] = v[j];
           }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < NT - c0) red[(c0 + j) * W_TILE + row] = v[j];
         }
       }
     }
   }
 
-  // split-K: the CTA that finishes a tile last adds the partials in split order
+  __syncwarp();  // the single-lane roles rejoin their warps before the aligned barriers below
   if (p.splits > 1) {
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      unsigned* ctr = p.counters + ((size_t)z * (gridDim.y / p.splits) + m_tile) * gridDim.x + blockIdx.x;
-      const unsigned old = atomicAdd(ctr, 1u);
-      if (old == (unsigned)p.splits - 1) {
-        *last_flag = 1;
-        *ctr = 0;
+    // every K slice has parked its partial: reduce one column slice of the tile over the
+    // cluster, peers in rank order
+    cluster_sync_all();
+    const uint32_t rank = cluster_ctarank();
+    const int c_lo = (int)(NT * rank / p.splits), c_hi = (int)(NT * (rank + 1) / p.splits);
+    const uint32_t red_addr = tc::smem_u32(smem);
+    for (int e4 = c_lo * (W_TILE / 4) + threadIdx.x; e4 < c_hi * (W_TILE / 4); e4 += GEMM_THREADS) {
+      const int col = e4 / (W_TILE / 4), row = (e4 % (W_TILE / 4)) * 4;
+      float4 v[MAX_SPLITS];
+#pragma unroll
+      for (int s = 0; s < MAX_SPLITS; ++s)  // all loads in flight before the first add
+        v[s] = s < p.splits ? ld_peer_f32x4(red_addr + (uint32_t)e4 * 16, (uint32_t)s) : make_float4(0.f, 0.f, 0.f, 0.f);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < MAX_SPLITS; ++s) {
+        acc[0] += v[s].x;
+        acc[1] += v[s].y;
+        acc[2] += v[s].z;
+        acc[3] += v[s].w;
+      }
+      if (m0 + col < p.M) {
+        bf16* c = p.C + z * p.c_bs + (long long)(m0 + col) * p.ldc + n0 + row;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n0 + row + j < p.N) c[j] = f2bf(acc[j]);
       }
     }
-    __syncthreads();
-    if (*last_flag) {
-      __threadfence();
-      const int mt = min(NT, p.M - m0), nt = min(W_TILE, p.N - n0);
-      const float* w = p.ws + ((long long)z * p.splits * p.M) * p.N;
-      for (int e = threadIdx.x; e < mt * W_TILE; e += GEMM_THREADS) {
-        const int ml = e / W_TILE, nl = e % W_TILE;
-        if (nl >= nt) continue;
-        float acc = 0.0f;
-        for (int s = 0; s < p.splits; ++s) acc += w[((long long)s * p.M + m0 + ml) * p.N + n0 + nl];
-        p.C[z * p.c_bs + (long long)(m0 + ml) * p.ldc + n0 + nl] = f2bf(acc);
-      }
-    }
+    cluster_sync_all();  // nobody leaves while a peer still reads its shared memory
   }
 
   tc::tc_fence_before();
@@ -181,22 +227,40 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
   }
 }
 
-struct Workspace {
-  float* ws = nullptr;
-  size_t ws_elems = 0;
-  unsigned* counters = nullptr;
-  size_t n_counters = 0;
-};
-Workspace g_ws[64];  // per device
-
 int pick_nt(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
+
+template <int NT, bool W_KN>
+cudaError_t launch_one(const CUtensorMap& tmW, const CUtensorMap& tmA, const GemmTcParams& p, dim3 grid, size_t smem,
+                       cudaStream_t st) {
+  static bool attr_set = false;
+  cudaError_t e;
+  if (!attr_set) {
+    e = cudaFuncSetAttribute(k_gemm_tc<NT, W_KN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = p.splits;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, k_gemm_tc<NT, W_KN>, tmW, tmA, p);
+}
 
 }  // namespace
 
 bool gemm_tc_supported(const GemmArgs& g) {
-  if (g.b_kn || g.M <= 0 || g.N <= 0 || g.K <= 0) return false;
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return false;
   if (g.K % 8 || g.lda % 8 || g.ldb % 8 || g.a_bs % 8 || g.b_bs % 8) return false;
   if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.B) & 15)) return false;
+  if (g.b_kn && g.N % 8) return false;
   return true;
 }
 
@@ -204,35 +268,20 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, int* d_status, cudaStream_t st) {
   int dev = 0, n_sm = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-  const int NT = pick_nt(g.M);
-  const int n_tiles = (g.N + W_TILE - 1) / W_TILE, m_tiles = (g.M + NT - 1) / NT;
+  static int sm_count[64] = {0};
+  if (!sm_count[dev & 63]) cudaDeviceGetAttribute(&sm_count[dev & 63], cudaDevAttrMultiProcessorCount, dev);
+  n_sm = sm_count[dev & 63];
+  int NT = pick_nt(g.M);
+  const int n_tiles = (g.N + W_TILE - 1) / W_TILE;
+  // a 256-token tile leaves no room for the parked partial: use it only when no K split is needed
+  if (NT == 256 && (long long)n_tiles * ((g.M + 255) / 256) * g.batch * 2 <= 2ll * n_sm) NT = 128;
+  const int m_tiles = (g.M + NT - 1) / NT;
   const int kc_total = (g.K + BK - 1) / BK;
-  // split K until the grid covers the SMs, keeping at least 4 K chunks per CTA
-  int splits = 1;
+  // K slices (a power of two, one cluster) while two CTAs per SM are not yet covered, keeping
+  // at least two K chunks per CTA
   const long long tiles = (long long)n_tiles * m_tiles * g.batch;
-  if (tiles < n_sm) splits = (int)std::min<long long>((n_sm + tiles - 1) / tiles, std::max(1, kc_total / 4));
-  while (splits > 1 && (size_t)g.batch * splits * g.M * g.N > (size_t)(64u << 20)) --splits;
-
-  Workspace& W = g_ws[dev & 63];
-  const size_t need_ws = splits > 1 ? (size_t)g.batch * splits * g.M * g.N : 0;
-  const size_t need_ctr = (size_t)tiles;
-  if (need_ws > W.ws_elems) {
-    if (W.ws) cudaFree(W.ws);
-    W.ws = nullptr;
-    W.ws_elems = 0;
-    if ((e = cudaMalloc((void**)&W.ws, need_ws * sizeof(float))) != cudaSuccess) return e;
-    W.ws_elems = need_ws;
-  }
-  if (need_ctr > W.n_counters) {
-    if (W.counters) cudaFree(W.counters);
-    W.counters = nullptr;
-    W.n_counters = 0;
-    const size_t n = std::max<size_t>(need_ctr, 4096);
-    if ((e = cudaMalloc((void**)&W.counters, n * sizeof(unsigned))) != cudaSuccess) return e;
-    if ((e = cudaMemset(W.counters, 0, n * sizeof(unsigned))) != cudaSuccess) return e;
-    W.n_counters = n;
-  }
+  int splits = 1;
+  while (splits < MAX_SPLITS && tiles * splits * 2 <= 2ll * n_sm && kc_total / (splits * 2) >= 2) splits *= 2;
 
   CUtensorMap tmW, tmA;
   const char* err = nullptr;
@@ -247,37 +296,43 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, int* d_status, cudaStream_t st) {
     return tc::cached_tmap(out, base, g.K, rows, g.batch, row_b, std::max<uint64_t>(bat_b, 16), BK, box_rows, 1, &err);
   };
   int w_swap = 0, a_swap = 0;
-  if (!build(&tmW, g.B, g.N, g.ldb, g.b_bs, W_TILE, &w_swap) || !build(&tmA, g.A, g.M, g.lda, g.a_bs, NT, &a_swap))
-    return cudaErrorInvalidValue;
+  bool ok;
+  if (g.b_kn) {
+    // W is [K, N]: dims {N, K, batch}, boxes of 64 n x 64 k
+    const uint64_t row_b = (uint64_t)g.ldb * 2;
+    const uint64_t bat_b = g.batch > 1 ? (uint64_t)g.b_bs * 2 : row_b * (uint64_t)g.K;
+    ok = tc::cached_tmap(&tmW, g.B, g.N, g.K, g.batch, row_b, std::max<uint64_t>(bat_b, 16), 64, BK, 1, &err);
+  } else {
+    ok = build(&tmW, g.B, g.N, g.ldb, g.b_bs, W_TILE, &w_swap);
+  }
+  if (!ok || !build(&tmA, g.A, g.M, g.lda, g.a_bs, NT, &a_swap)) return cudaErrorInvalidValue;
 
   GemmTcParams p;
-  p.C = g.C; p.ws = W.ws; p.counters = W.counters; p.d_status = d_status;
+  p.C = g.C; p.d_status = d_status;
   p.M = g.M; p.N = g.N; p.K = g.K; p.ldc = g.ldc; p.c_bs = g.c_bs;
   p.splits = splits; p.kc_total = kc_total; p.w_swap = w_swap; p.a_swap = a_swap;
   const int stage_bytes = W_BYTES + NT * BK * 2;
-  p.stages = std::max(2, std::min(8, (200 * 1024) / stage_bytes));
-  const size_t smem = (size_t)p.stages * stage_bytes + 1024 /* alignment */ + 256 /* barriers */;
+  p.stages = std::max(2, std::min(8, (96 * 1024) / stage_bytes));
+  const size_t ring = (size_t)p.stages * stage_bytes, red = splits > 1 ? (size_t)NT * W_TILE * 4 : 0;
+  const size_t smem = std::max(ring, red) + 1024 /* alignment */ + 256 /* barriers */;
   dim3 grid(n_tiles, m_tiles * splits, g.batch);
 
-#define FST_LAUNCH_GEMM(NTV)                                                                      \
-  do {                                                                                            \
-    static bool attr_set = false;                                                                 \
-    if (!attr_set) {                                                                              \
-      e = cudaFuncSetAttribute(k_gemm_tc<NTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); \
-      if (e != cudaSuccess) return e;                                                             \
-      attr_set = true;                                                                            \
-    }                                                                                             \
-    k_gemm_tc<NTV><<<grid, GEMM_THREADS, smem, st>>>(tmW, tmA, p);                                \
-  } while (0)
+#define FST_GEMM_CASE(NTV)                                                                   \
+  case NTV:                                                                                  \
+    e = g.b_kn ? launch_one<NTV, true>(tmW, tmA, p, grid, smem, st)                          \
+               : launch_one<NTV, false>(tmW, tmA, p, grid, smem, st);                        \
+    break
   switch (NT) {
-    case 16: FST_LAUNCH_GEMM(16); break;
-    case 32: FST_LAUNCH_GEMM(32); break;
-    case 64: FST_LAUNCH_GEMM(64); break;
-    case 128: FST_LAUNCH_GEMM(128); break;
-    default: FST_LAUNCH_GEMM(256); break;
+    FST_GEMM_CASE(16);
+    FST_GEMM_CASE(32);
+    FST_GEMM_CASE(64);
+    FST_GEMM_CASE(128);
+    default:
+      e = g.b_kn ? launch_one<256, true>(tmW, tmA, p, grid, smem, st) : launch_one<256, false>(tmW, tmA, p, grid, smem, st);
+      break;
   }
-#undef FST_LAUNCH_GEMM
-  return cudaGetLastError();
+#undef FST_GEMM_CASE
+  return e;
 }
 
 // ---- host: tensor map encoding through the driver entry point (no link-time libcuda) ----------
@@ -319,6 +374,7 @@ bool make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t
 }
 
 namespace {
+
 struct TmapKey {
   const void* base;
   uint64_t d0, d1, d2, s1, s2;
@@ -358,7 +414,6 @@ bool cached_tmap(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, u
   g_tmaps.emplace(key, *out);
   return true;
 }
-
 
 }  // namespace tc
 }  // namespace fst

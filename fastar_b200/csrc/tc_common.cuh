@@ -1,4 +1,4 @@
-// sm_100a building blocks: mbarrier, TMA (cp.async.bulk.tensor, never multicast), TMEM
+// sm_100a building blocks: mbarrier, TMA (plain per-CTA cp.async.bulk.tensor loads), TMEM
 // allocation, tcgen05.mma / commit / ld / st, and the UMMA descriptors.
 #pragma once
 #include <cuda.h>
@@ -52,9 +52,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
                                           int* d_status, int code) {
   for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) {
+    if (it > 1024) {  // the common case completes within a few polls: back off only after that
       if (*abort_flag) return false;
-      __nanosleep(it > 4096 ? 256 : 32);
+      __nanosleep(it > 65536 ? 256 : 20);
     }
   }
   *abort_flag = 1;
@@ -71,6 +71,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* m, uin
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
+}
+// Brings a box into L2 only (no shared-memory destination, no barrier).
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z)
+               : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z) {
   asm volatile(

@@ -80,18 +80,16 @@ def test_shapes_with_tails(ctx, M, N, K):
     assert np.max(np.abs(got - want)) <= 2.0 ** -8 * np.max(np.abs(want)) + 1e-6
 
 
-def test_b_row_major_operand(ctx):
-    # the qksv-style [K, N] operand (src/fst_engine.cpp:480); only the CUDA-core kernel takes it
-    if ctx.cfg.gemm_impl == mla.IMPL_TENSOR:
-        with pytest.raises(mla.MlaError):
-            ctx.gemm(np.zeros((4, 128), np.uint16), np.zeros((128, 512), np.uint16), b_kn=True)
-        return
-    rng = np.random.default_rng(5)
-    A = synth.to_bf16_bits(rng.standard_normal((9, 128)).astype(np.float32))
-    B = synth.to_bf16_bits(rng.standard_normal((128, 512)).astype(np.float32))
+@pytest.mark.parametrize("M,K,N", [(9, 128, 512), (64, 128, 512), (3, 200, 136)])
+def test_b_row_major_operand(ctx, M, K, N):
+    # the qksv-style [K, N] operand (src/fst_engine.cpp:480)
+    rng = np.random.default_rng(5 + M)
+    A = synth.to_bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    B = synth.to_bf16_bits(rng.standard_normal((K, N)).astype(np.float32))
     got = synth.from_bf16_bits(ctx.gemm(A, B, b_kn=True))
     want = ref_gemm(A, B, b_kn=True)
     assert cosine(got, want) >= 0.99999
+    assert np.max(np.abs(got - want)) <= 2.0 ** -8 * np.max(np.abs(want)) + 1e-6
 
 
 def test_same_inputs_give_identical_bits(ctx):
