@@ -18,8 +18,8 @@
 // QK MMAs of the next tile start on the chunks that have landed.  With 576-wide rows the
 // rope chunk is dead after QK, so P^T is written over it.
 //
-// Warp roles: warp 0 lane 0 issues TMA (and prefetches the next tile into L2, so that the
-// refill of a freed chunk is an L2 hit); warp 1 lane 0 issues tcgen05.mma (warp 1 owns the TMEM
+// Warp roles: one lane of warps 0, 10 and 11 issues TMA (and prefetches the next tile into L2,
+// so that the refill of a freed chunk is an L2 hit); warp 1 lane 0 issues tcgen05.mma (warp 1 owns the TMEM
 // allocation); warps 2-9 are the softmax / epilogue threads: two per cached token (TMEM lane),
 // 32 heads each.  TMEM: S^T in columns [0, 64).  O is two 64-row accumulators [64, 256] in
 // columns [64, 320): a 64-row accumulator occupies lanes 0-15 of each 32-lane quadrant (head h
@@ -36,7 +36,7 @@ constexpr int HEADS = 64;
 constexpr int D_V = 512;
 constexpr int Q_CHUNK = HEADS * 128;   // bytes of one [64 x 64] bf16 chunk of Q
 constexpr int KV_CHUNK = TILE * 128;   // bytes of one [128 x 64] bf16 chunk of the tile
-constexpr int ATTN_THREADS = 320;
+constexpr int ATTN_THREADS = 384;
 constexpr int SOFTMAX_THREADS = 256;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_O = 64;
@@ -51,10 +51,17 @@ struct AttnTcParams {
   float* part_l;
   float* part_o;
   int* d_status;
+  const bf16* pool;
   int pool_rows;   // first row index outside the pool: TMA fills zeros there
   float scale_log2;
 };
 
+#ifndef FST_PREFETCH
+#define FST_PREFETCH 1
+#endif
+#ifndef FST_STAGGER
+#define FST_STAGGER 1200
+#endif
 #ifdef FST_ATTN_TRACE
 // Phase timestamps (SM clock) of CTA 0, for tuning builds only: [tile][event].
 __device__ long long g_attn_trace[64 * 16];
@@ -150,11 +157,21 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   tc::tc_fence_after();
   const uint32_t tmem = mi->tmem_slot;
 
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
+  if (warp == 0 || warp >= 10) {
+    // ---------------- TMA producers ----------------
+    // Three producer warps (0, 10, 11), one lane each: a thread needs ~200 cycles per tensor
+    // copy it issues, so the 18 copies of a tile are split three ways.  Producer r streams
+    // chunks r, r+3, r+6: the SV MMAs free chunks 0-3 first and 4-8 last, and this way no
+    // producer has more than two of the late chunks.
     if (lane == 0) {
-      tc::tma_prefetch_desc(&tmQ);
-      tc::tma_prefetch_desc(&tmKV);
+      const int r = warp == 0 ? 0 : warp - 9;
+      if (r == 0) {
+        tc::tma_prefetch_desc(&tmQ);
+        tc::tma_prefetch_desc(&tmKV);
+      }
+      // half of the CTAs start a little later, so that the SMs do not all refill their tile
+      // (and compete for L2 bandwidth) at the same instant
+      if (FST_STAGGER && (blockIdx.x & 1)) __nanosleep(FST_STAGGER);
       int g = 0;
       bool ok = true;
       for (int si = seg0; si < seg1 && ok; ++si) {
@@ -165,33 +182,33 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
           const int base = sg.kv_begin + t * TILE;
           const int row0 = table[base >> 6] * 64;
           const int row1 = base + 64 < sg.kv_end ? table[(base >> 6) + 1] * 64 : p.pool_rows;
-          // start the HBM reads of the NEXT tile of this segment now; its TMA loads, issued as
-          // chunks are freed, then hit L2
-          if (base + TILE < sg.kv_end) {
-            const int nrow0 = table[(base >> 6) + 2] * 64;
-            const int nrow1 = base + TILE + 64 < sg.kv_end ? table[(base >> 6) + 3] * 64 : -1;
-            for (int c = 0; c < NCH; ++c) {
-              tc::tma_prefetch_3d(&tmKV, c * 64, nrow0, 0);
-              if (nrow1 >= 0) tc::tma_prefetch_3d(&tmKV, c * 64, nrow1, 0);
-            }
-          }
-          for (int c = 0; c < NCH; ++c) {
+          for (int c = r; c < NCH; c += 3) {
             if (g > 0) {
               ok = tc::mbar_wait(&mi->kv_empty[c], (g - 1) & 1, abort_flag, p.d_status, ST_TMA_TIMEOUT);
               if (!ok) break;
             }
             if (c == 0) TRACE(g, 0);
-            if (t == 0 && c == 0) {
-              // the QK MMAs of the previous segment have retired (they precede the SV MMAs
-              // that freed chunk 0), so Q_eff may be replaced
-              tc::mbar_expect_tx(&mi->q_full, L::Q_BYTES);
-              for (int cc = 0; cc < NCH; ++cc)
-                tc::tma_load_3d(s_q + cc * Q_CHUNK, &tmQ, &mi->q_full, cc * 64, sg.tok * HEADS, 0);
+            if (t == 0) {
+              // The QK MMAs of the previous segment have retired (they precede the SV MMAs that
+              // freed this chunk), so Q_eff may be replaced.  Producer 0 arms the barrier; a copy
+              // that completes before that only makes the pending byte count negative.
+              if (c == 0) tc::mbar_expect_tx(&mi->q_full, L::Q_BYTES);
+              tc::tma_load_3d(s_q + c * Q_CHUNK, &tmQ, &mi->q_full, c * 64, sg.tok * HEADS, 0);
             }
             tc::mbar_expect_tx(&mi->kv_full[c], KV_CHUNK);
             tc::tma_load_3d(s_kv + c * KV_CHUNK, &tmKV, &mi->kv_full[c], c * 64, row0, 0);
             tc::tma_load_3d(s_kv + c * KV_CHUNK + KV_CHUNK / 2, &tmKV, &mi->kv_full[c], c * 64, row1, 0);
             if (c == NCH - 1) TRACE(g, 1);
+          }
+          // Start the HBM reads of the NEXT tile of this segment now: its copies, issued as
+          // chunks are freed, then hit L2.
+          if (ok && FST_PREFETCH && base + TILE < sg.kv_end) {
+            const int nrow0 = table[(base >> 6) + 2] * 64;
+            const int nrow1 = base + TILE + 64 < sg.kv_end ? table[(base >> 6) + 3] * 64 : -1;
+            for (int c = r; c < NCH; c += 3) {
+              tc::tma_prefetch_3d(&tmKV, c * 64, nrow0, 0);
+              if (nrow1 >= 0) tc::tma_prefetch_3d(&tmKV, c * 64, nrow1, 0);
+            }
           }
         }
       }
@@ -448,6 +465,7 @@ cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st) {
   AttnTcParams p;
   p.tables = a.tables; p.tok_table = a.tok_table; p.segs = a.segs; p.cta_seg = a.cta_seg;
   p.part_m = a.part_m; p.part_l = a.part_l; p.part_o = a.part_o; p.d_status = a.d_status;
+  p.pool = a.pool;
   p.pool_rows = (int)a.pool_rows;
   p.scale_log2 = a.scale * 1.4426950408889634f;
   cudaError_t e;

@@ -72,6 +72,11 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* m, uin
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// Brings `bytes` (a multiple of 16, from a 16-byte aligned address) of global memory into L2.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gptr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(gptr)), "r"(bytes)
+               : "memory");
+}
 // Brings a box into L2 only (no shared-memory destination, no barrier).
 __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int x, int y, int z) {
   asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"

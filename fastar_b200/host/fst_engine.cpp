@@ -1,0 +1,151 @@
+// FSTEngine (MLA subset) over the CUDA C ABI.  See fst_engine.h.
+#include "fst_engine.h"
+
+#include <cmath>
+#include <cstring>
+#include <stdexcept>
+
+static inline float bf16f(bf16_t v) {  // reference src/fst_engine.cpp:26
+  uint32_t b = (uint32_t)v << 16;
+  float f;
+  memcpy(&f, &b, 4);
+  return f;
+}
+static inline bf16_t f2bf(float f) {  // reference src/fst_engine.cpp:27 (truncating)
+  uint32_t b;
+  memcpy(&b, &f, 4);
+  return (bf16_t)(b >> 16);
+}
+
+void FSTEngine::check(int rc, const char* what) {
+  if (rc != FST_MLA_OK)
+    throw std::runtime_error(std::string(what) + ": " + fst_cuda_mla_last_error());
+}
+
+FSTEngine::FSTEngine(const ModelConfig& cfg) : config_(cfg) {
+  shared_.resize(cfg.n_layers);
+  FstMlaConfig c;
+  memset(&c, 0, sizeof(c));
+  c.preset = cfg.preset;
+  c.hidden = cfg.hidden_dim;
+  c.n_heads = MLA_N_HEADS;
+  c.q_lora = MLA_Q_LORA;
+  c.kv_lora = MLA_KV_LORA;
+  c.qk_nope = 128;
+  c.qk_rope = cfg.rope_dim;
+  c.v_head = 128;
+  c.o_groups = 8;
+  c.o_lora = 1024;
+  c.rope_theta = 10000.0f;
+  c.rms_eps = 1e-6f;
+  // one context serves layers of one RoPE kind; a model mixing plain and YaRN layers uses two
+  c.rope_yarn = !cfg.compress_ratios.empty() && cfg.compress_ratios[0] != 0;
+  c.n_layers = cfg.n_layers;
+  c.page_tokens = cfg.page_tokens;
+  const int pages_per_seq = (cfg.max_seq + cfg.page_tokens - 1) / cfg.page_tokens;
+  c.n_pages = pages_per_seq * cfg.max_seqs;
+  c.max_seqs = cfg.max_seqs;
+  c.max_tokens = cfg.max_tokens;
+  c.device = cfg.device;
+  c.attn_impl = cfg.attn_impl;
+  c.gemm_impl = cfg.gemm_impl;
+  check(fst_cuda_mla_create(&c, &ctx_), "fst_cuda_mla_create");
+  int32_t s = -1;
+  check(fst_cuda_mla_seq_alloc(ctx_, &s), "seq_alloc");
+  seq_ = s;
+}
+
+FSTEngine::~FSTEngine() { fst_cuda_mla_destroy(ctx_); }
+
+void FSTEngine::preload_all_layers() {
+  for (int l = 0; l < config_.n_layers; ++l) {
+    const LayerWeightsC& w = shared_[l];
+    FstMlaWeights fw;
+    memset(&fw, 0, sizeof(fw));
+    auto p = [](const std::vector<bf16_t>& v) { return v.empty() ? nullptr : v.data(); };
+    fw.wq_a = p(w.wq_a);
+    fw.wq_b = p(w.wq_b);
+    fw.wkv_a = p(w.wkv);
+    fw.wkv_b = p(w.wkv_b);
+    fw.wo_a = p(w.wo_a);
+    fw.wo_b = p(w.wo_b);
+    fw.q_norm = p(w.q_norm);
+    fw.kv_norm = p(w.kv_norm);
+    fw.attn_sinks = w.attn_sinks.empty() ? nullptr : w.attn_sinks.data();
+    check(fst_cuda_mla_set_layer_weights(ctx_, l, &fw), "set_layer_weights");
+  }
+}
+
+void FSTEngine::process_mla(int lid, bf16_t* h, int M) {
+  if (seq_pos_ + M > config_.max_seq)  // assert(seq_pos_ + M <= config_.max_seq), reference 3327
+    throw std::runtime_error("process_mla: seq_pos_ + M exceeds max_seq");
+  const int32_t seq = seq_, pos = seq_pos_, q = M;
+  check(fst_cuda_mla_forward(ctx_, lid, h, h, &seq, &pos, &q, 1, is_prefill_ ? 1 : 0), "process_mla");
+}
+
+void FSTEngine::process_mla_batch(int lid, bf16_t* h, const int* seq_ids, const int* pos0, const int* q_lens, int B,
+                                  bool causal) {
+  for (int b = 0; b < B; ++b)
+    if (pos0[b] + q_lens[b] > config_.max_seq) throw std::runtime_error("process_mla_batch: a sequence exceeds max_seq");
+  check(fst_cuda_mla_forward(ctx_, lid, h, h, seq_ids, pos0, q_lens, B, causal ? 1 : 0), "process_mla_batch");
+}
+
+void FSTEngine::reset_session() {
+  check(fst_cuda_mla_reset(ctx_), "reset");
+  int32_t s = -1;
+  check(fst_cuda_mla_seq_alloc(ctx_, &s), "seq_alloc");
+  seq_ = s;
+  seq_pos_ = 0;
+  is_prefill_ = true;
+}
+
+void FSTEngine::rollback(int keep_len) {
+  int32_t len = 0;
+  check(fst_cuda_mla_seq_len(ctx_, seq_, &len), "seq_len");
+  if (keep_len < len) check(fst_cuda_mla_seq_truncate(ctx_, seq_, keep_len), "seq_truncate");
+  seq_pos_ = keep_len;
+}
+
+int FSTEngine::new_sequence() {
+  int32_t s = -1;
+  check(fst_cuda_mla_seq_alloc(ctx_, &s), "seq_alloc");
+  return s;
+}
+
+void FSTEngine::free_sequence(int seq) { check(fst_cuda_mla_seq_free(ctx_, seq), "seq_free"); }
+
+std::vector<RandmatResult> FSTEngine::randmat_test() {
+  // same generator, shapes and reference computation as the engine's probe (592-640)
+  uint64_t st = 0x123456789abcdefULL;
+  auto nxt = [&]() -> uint32_t {
+    st ^= st << 13;
+    st ^= st >> 7;
+    st ^= st << 17;
+    return (uint32_t)(st >> 32);
+  };
+  auto rbf = [&]() -> bf16_t { return f2bf(((float)(nxt() & 0xffff) / 65535.0f) * 2.0f - 1.0f); };
+  struct Probe { const char* name; int K, N; };
+  const Probe probes[] = {{"ffn_gate/up", 4096, 2048}, {"ffn_down", 2048, 2048}, {"qc (wq_a)", 4096, 1024},
+                          {"wqb (wq_b)", 1024, 2048},  {"ob (wo_b)", 8192, 2048}, {"qck (full K)", 4096, 1024}};
+  const int M = 16;
+  std::vector<RandmatResult> out;
+  for (const auto& p : probes) {
+    std::vector<bf16_t> A((size_t)M * p.K), B((size_t)p.N * p.K), C((size_t)M * p.N, 0);
+    for (auto& v : A) v = rbf();
+    for (auto& v : B) v = rbf();
+    check(fst_cuda_mla_gemm(ctx_, C.data(), A.data(), B.data(), M, p.N, p.K, 0), "gemm");
+    double dot = 0, nn = 0, nr = 0, me = 0;
+    for (int m = 0; m < M; ++m)
+      for (int n = 0; n < p.N; ++n) {
+        double acc = 0;
+        for (int k = 0; k < p.K; ++k) acc += (double)bf16f(A[(size_t)m * p.K + k]) * (double)bf16f(B[(size_t)n * p.K + k]);
+        const double got = bf16f(C[(size_t)m * p.N + n]);
+        dot += got * acc;
+        nn += got * got;
+        nr += acc * acc;
+        me = std::max(me, std::fabs(got - acc));
+      }
+    out.push_back({p.name, M, p.K, p.N, dot / (std::sqrt(nn) * std::sqrt(nr) + 1e-30), std::sqrt(nn / nr), me});
+  }
+  return out;
+}

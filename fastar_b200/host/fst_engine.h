@@ -1,0 +1,104 @@
+// Host side of the MLA path, shaped like the reference engine (include/fst_engine.h) so that
+// process_mla is a drop-in: the same entry point, the same implicit state (seq_pos_,
+// is_prefill_, shared_[lid]), the same in-place contract on `h`.  What changes underneath is
+// what the reference did with NPU dispatches and XRT buffer objects: weights, the latent cache
+// (now paged, device resident) and every intermediate live on the GPU behind the C ABI of
+// include/fst_cuda_mla.h.  Only the MLA subset of the engine exists here; the MoE / expert
+// pager / sampler / tokenizer sides are not part of this library.
+#pragma once
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "fst_cuda_mla.h"
+
+typedef uint16_t bf16_t;  // reference include/fst_engine.h:16
+
+// reference include/fst_engine.h:92-95
+constexpr int MLA_Q_LORA = 1024, MLA_KV_LORA = 512;
+constexpr int MLA_N_HEADS = 64, MLA_HEAD_DIM = 512, MLA_Q_FLAT = MLA_N_HEADS * MLA_HEAD_DIM;
+constexpr int MLA_ROPE_DIM = 64;
+
+// reference ModelConfig (include/fst_engine.h:127-139), MLA members plus the paged-cache sizes.
+struct ModelConfig {
+  int n_layers = 1;
+  int hidden_dim = 4096;
+  int max_seq = 128;        // capacity of one sequence (the reference's flat cache length)
+  int rope_dim = MLA_ROPE_DIM;
+  std::vector<int> compress_ratios;  // per layer; non-zero selects the YaRN RoPE table (1979-1982)
+  // what this build adds
+  int preset = FST_MLA_PRESET_FASTAR_V4;  // FST_MLA_PRESET_BASELINE for the 576-wide form
+  int page_tokens = 64;
+  int max_seqs = 1;         // sequences alive at once (batched decode)
+  int max_tokens = 16;      // new tokens per layer call (prefill_tiled feeds 16, src/fst_engine.cpp:2959)
+  int device = 0;
+  int attn_impl = FST_MLA_IMPL_AUTO;
+  int gemm_impl = FST_MLA_IMPL_AUTO;
+};
+
+// reference LayerWeightsC (include/fst_engine.h:165-188), MLA members; bf16 [N_out, K_in].
+struct LayerWeightsC {
+  std::vector<bf16_t> q_norm, kv_norm, wq_a, wq_b, wkv, wo_a, wo_b;
+  std::vector<bf16_t> wkv_b;        // BASELINE preset: per head W_UK rows then W_UV rows
+  std::vector<float> attn_sinks;    // per-head sink logit (empty: 0, src/fst_engine.cpp:3623)
+};
+
+struct RandmatResult {  // one line of randmat_test (src/fst_engine.cpp:586-685)
+  std::string name;
+  int M, K, N;
+  double cosine, norm_ratio, max_abs_err;
+};
+
+class FSTEngine {
+ public:
+  ModelConfig config_;
+  std::vector<LayerWeightsC> shared_;
+
+  // The reference constructor loads a .fst file (src/fst_engine.cpp:1250); model loading is
+  // outside this path, so the caller fills shared_ and calls preload_all_layers().
+  explicit FSTEngine(const ModelConfig& cfg);
+  ~FSTEngine();
+  FSTEngine(const FSTEngine&) = delete;
+  FSTEngine& operator=(const FSTEngine&) = delete;
+
+  // Upload shared_[*] to the device (preload_all_layers, src/fst_engine.cpp:1152-1197).
+  void preload_all_layers();
+
+  // The hot path (src/fst_engine.cpp:3320-3890): h[M, hidden] attn-normed rows at positions
+  // seq_pos_ .. seq_pos_+M-1 of the current sequence, overwritten with the attention output.
+  // Causal among the M rows when is_prefill_ (3626).  Throws std::runtime_error on failure;
+  // seq_pos_ + M > max_seq is an error (the reference asserts, 3327).
+  void process_mla(int lid, bf16_t* h, int M);
+
+  // Batched sibling: B sequences, q_lens[b] new rows each at pos0[b]; h is [sum q_lens, hidden].
+  void process_mla_batch(int lid, bf16_t* h, const int* seq_ids, const int* pos0, const int* q_lens, int B,
+                         bool causal);
+
+  // Session state (reset_session 2992-3012; seq_pos_ advanced by the caller, 2972 / 6262).
+  void reset_session();
+  int seq_pos() const { return seq_pos_; }
+  void set_seq_pos(int p) { seq_pos_ = p; }
+  void advance(int n) { seq_pos_ += n; }
+  void set_prefill(bool p) { is_prefill_ = p; }
+  bool is_prefill() const { return is_prefill_; }
+  // Speculative-decoding rollback (6132-6147): forget rows >= keep_len of the current sequence.
+  void rollback(int keep_len);
+
+  // Extra sequences for batched decode.
+  int new_sequence();
+  void free_sequence(int seq);
+  int current_sequence() const { return seq_; }
+
+  // Random-matrix probe of the GEMM tile engine (randmat_test, 586-685): xorshift-seeded
+  // uniform [-1, 1] bf16 A[16, K], B[N, K] against a double-precision CPU product.
+  std::vector<RandmatResult> randmat_test();
+
+  FstMlaCtx* ctx() { return ctx_; }
+
+ private:
+  FstMlaCtx* ctx_ = nullptr;
+  int seq_ = -1;
+  int seq_pos_ = 0;
+  bool is_prefill_ = true;
+  void check(int rc, const char* what);
+};

@@ -94,3 +94,17 @@ def test_kv_slices_are_page_aligned_and_cover():
             assert a % 64 == 0 and b % 64 == 0
     assert parallel.owner_of_row(131072, 131072, 8) == 7
     assert parallel.owner_of_row(0, 131072, 8) == 0
+
+
+def test_engine_library_loads_and_exports_its_entry_points():
+    lib = ctypes.CDLL(os.path.join(os.path.dirname(mla.LIB_PATH), "libfst_engine.so"))
+    for n in ("fst_engine_create", "fst_engine_destroy", "fst_engine_set_weight", "fst_engine_preload",
+              "fst_engine_process_mla", "fst_engine_process_mla_batch", "fst_engine_reset_session",
+              "fst_engine_rollback", "fst_engine_randmat_test", "fst_engine_last_error"):
+        assert hasattr(lib, n), n
+    import torch
+    if not torch.cuda.is_available():
+        lib.fst_engine_create.restype = ctypes.c_void_p
+        lib.fst_engine_last_error.restype = ctypes.c_char_p
+        assert not lib.fst_engine_create(1, 1, 128, 1, 16, 0, 0, 0)
+        assert b"no CPU fallback" in lib.fst_engine_last_error()
