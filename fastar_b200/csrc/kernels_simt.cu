@@ -359,92 +359,126 @@ __device__ __forceinline__ void finish_row(float* s_out, bf16* o_row, const floa
   for (int j = threadIdx.x; j < d_v; j += blockDim.x) o_row[j] = f2bf(s_out[j]);
 }
 
-__global__ void __launch_bounds__(128) k_merge(MergeArgs a) {
-  __shared__ float s_out[1024];
-  const int r = blockIdx.x, t = r / a.H, h = r % a.H;
-  const int p0 = a.tok_part[t], p1 = a.tok_part[t + 1];
-  const bool sink = a.sinks != nullptr;
-  float M = sink ? a.sinks[h] : -INFINITY;
-  for (int p = p0; p < p1; ++p) M = fmaxf(M, a.part_m[(long long)p * a.H + h]);
-  float den = sink ? expf(a.sinks[h] - M) : 0.0f;
-  float acc[8];
+// One block per query row (token, head).  8 warps take the parts round-robin, a lane owns
+// columns lane*4 + 128*j; the warps' sums are then added in warp order (deterministic).
+constexpr int MERGE_THREADS = 256;
+
+struct PartRef {
+  float m, l;
+  const float* o;
+};
+
+template <class GetPart>
+__device__ __forceinline__ void merge_row(int n_parts, GetPart get, const float* sinks, int h, int d_v,
+                                          float* s_acc /* [8][512] */, float* s_red /* [32] */, float& M_out,
+                                          float& den_out) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool sink = sinks != nullptr;
+  // reference maximum over all parts (and the sink)
+  float M = sink ? sinks[h] : -INFINITY;
+  for (int p = threadIdx.x; p < n_parts; p += MERGE_THREADS) M = fmaxf(M, get(p).m);
+  M = warp_max(M);
+  if (lane == 0) s_red[warp] = M;
+  __syncthreads();
+  M = s_red[0];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
-  for (int p = p0; p < p1; ++p) {
-    const float mp = a.part_m[(long long)p * a.H + h];
-    if (mp == -INFINITY) continue;
-    const float w = expf(mp - M);
-    den += w * a.part_l[(long long)p * a.H + h];
-    const float* o = a.part_o + ((long long)p * a.H + h) * a.d_v;
+  for (int w = 1; w < 8; ++w) M = fmaxf(M, s_red[w]);
+  __syncthreads();
+  float acc[16];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const int j = threadIdx.x + c * 128;
-      if (j < a.d_v) acc[c] = fmaf(w, o[j], acc[c]);
+  for (int c = 0; c < 16; ++c) acc[c] = 0.0f;
+  float den = 0.0f;
+  for (int p = warp; p < n_parts; p += 8) {
+    const PartRef pr = get(p);
+    if (pr.m == -INFINITY) continue;
+    const float w = expf(pr.m - M);
+    den += w * pr.l;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = lane * 4 + 128 * j;
+      if (col < d_v) {
+        // 8-byte loads: a gathered partial row starts 8 bytes into its (max, sum, O) record
+        const float2 v0 = *reinterpret_cast<const float2*>(pr.o + col);
+        const float2 v1 = *reinterpret_cast<const float2*>(pr.o + col + 2);
+        acc[4 * j] = fmaf(w, v0.x, acc[4 * j]);
+        acc[4 * j + 1] = fmaf(w, v0.y, acc[4 * j + 1]);
+        acc[4 * j + 2] = fmaf(w, v1.x, acc[4 * j + 2]);
+        acc[4 * j + 3] = fmaf(w, v1.y, acc[4 * j + 3]);
+      }
     }
   }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int col = lane * 4 + 128 * j;
+    if (col < d_v)
+      *reinterpret_cast<float4*>(s_acc + warp * 512 + col) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+  }
+  if (lane == 0) s_red[8 + warp] = den;
+  __syncthreads();
+  den = sink ? expf(sinks[h] - M) : 0.0f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) den += s_red[8 + w];
+  // column sums over the warps, in warp order, left in s_acc[0][*]
+  for (int col = threadIdx.x; col < d_v; col += MERGE_THREADS) {
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) v += s_acc[w * 512 + col];
+    s_acc[col] = v;  // only this thread reads column `col` of the other warps' rows
+  }
+  __syncthreads();
+  M_out = M;
+  den_out = den;
+}
+
+__global__ void __launch_bounds__(MERGE_THREADS) k_merge(MergeArgs a) {
+  __shared__ __align__(16) float s_acc[8 * 512];
+  __shared__ float s_red[32];
+  const int r = blockIdx.x, t = r / a.H, h = r % a.H;
+  const int p0 = a.tok_part[t], n_parts = a.tok_part[t + 1] - p0;
+  auto get = [&](int p) {
+    const long long i = (long long)(p0 + p) * a.H + h;
+    return PartRef{a.part_m[i], a.part_l[i], a.part_o + i * a.d_v};
+  };
+  float M, den;
+  merge_row(n_parts, get, a.sinks, h, a.d_v, s_acc, s_red, M, den);
   if (a.mode == 1) {
     float* o = a.rank_partial + (long long)r * (2 + a.d_v);
     if (threadIdx.x == 0) {
       o[0] = M;
       o[1] = den;
     }
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const int j = threadIdx.x + c * 128;
-      if (j < a.d_v) o[2 + j] = acc[c];
-    }
+    for (int j = threadIdx.x; j < a.d_v; j += MERGE_THREADS) o[2 + j] = s_acc[j];
     return;
   }
   const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const int j = threadIdx.x + c * 128;
-    if (j < a.d_v) s_out[j] = rbf(acc[c] * inv);
-  }
-  finish_row(s_out, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope,
-             a.inv_rope);
+  for (int j = threadIdx.x; j < a.d_v; j += MERGE_THREADS) s_acc[j] = rbf(s_acc[j] * inv);
+  finish_row(s_acc, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope, a.inv_rope);
 }
 
 void launch_merge(const MergeArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
-  k_merge<<<a.T * a.H, 128, 0, st>>>(a);
+  k_merge<<<a.T * a.H, MERGE_THREADS, 0, st>>>(a);
 }
 
-__global__ void __launch_bounds__(128) k_merge_gathered(MergeGatheredArgs a) {
-  __shared__ float s_out[1024];
+__global__ void __launch_bounds__(MERGE_THREADS) k_merge_gathered(MergeGatheredArgs a) {
+  __shared__ __align__(16) float s_acc[8 * 512];
+  __shared__ float s_red[32];
   const int r = blockIdx.x, t = r / a.H, h = r % a.H;
   const long long rows = (long long)a.T * a.H, w_row = 2 + a.d_v;
-  const bool sink = a.sinks != nullptr;
-  float M = sink ? a.sinks[h] : -INFINITY;
-  for (int p = 0; p < a.n_parts; ++p) M = fmaxf(M, a.parts[(p * rows + r) * w_row]);
-  float den = sink ? expf(a.sinks[h] - M) : 0.0f;
-  float acc[8];
-#pragma unroll
-  for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
-  for (int p = 0; p < a.n_parts; ++p) {
+  auto get = [&](int p) {
     const float* pr = a.parts + (p * rows + r) * w_row;
-    if (pr[0] == -INFINITY) continue;
-    const float w = expf(pr[0] - M);
-    den += w * pr[1];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const int j = threadIdx.x + c * 128;
-      if (j < a.d_v) acc[c] = fmaf(w, pr[2 + j], acc[c]);
-    }
-  }
+    return PartRef{pr[0], pr[1], pr + 2};
+  };
+  float M, den;
+  merge_row(a.n_parts, get, a.sinks, h, a.d_v, s_acc, s_red, M, den);
   const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const int j = threadIdx.x + c * 128;
-    if (j < a.d_v) s_out[j] = rbf(acc[c] * inv);
-  }
-  finish_row(s_out, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope,
-             a.inv_rope);
+  for (int j = threadIdx.x; j < a.d_v; j += MERGE_THREADS) s_acc[j] = rbf(s_acc[j] * inv);
+  finish_row(s_acc, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope, a.inv_rope);
 }
 
 void launch_merge_gathered(const MergeGatheredArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
-  k_merge_gathered<<<a.T * a.H, 128, 0, st>>>(a);
+  k_merge_gathered<<<a.T * a.H, MERGE_THREADS, 0, st>>>(a);
 }
 
 // Zero whole cache rows (speculative rollback, reference src/fst_engine.cpp:6132-6147).
