@@ -109,6 +109,7 @@ def load_library() -> C.CDLL:
     L.fst_cuda_mla_set_profiling.argtypes = [vp, C.c_int]
     L.fst_cuda_mla_kernel_times.argtypes = [vp, C.POINTER(C.c_float), i32p]
     L.fst_cuda_mla_plan_info.argtypes = [vp, i32p, i32p, C.POINTER(i64)]
+    L.fst_cuda_mla_attention_noalloc.argtypes = [vp, vp, i32, i32, i32, i32, C.c_float, vp, vp]
     _lib = L
     return L
 
@@ -341,6 +342,14 @@ class MlaContext:
         n = (C.c_int32 * len(KERNEL_NAMES))()
         self._check(self.lib.fst_cuda_mla_kernel_times(self._h, ms, n))
         return {k: (ms[i], n[i]) for i, k in enumerate(KERNEL_NAMES)}
+
+
+def attention_noalloc(d_q_eff: int, d_cache: int, n_rows: int, n_heads: int, d_qk: int, d_v: int, scale: float,
+                      d_o_lat: int, stream: int = 0) -> int:
+    """Decode attention of one query token over a contiguous device cache, for callers that must
+    not allocate (see include/fst_cuda_mla.h).  Device pointers as integers; returns the status."""
+    return load_library().fst_cuda_mla_attention_noalloc(C.c_void_p(d_q_eff), C.c_void_p(d_cache), n_rows, n_heads,
+                                                         d_qk, d_v, scale, C.c_void_p(d_o_lat), C.c_void_p(stream))
 
 
 def default_scale(cfg: Config) -> float:

@@ -213,6 +213,31 @@ int fst_cuda_mla_kernel_times(FstMlaCtx* ctx, float* ms_out, int32_t* n_out);
 /* Schedule of the current plan: partial count, CTAs of the attention kernel, cached rows read. */
 int fst_cuda_mla_plan_info(FstMlaCtx* ctx, int32_t* n_partials, int32_t* n_ctas, int64_t* kv_rows);
 
+/* ---- decode attention without any allocation -------------------------------------------- */
+/* No counterpart in the reference.  For callers that cannot allocate device memory at the
+ * moment they need attention: a serving process whose device memory was handed out in full at
+ * start-up, a latency-critical callback where cudaMalloc (which synchronises the device) is not
+ * allowed, a plugin that only receives device pointers.  It needs no FstMlaCtx and calls no
+ * cudaMalloc / cudaFree nor any allocating library routine.
+ *
+ * One query token: d_q_eff device bf16 [n_heads, d_qk]; d_cache device bf16 [n_rows, d_qk],
+ * contiguous rows, keys = row[:d_qk], values = row[:d_v]; d_o_lat device bf16 [n_heads, d_v]
+ * = softmax(scale * q K^T) V, no sink.  Both inputs 16-byte aligned.  Work is enqueued on
+ * cuda_stream (NULL: default stream) of the current device; the call does not synchronise.
+ *
+ * The split-KV partials live in a fixed array inside the library image (about 4 MiB, held by
+ * every GPU that loads the library until the process exits), hence the limits: n_rows <= 65536,
+ * n_heads <= 64, d_qk <= 576 (multiple of 8), d_v <= 512 (multiple of 64, <= d_qk).  Anything
+ * larger returns FST_MLA_ERR_CAPACITY (a line on stderr says why); use the context API then.
+ * All calls share that one array: it keeps the previous call's contents, every call rewrites
+ * whatever it later reads (nothing has to start at zero), and two calls that overlap on the
+ * GPU -- different streams, or different host threads -- race on it.  Serialise them.
+ * The first call on a device looks up the array's device address; make that first call
+ * before any stream capture begins. */
+int fst_cuda_mla_attention_noalloc(const void* d_q_eff, const void* d_cache, int32_t n_rows, int32_t n_heads,
+                                   int32_t d_qk, int32_t d_v, float softmax_scale, void* d_o_lat,
+                                   void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
