@@ -78,6 +78,7 @@ struct MergeArgs {
   bf16* o_lat;              // [T * H, d_v]                 (mode 0)
   float* rank_partial;      // [T * H, 2 + d_v] fp32        (mode 1, no sink)
   int T, H, d_v, rope, inv_rope, mode;
+  int threads;              // 128: rows have few parts (a thread per 4 columns); otherwise 256 (8 warps share the parts)
 };
 void launch_merge(const MergeArgs& a, cudaStream_t st);
 

@@ -361,7 +361,7 @@ __device__ __forceinline__ void finish_row(float* s_out, bf16* o_row, const floa
 
 // One block per query row (token, head).  8 warps take the parts round-robin, a lane owns
 // columns lane*4 + 128*j; the warps' sums are then added in warp order (deterministic).
-constexpr int MERGE_THREADS = 256;
+constexpr int MERGE_THREADS = 256;  // rows with few parts use 128 threads, one per 4 columns
 
 struct PartRef {
   float m, l;
@@ -372,23 +372,50 @@ template <class GetPart>
 __device__ __forceinline__ void merge_row(int n_parts, GetPart get, const float* sinks, int h, int d_v,
                                           float* s_acc /* [8][512] */, float* s_red /* [32] */, float& M_out,
                                           float& den_out) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (blockDim.x == 128) {
+    // few parts per row: every thread walks all parts for its own 4 columns, no exchange
+    const bool sk = sinks != nullptr;
+    float M = sk ? sinks[h] : -INFINITY;
+    for (int p = 0; p < n_parts; ++p) M = fmaxf(M, get(p).m);
+    float den = sk ? expf(sinks[h] - M) : 0.0f;
+    float a4[4] = {0.f, 0.f, 0.f, 0.f};
+    const int col = threadIdx.x * 4;
+    for (int p = 0; p < n_parts; ++p) {
+      const PartRef pr = get(p);
+      if (pr.m == -INFINITY) continue;
+      const float w = expf(pr.m - M);
+      den += w * pr.l;
+      if (col < d_v) {
+        const float2 v0 = *reinterpret_cast<const float2*>(pr.o + col);
+        const float2 v1 = *reinterpret_cast<const float2*>(pr.o + col + 2);
+        a4[0] = fmaf(w, v0.x, a4[0]);
+        a4[1] = fmaf(w, v0.y, a4[1]);
+        a4[2] = fmaf(w, v1.x, a4[2]);
+        a4[3] = fmaf(w, v1.y, a4[3]);
+      }
+    }
+    if (col < d_v) *reinterpret_cast<float4*>(s_acc + col) = make_float4(a4[0], a4[1], a4[2], a4[3]);
+    __syncthreads();
+    M_out = M;
+    den_out = den;
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const bool sink = sinks != nullptr;
   // reference maximum over all parts (and the sink)
   float M = sink ? sinks[h] : -INFINITY;
-  for (int p = threadIdx.x; p < n_parts; p += MERGE_THREADS) M = fmaxf(M, get(p).m);
+  for (int p = threadIdx.x; p < n_parts; p += blockDim.x) M = fmaxf(M, get(p).m);
   M = warp_max(M);
   if (lane == 0) s_red[warp] = M;
   __syncthreads();
   M = s_red[0];
-#pragma unroll
-  for (int w = 1; w < 8; ++w) M = fmaxf(M, s_red[w]);
+  for (int w = 1; w < nw; ++w) M = fmaxf(M, s_red[w]);
   __syncthreads();
   float acc[16];
 #pragma unroll
   for (int c = 0; c < 16; ++c) acc[c] = 0.0f;
   float den = 0.0f;
-  for (int p = warp; p < n_parts; p += 8) {
+  for (int p = warp; p < n_parts; p += nw) {
     const PartRef pr = get(p);
     if (pr.m == -INFINITY) continue;
     const float w = expf(pr.m - M);
@@ -416,13 +443,11 @@ __device__ __forceinline__ void merge_row(int n_parts, GetPart get, const float*
   if (lane == 0) s_red[8 + warp] = den;
   __syncthreads();
   den = sink ? expf(sinks[h] - M) : 0.0f;
-#pragma unroll
-  for (int w = 0; w < 8; ++w) den += s_red[8 + w];
+  for (int w = 0; w < nw; ++w) den += s_red[8 + w];
   // column sums over the warps, in warp order, left in s_acc[0][*]
-  for (int col = threadIdx.x; col < d_v; col += MERGE_THREADS) {
+  for (int col = threadIdx.x; col < d_v; col += blockDim.x) {
     float v = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) v += s_acc[w * 512 + col];
+    for (int w = 0; w < nw; ++w) v += s_acc[w * 512 + col];
     s_acc[col] = v;  // only this thread reads column `col` of the other warps' rows
   }
   __syncthreads();
@@ -447,17 +472,17 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge(MergeArgs a) {
       o[0] = M;
       o[1] = den;
     }
-    for (int j = threadIdx.x; j < a.d_v; j += MERGE_THREADS) o[2 + j] = s_acc[j];
+    for (int j = threadIdx.x; j < a.d_v; j += blockDim.x) o[2 + j] = s_acc[j];
     return;
   }
   const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
-  for (int j = threadIdx.x; j < a.d_v; j += MERGE_THREADS) s_acc[j] = rbf(s_acc[j] * inv);
+  for (int j = threadIdx.x; j < a.d_v; j += blockDim.x) s_acc[j] = rbf(s_acc[j] * inv);
   finish_row(s_acc, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope, a.inv_rope);
 }
 
 void launch_merge(const MergeArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
-  k_merge<<<a.T * a.H, MERGE_THREADS, 0, st>>>(a);
+  k_merge<<<a.T * a.H, a.threads == 128 ? 128 : MERGE_THREADS, 0, st>>>(a);
 }
 
 __global__ void __launch_bounds__(MERGE_THREADS) k_merge_gathered(MergeGatheredArgs a) {
@@ -472,13 +497,13 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge_gathered(MergeGatheredA
   float M, den;
   merge_row(a.n_parts, get, a.sinks, h, a.d_v, s_acc, s_red, M, den);
   const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
-  for (int j = threadIdx.x; j < a.d_v; j += MERGE_THREADS) s_acc[j] = rbf(s_acc[j] * inv);
+  for (int j = threadIdx.x; j < a.d_v; j += blockDim.x) s_acc[j] = rbf(s_acc[j] * inv);
   finish_row(s_acc, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope, a.inv_rope);
 }
 
 void launch_merge_gathered(const MergeGatheredArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
-  k_merge_gathered<<<a.T * a.H, MERGE_THREADS, 0, st>>>(a);
+  k_merge_gathered<<<a.T * a.H, a.n_parts <= 4 ? 128 : MERGE_THREADS, 0, st>>>(a);
 }
 
 // Zero whole cache rows (speculative rollback, reference src/fst_engine.cpp:6132-6147).

@@ -4,6 +4,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -85,6 +86,11 @@ struct FstMlaCtx {
   int32_t *d_tables = nullptr, *d_tok_table = nullptr, *d_cta_seg = nullptr, *d_tok_part = nullptr;
   AttnSeg* d_segs = nullptr;
   int tables_cap = 0, segs_cap = 0;
+  // the plan arrays above are slices of one device blob, filled through one pinned host blob
+  // with a single copy per plan
+  unsigned char *d_plan = nullptr, *h_plan = nullptr;
+  size_t plan_cap = 0;
+  cudaEvent_t plan_ev = nullptr;
   // plan (host)
   bool planned = false;
   int T = 0, n_segs = 0, n_parts = 0, n_ctas = 0;
@@ -373,6 +379,7 @@ int run_merge_local(FstMlaCtx* c, int lid, int mode, float* rank_partial) {
   m.sinks = (d.v4 && mode == 0) ? c->layers[lid].sinks : nullptr;
   m.lut = c->d_lut; m.o_lat = c->d_olat; m.rank_partial = rank_partial;
   m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope; m.inv_rope = d.v4 ? 1 : 0; m.mode = mode;
+  m.threads = c->n_parts <= 6 * c->T ? 128 : 256;
   launch_merge(m, c->stream);
   c->launches += 1;
   return FST_MLA_OK;
@@ -462,15 +469,16 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
   if (!rc) rc = dev_alloc(&x->d_part_m, (size_t)x->max_parts * d.H);
   if (!rc) rc = dev_alloc(&x->d_part_l, (size_t)x->max_parts * d.H);
   if (!rc) rc = dev_alloc(&x->d_part_o, (size_t)x->max_parts * d.H * d.d_v);
-  if (!rc) rc = dev_alloc(&x->d_lut, T * d.rope);
-  if (!rc) rc = dev_alloc(&x->d_dst, T);
-  if (!rc) rc = dev_alloc(&x->d_tok_table, T);
-  if (!rc) rc = dev_alloc(&x->d_tok_part, T + 1);
-  if (!rc) rc = dev_alloc(&x->d_cta_seg, (size_t)x->n_sm + 1);
   x->segs_cap = x->max_parts;
-  if (!rc) rc = dev_alloc(&x->d_segs, (size_t)x->segs_cap);
   x->tables_cap = c.n_pages + c.max_seqs;
-  if (!rc) rc = dev_alloc(&x->d_tables, (size_t)x->tables_cap);
+  x->plan_cap = T * d.rope * sizeof(float) + T * sizeof(long long) + (2 * T + 1) * sizeof(int32_t) +
+                ((size_t)x->n_sm + 1) * sizeof(int32_t) + (size_t)x->segs_cap * sizeof(AttnSeg) +
+                (size_t)x->tables_cap * sizeof(int32_t) + 8 * 256;
+  if (!rc) rc = dev_alloc(&x->d_plan, x->plan_cap);
+  if (!rc && cudaHostAlloc((void**)&x->h_plan, x->plan_cap, cudaHostAllocDefault) != cudaSuccess)
+    rc = fail(FST_MLA_ERR_CUDA, "cudaHostAlloc(plan) failed");
+  if (!rc && cudaEventCreateWithFlags(&x->plan_ev, cudaEventDisableTiming) != cudaSuccess)
+    rc = fail(FST_MLA_ERR_CUDA, "cudaEventCreate failed");
   if (!rc) rc = dev_alloc(&x->d_status, 1);
   if (!rc && cudaMemset(x->d_status, 0, sizeof(int)) != cudaSuccess) rc = fail(FST_MLA_ERR_CUDA, "cudaMemset failed");
   if (!rc && cudaHostAlloc((void**)&x->h_pinned, T * d.hidden * sizeof(uint16_t), cudaHostAllocDefault) != cudaSuccess)
@@ -497,8 +505,9 @@ void fst_cuda_mla_destroy(FstMlaCtx* c) {
   cudaFree(c->d_h); cudaFree(c->d_cmp); cudaFree(c->d_qc); cudaFree(c->d_kvnew); cudaFree(c->d_qfull);
   cudaFree(c->d_qeff); cudaFree(c->d_olat); cudaFree(c->d_low); cudaFree(c->d_out);
   cudaFree(c->d_part_m); cudaFree(c->d_part_l); cudaFree(c->d_part_o);
-  cudaFree(c->d_lut); cudaFree(c->d_dst); cudaFree(c->d_tables); cudaFree(c->d_tok_table);
-  cudaFree(c->d_cta_seg); cudaFree(c->d_tok_part); cudaFree(c->d_segs); cudaFree(c->d_status);
+  cudaFree(c->d_plan); cudaFree(c->d_status);
+  if (c->h_plan) cudaFreeHost(c->h_plan);
+  if (c->plan_ev) cudaEventDestroy(c->plan_ev);
   if (c->h_pinned) cudaFreeHost(c->h_pinned);
   for (auto& es : c->ev_pool)
     for (auto& e : es.ev) cudaEventDestroy(e);
@@ -792,7 +801,12 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
     total_tiles += (kvlen[i] + ATTN_TILE - 1) / ATTN_TILE;
     kv_rows += kvlen[i];
   }
-  const int n_ctas = (int)std::min<long long>(c->n_sm, std::max<long long>(total_tiles, 1));
+  int max_ctas = c->n_sm;
+  if (const char* e = getenv("FST_MLA_MAX_CTAS")) {  // tuning aid: fewer attention CTAs than SMs
+    const int v = atoi(e);
+    if (v > 0 && v < max_ctas) max_ctas = v;
+  }
+  const int n_ctas = (int)std::min<long long>(max_ctas, std::max<long long>(total_tiles, 1));
   std::vector<AttnSeg> segs;
   std::vector<int32_t> cta_seg(n_ctas + 1, 0);
   {
@@ -834,19 +848,27 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
   if ((int)segs.size() > c->segs_cap || (int)segs.size() > c->max_parts)
     return fail(FST_MLA_ERR_CAPACITY, "split schedule overflow");
 
+  // pack everything into the pinned blob (once the previous plan's copy has left it) and
+  // upload it with one copy; the device arrays are slices of the device blob
   cudaStream_t st = c->stream;
-  if (T > 0) {
-    CU(cudaMemcpyAsync(c->d_lut, lut.data(), lut.size() * sizeof(float), cudaMemcpyHostToDevice, st));
-    CU(cudaMemcpyAsync(c->d_dst, dst.data(), T * sizeof(long long), cudaMemcpyHostToDevice, st));
-    CU(cudaMemcpyAsync(c->d_tok_table, tok_table.data(), T * sizeof(int32_t), cudaMemcpyHostToDevice, st));
-  }
-  CU(cudaMemcpyAsync(c->d_tok_part, tok_part.data(), (T + 1) * sizeof(int32_t), cudaMemcpyHostToDevice, st));
-  if (!tables.empty())
-    CU(cudaMemcpyAsync(c->d_tables, tables.data(), tables.size() * sizeof(int32_t), cudaMemcpyHostToDevice, st));
-  if (!segs.empty())
-    CU(cudaMemcpyAsync(c->d_segs, segs.data(), segs.size() * sizeof(AttnSeg), cudaMemcpyHostToDevice, st));
-  CU(cudaMemcpyAsync(c->d_cta_seg, cta_seg.data(), cta_seg.size() * sizeof(int32_t), cudaMemcpyHostToDevice, st));
-  CU(cudaStreamSynchronize(st));  // the host vectors go out of scope
+  CU(cudaEventSynchronize(c->plan_ev));
+  size_t off = 0;
+  auto put = [&](const void* src, size_t bytes) -> unsigned char* {
+    unsigned char* dev = c->d_plan + off;
+    if (bytes) memcpy(c->h_plan + off, src, bytes);
+    off = (off + bytes + 255) & ~(size_t)255;
+    return dev;
+  };
+  c->d_lut = reinterpret_cast<float*>(put(lut.data(), lut.size() * sizeof(float)));
+  c->d_dst = reinterpret_cast<long long*>(put(dst.data(), (size_t)T * sizeof(long long)));
+  c->d_tok_table = reinterpret_cast<int32_t*>(put(tok_table.data(), (size_t)T * sizeof(int32_t)));
+  c->d_tok_part = reinterpret_cast<int32_t*>(put(tok_part.data(), (size_t)(T + 1) * sizeof(int32_t)));
+  c->d_cta_seg = reinterpret_cast<int32_t*>(put(cta_seg.data(), cta_seg.size() * sizeof(int32_t)));
+  c->d_segs = reinterpret_cast<AttnSeg*>(put(segs.data(), segs.size() * sizeof(AttnSeg)));
+  c->d_tables = reinterpret_cast<int32_t*>(put(tables.data(), tables.size() * sizeof(int32_t)));
+  if (off > c->plan_cap) return fail(FST_MLA_ERR_CAPACITY, "plan blob overflow");
+  CU(cudaMemcpyAsync(c->d_plan, c->h_plan, off, cudaMemcpyHostToDevice, st));
+  CU(cudaEventRecord(c->plan_ev, st));
   c->T = (int)T;
   c->n_segs = (int)segs.size();
   c->n_parts = (int)segs.size();

@@ -148,6 +148,7 @@ extern "C" int fst_cuda_mla_attention_noalloc(const void* d_q_eff, const void* d
   m.rope = 0;
   m.inv_rope = 0;
   m.mode = 0;
+  m.threads = 256;
   launch_merge(m, st);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return na_fail(FST_MLA_ERR_CUDA, cudaGetErrorString(e));
