@@ -320,8 +320,6 @@ def main():
     if rank == 0:
         sampler.start()
         time.sleep(0.25)  # nvidia-smi needs a moment to deliver its first sample
-    ctx.set_profiling(True)
-    ctx.kernel_times()  # clear
     n0 = ctx.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -332,6 +330,13 @@ def main():
     barrier()
     ms = max_over_ranks(ev0.elapsed_time(ev1))
     launches = ctx.launch_count() - n0
+    # per-kernel device times: the same K steps once more with a CUDA event between every two
+    # kernels on the context's stream (kept out of the timed region above, where events between
+    # the kernels would undo the overlap of one kernel's prologue with its predecessor's tail)
+    ctx.set_profiling(True)
+    ctx.kernel_times()  # clear
+    for _ in range(a.steps):
+        step_device()
     ktimes = ctx.kernel_times()
     ctx.set_profiling(False)
     # nvidia-smi samples every 100 ms: when the timed region was shorter than that allows, keep
@@ -381,7 +386,8 @@ def main():
                        "l2": "inputs larger than L2 (cache + weights read per step exceed 126 MB)"
                              if kv_bytes + 122e6 > 126e6 else "inputs smaller than L2; no flush",
                        "attn_ctas": info["n_ctas"], "attn_partials": info["n_partials"],
-                       "value_excludes": "per-step plan upload (amortised over the layers of a step)"},
+                       "value_excludes": "per-step plan upload (amortised over the layers of a step)",
+                       "kernel_events": "second pass of the same steps, one CUDA event between kernels"},
             "e2e": {"value": e2e, "unit": "layer-tokens/s", "h2d_bytes_per_step": int(h_host.numel() * 2),
                     "d2h_bytes_per_step": int(out_host.numel() * 2)},
             "gpu_launches": int(launches),

@@ -156,6 +156,10 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = mi->tmem_slot;
+  // everything above overlapped with the tail of the previous kernel; Q_eff and the appended
+  // cache rows are its products
+  pdl_launch();
+  pdl_wait();
 
   if (warp == 0 || warp >= 10) {
     // ---------------- TMA producers ----------------
@@ -476,7 +480,8 @@ cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st) {
       if (e != cudaSuccess) return e;
       set9 = true;
     }
-    k_attn_tc<9><<<a.n_ctas, ATTN_THREADS, Smem<9>::TOTAL, st>>>(tmQ, tmKV, p);
+    e = launch_pdl(k_attn_tc<9>, dim3(a.n_ctas), dim3(ATTN_THREADS), Smem<9>::TOTAL, st, 1, tmQ, tmKV, p);
+    if (e != cudaSuccess) return e;
   } else {
     static bool set8 = false;
     if (!set8) {
@@ -484,7 +489,8 @@ cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st) {
       if (e != cudaSuccess) return e;
       set8 = true;
     }
-    k_attn_tc<8><<<a.n_ctas, ATTN_THREADS, Smem<8>::TOTAL, st>>>(tmQ, tmKV, p);
+    e = launch_pdl(k_attn_tc<8>, dim3(a.n_ctas), dim3(ATTN_THREADS), Smem<8>::TOTAL, st, 1, tmQ, tmKV, p);
+    if (e != cudaSuccess) return e;
   }
   return cudaGetLastError();
 }

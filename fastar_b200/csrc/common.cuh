@@ -35,6 +35,14 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return warp_sum(t);
 }
 
+// Programmatic dependent launch: the kernels of a layer call are launched with programmatic
+// stream serialisation, so a kernel's prologue (barrier set-up, TMEM allocation, loads of
+// weights, which no earlier kernel writes) runs while its predecessor drains.  pdl_launch lets
+// the successor start; pdl_wait blocks until every earlier kernel has completed and its writes
+// are visible -- every thread calls it before it touches anything an earlier kernel produced.
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // One segment of the split-KV schedule: query token `tok` attends to cache rows
 // [kv_begin, kv_end) of its sequence and writes partial slot `part`.
 struct AttnSeg {

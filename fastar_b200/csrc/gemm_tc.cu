@@ -104,10 +104,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     if (lane == 0) {
       tc::tma_prefetch_desc(&tmW);
       tc::tma_prefetch_desc(&tmA);
-      for (int i = 0; i < n_kc; ++i) {
+      auto load_w = [&](int i) {
         const int s = i % p.stages;
-        if (i >= p.stages && !tc::mbar_wait(&empty[s], ((i / p.stages) - 1) & 1, abort_flag, p.d_status, ST_TMA_TIMEOUT))
-          break;
         unsigned char* st = smem + (size_t)s * STAGE_BYTES;
         const int k0 = (kc0 + i) * BK;
         tc::mbar_expect_tx(&full[s], STAGE_BYTES);
@@ -118,10 +116,29 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
         } else {
           tc::tma_load_3d(st, &tmW, &full[s], k0, p.w_swap ? z : n0, p.w_swap ? n0 : z);
         }
-        tc::tma_load_3d(st + W_BYTES, &tmA, &full[s], k0, p.a_swap ? z : m0, p.a_swap ? m0 : z);
+      };
+      auto load_a = [&](int i) {
+        const int s = i % p.stages;
+        tc::tma_load_3d(smem + (size_t)s * STAGE_BYTES + W_BYTES, &tmA, &full[s], (kc0 + i) * BK, p.a_swap ? z : m0,
+                        p.a_swap ? m0 : z);
+      };
+      // Weights are written by no kernel: the first ring of weight tiles is requested while the
+      // previous kernel still runs; the activations are its output and wait for it.
+      const int first = min(n_kc, p.stages);
+      for (int i = 0; i < first; ++i) load_w(i);
+      pdl_launch();
+      pdl_wait();
+      for (int i = 0; i < first; ++i) load_a(i);
+      for (int i = first; i < n_kc; ++i) {
+        if (!tc::mbar_wait(&empty[i % p.stages], ((i / p.stages) - 1) & 1, abort_flag, p.d_status, ST_TMA_TIMEOUT)) break;
+        load_w(i);
+        load_a(i);
       }
+    } else {
+      pdl_wait();
     }
   } else if (warp == 1) {
+    pdl_wait();
     if (lane == 0) {
       constexpr uint32_t idesc = tc::umma_idesc_bf16(W_TILE, NT, W_KN ? 1 : 0, 0);
       // descriptors differ only in the start-address field: keep the rest in registers
@@ -150,6 +167,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     }
   } else {
     // epilogue warps: TMEM lane quadrant = warp % 4; thread = one weight row n
+    pdl_wait();
     const int quad = warp & 3;
     bool ok = n_kc == 0 || tc::mbar_wait(acc_bar, 0, abort_flag, p.d_status, ST_EPI_TIMEOUT);
     ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
@@ -239,19 +257,7 @@ cudaError_t launch_one(const CUtensorMap& tmW, const CUtensorMap& tmA, const Gem
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = p.splits;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, k_gemm_tc<NT, W_KN>, tmW, tmA, p);
+  return launch_pdl(k_gemm_tc<NT, W_KN>, grid, dim3(GEMM_THREADS, 1, 1), smem, st, p.splits, tmW, tmA, p);
 }
 
 }  // namespace

@@ -19,6 +19,8 @@ __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
 // A warp owns a 8 x 4 output tile; its lanes split K in 16-byte pieces.
 template <bool VEC>
 __global__ void __launch_bounds__(128) k_gemm_nk(GemmArgs g) {
+  pdl_launch();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bf16* A = g.A + (long long)blockIdx.z * g.a_bs;
   const bf16* B = g.B + (long long)blockIdx.z * g.b_bs;
@@ -73,6 +75,8 @@ __global__ void __launch_bounds__(128) k_gemm_nk(GemmArgs g) {
 
 // ---- GEMM, B in [K, N] (the b_row_maj operand, reference src/fst_engine.cpp:480) ----
 __global__ void __launch_bounds__(128) k_gemm_kn(GemmArgs g) {
+  pdl_launch();
+  pdl_wait();
   const bf16* A = g.A + (long long)blockIdx.z * g.a_bs;
   const bf16* B = g.B + (long long)blockIdx.z * g.b_bs;
   bf16* C = g.C + (long long)blockIdx.z * g.c_bs;
@@ -97,7 +101,7 @@ void launch_gemm_simt(const GemmArgs& g, cudaStream_t st) {
   if (g.M <= 0 || g.N <= 0 || g.batch <= 0) return;
   if (g.b_kn) {
     dim3 grid((g.N + 127) / 128, (g.M + 7) / 8, g.batch);
-    k_gemm_kn<<<grid, 128, 0, st>>>(g);
+    launch_pdl(k_gemm_kn, grid, dim3(128), 0, st, 1, g);
     return;
   }
   dim3 grid((g.N + 15) / 16, (g.M + 7) / 8, g.batch);
@@ -105,15 +109,17 @@ void launch_gemm_simt(const GemmArgs& g, cudaStream_t st) {
                    g.b_bs % 8 == 0 && (reinterpret_cast<uintptr_t>(g.A) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(g.B) & 15) == 0;
   if (vec)
-    k_gemm_nk<true><<<grid, 128, 0, st>>>(g);
+    launch_pdl(k_gemm_nk<true>, grid, dim3(128), 0, st, 1, g);
   else
-    k_gemm_nk<false><<<grid, 128, 0, st>>>(g);
+    launch_pdl(k_gemm_nk<false>, grid, dim3(128), 0, st, 1, g);
 }
 
 // ---- q_norm / kv_norm / key RoPE / cache append -------------------------------------------
 // Reference src/fst_engine.cpp:3385-3394 (norms), 3504-3517 (RoPE on the key), 3534-3544
 // (cache push).  One block per new token.  RMSNorm follows rms_cpu (89-91).
 __global__ void __launch_bounds__(256) k_norm_append(NormAppendArgs a) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ float s_row[];  // [row]
   __shared__ float scratch[32];
   const int t = blockIdx.x;
@@ -164,7 +170,7 @@ __global__ void __launch_bounds__(256) k_norm_append(NormAppendArgs a) {
 
 void launch_norm_append(const NormAppendArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
-  k_norm_append<<<a.T, 256, a.row * sizeof(float), st>>>(a);
+  launch_pdl(k_norm_append, dim3(a.T), dim3(256), a.row * sizeof(float), st, 1, a);
 }
 
 // ---- query preparation -----------------------------------------------------------------------
@@ -172,6 +178,8 @@ void launch_norm_append(const NormAppendArgs& a, cudaStream_t st) {
 // (rope_qpe_all_heads, reference src/fst_engine.cpp:2025-2058; the absorb GEMM fills the rest).
 // V4: per-head weightless RMSNorm (3487-3495), then the tail rotation (3503).
 __global__ void __launch_bounds__(128) k_q_prep(QPrepArgs a) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float scratch[32];
   __shared__ float s_q[1024];
   const int r = blockIdx.x, t = r / a.H;
@@ -208,7 +216,7 @@ __global__ void __launch_bounds__(128) k_q_prep(QPrepArgs a) {
 
 void launch_q_prep(const QPrepArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
-  k_q_prep<<<a.T * a.H, 128, 0, st>>>(a);
+  launch_pdl(k_q_prep, dim3(a.T * a.H), dim3(128), 0, st, 1, a);
 }
 
 // ---- split-KV attention on CUDA cores -----------------------------------------------------
@@ -220,6 +228,8 @@ constexpr int SIMT_TILE = 32;
 constexpr int SIMT_HPW = 8;  // heads per warp
 
 __global__ void __launch_bounds__(256, 1) k_attn_simt(AttnArgs a) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem[];
   const int stride = a.row * 2 + 16;  // bytes; the 16-byte pad keeps 16-byte loads conflict free
   bf16* s_q = reinterpret_cast<bf16*>(smem);  // [H, d_qk]
@@ -337,7 +347,7 @@ void launch_attn_simt(const AttnArgs& a, cudaStream_t st) {
     cudaFuncSetAttribute(k_attn_simt, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     configured = smem;
   }
-  k_attn_simt<<<a.n_segs, 256, smem, st>>>(a);
+  launch_pdl(k_attn_simt, dim3(a.n_segs), dim3(256), smem, st, 1, a);
 }
 
 // ---- log-sum-exp merge ---------------------------------------------------------------------
@@ -456,6 +466,8 @@ __device__ __forceinline__ void merge_row(int n_parts, GetPart get, const float*
 }
 
 __global__ void __launch_bounds__(MERGE_THREADS) k_merge(MergeArgs a) {
+  pdl_launch();
+  pdl_wait();
   __shared__ __align__(16) float s_acc[8 * 512];
   __shared__ float s_red[32];
   const int r = blockIdx.x, t = r / a.H, h = r % a.H;
@@ -482,10 +494,12 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge(MergeArgs a) {
 
 void launch_merge(const MergeArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
-  k_merge<<<a.T * a.H, a.threads == 128 ? 128 : MERGE_THREADS, 0, st>>>(a);
+  launch_pdl(k_merge, dim3(a.T * a.H), dim3(a.threads == 128 ? 128 : MERGE_THREADS), 0, st, 1, a);
 }
 
 __global__ void __launch_bounds__(MERGE_THREADS) k_merge_gathered(MergeGatheredArgs a) {
+  pdl_launch();
+  pdl_wait();
   __shared__ __align__(16) float s_acc[8 * 512];
   __shared__ float s_red[32];
   const int r = blockIdx.x, t = r / a.H, h = r % a.H;
@@ -503,7 +517,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge_gathered(MergeGatheredA
 
 void launch_merge_gathered(const MergeGatheredArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
-  k_merge_gathered<<<a.T * a.H, a.n_parts <= 4 ? 128 : MERGE_THREADS, 0, st>>>(a);
+  launch_pdl(k_merge_gathered, dim3(a.T * a.H), dim3(a.n_parts <= 4 ? 128 : MERGE_THREADS), 0, st, 1, a);
 }
 
 // Zero whole cache rows (speculative rollback, reference src/fst_engine.cpp:6132-6147).
