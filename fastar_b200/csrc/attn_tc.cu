@@ -66,8 +66,13 @@ struct AttnTcParams {
 // Phase timestamps (SM clock) of CTA 0, for tuning builds only: [tile][event].
 __device__ long long g_attn_trace[64 * 16];
 #define TRACE(tile, ev) do { if (blockIdx.x == 0 && (tile) < 64) g_attn_trace[(tile) * 16 + (ev)] = clock64(); } while (0)
+// Per-CTA summary: [cta][0..7] = global ns at entry, after the dependency wait, at exit; segments; SM clock at entry, exit.
+__device__ long long g_attn_cta[256 * 8];
+__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define CTA_TRACE(ev, val) do { if (threadIdx.x == 0 && blockIdx.x < 256) g_attn_cta[blockIdx.x * 8 + (ev)] = (val); } while (0)
 #else
 #define TRACE(tile, ev) do { } while (0)
+#define CTA_TRACE(ev, val) do { } while (0)
 #endif
 
 template <int NCH>
@@ -137,6 +142,11 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seg0 = p.cta_seg[blockIdx.x], seg1 = p.cta_seg[blockIdx.x + 1];
+#ifdef FST_ATTN_TRACE
+  CTA_TRACE(0, gtime());
+  CTA_TRACE(4, clock64());
+  CTA_TRACE(3, (long long)(seg1 - seg0));
+#endif
 
   if (threadIdx.x == 0) {
     tc::mbar_init(&mi->q_full, 1);
@@ -160,6 +170,9 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   // cache rows are its products
   pdl_launch();
   pdl_wait();
+#ifdef FST_ATTN_TRACE
+  CTA_TRACE(1, gtime());
+#endif
 
   if (warp == 0 || warp >= 10) {
     // ---------------- TMA producers ----------------
@@ -429,6 +442,10 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 
   tc::tc_fence_before();
   __syncthreads();
+#ifdef FST_ATTN_TRACE
+  CTA_TRACE(2, gtime());
+  CTA_TRACE(5, clock64());
+#endif
   if (*abort_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies and MMAs in flight settle
   }
@@ -443,6 +460,9 @@ k_attn_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 #ifdef FST_ATTN_TRACE
 extern "C" int fst_debug_read_attn_trace(long long* out) {
   return (int)cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(long long) * 64 * 16);
+}
+extern "C" int fst_debug_read_attn_cta(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_attn_cta, sizeof(long long) * 256 * 8);
 }
 #endif
 

@@ -298,7 +298,10 @@ int run_attention(FstMlaCtx* c, int lid, const bf16* q_eff) {
   if (c->cfg.attn_impl == FST_MLA_IMPL_TENSOR && !tc_ok)
     return fail(FST_MLA_ERR_ARG, "this shape has no tcgen05 attention path");
   if (c->cfg.attn_impl != FST_MLA_IMPL_SIMT && tc_ok) {
-    cudaError_t e = launch_attn_tc(a, c->stream);
+    // FST_MLA_ATTN_NAT in the environment selects the kernel that keeps Q_eff in tensor memory
+    // (576-wide rows only), for comparisons
+    static const bool nat = getenv("FST_MLA_ATTN_NAT") != nullptr;
+    cudaError_t e = (nat && attn_nat_supported(a)) ? launch_attn_nat(a, c->stream) : launch_attn_tc(a, c->stream);
     if (e != cudaSuccess) return fail(FST_MLA_ERR_CUDA, "tcgen05 attention launch: %s", cudaGetErrorString(e));
   } else {
     launch_attn_simt(a, c->stream);
