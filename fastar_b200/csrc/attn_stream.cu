@@ -1,0 +1,602 @@
+// Split-KV latent attention as a STREAM of 64-token tiles; Q_eff lives in tensor memory.
+//
+// Same job as attn_tc.cu (QK, softmax, SV of process_mla, reference src/fst_engine.cpp:
+// 3573-3683, over the paged bf16 cache), 64 heads, 512- or 576-wide rows.  Both products are in
+// their natural orientation with the 64 heads as MMA M:
+//   S[64 heads, 64 tok]   = Q[64, d_qk] * K^T   A = Q_eff from TENSOR MEMORY; B = one 8 KB chunk
+//                                               [64 tok x 64 dims] of the page, K-major
+//   O[64 heads, 512]     += P[64, 64] * V       A = P (shared memory, K-major, written by the softmax
+//                                               threads); B = the same chunks read MN-major, N = 256
+//                                               latent columns (four chunks) at a time
+//
+// Why 64-token tiles.  The kernel is bound by how many cache bytes an SM can keep in flight: a
+// chunk occupies shared memory from the moment its copy is issued until the SV MMAs of its tile
+// have retired.  With 128-token tiles one tile (144 KB) fills the SM, so copies, MMAs and softmax
+// take turns.  A page-sized tile is 72 KB; with Q_eff out of shared memory the ring holds three
+// tiles, so the copies of the next tiles are in flight while this one is computed.
+//
+// MMA issue.  One thread issues a tcgen05.mma about every 50-80 cycles whatever its size, and a
+// 64-token tile needs 36 QK MMAs (K = 16 each) and 8 SV MMAs: there are two QK issuers (each
+// accumulates half of the chunks of every tile into a score buffer of its own) and one SV issuer.
+// They touch different accumulators and are ordered against each other only through the mbarriers
+// of the softmax hand-off.
+//
+// Tensor memory (512 columns).  A 64-row operand or accumulator occupies lanes 0-15 of each
+// 32-lane quadrant (row r in lane 32*(r/16) + r%16).  An accumulator may also sit at lane offset
+// 16; an A operand may not, and an MMA that takes A from tensor memory needs its accumulator on
+// the same lanes as A.  Hence:
+//   lanes  0-15: Q_eff (bf16 pairs) in columns [0, d_qk/2) | three score buffers of 64 columns behind it
+//   lanes 16-31: O[64, 512] in columns [0,512)  (its MMAs take A = P from shared memory)
+// The softmax threads touch lanes 0-15 only through the 16-lane access shape (O is rescaled the
+// same way at lane offset 16); 32-lane loads are used where the other 16 lanes are only read.
+#include "kernels.cuh"
+#include "tc_common.cuh"
+
+namespace fst {
+
+namespace {
+
+constexpr int TILE = 64;               // tokens per tile = one cache page
+constexpr int HEADS = 64;
+constexpr int D_V = 512;
+constexpr int CHUNK = TILE * 128;      // 8 KB: [64 tok x 64 dims]
+constexpr int P_BYTES = HEADS * TILE * 2;  // 8 KB
+constexpr int ST_THREADS = 448;  // warps: 0, 10, 11 copy; 1, 13 issue QK; 12 issues SV; 2-9 softmax
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_Q = 0, COL_S = 288, COL_O = 0;
+constexpr uint32_t LANE16 = 16u << 16;
+constexpr float RESCALE_THRESHOLD = 8.0f;
+
+// Shared memory: a ring of three tile frames (NCH chunk slots each), P (also the staging area of
+// the epilogue), barriers and small arrays.
+constexpr int MISC_BYTES = 2048;
+__host__ __device__ constexpr int off_p(int nch) { return 3 * nch * CHUNK; }
+__host__ __device__ constexpr int off_misc(int nch) { return off_p(nch) + P_BYTES; }
+__host__ __device__ constexpr int smem_total(int nch) { return off_misc(nch) + MISC_BYTES + 1024; }
+
+struct StreamParams {
+  const bf16* q_eff;
+  const int32_t* tables;
+  const int32_t* tok_table;
+  const AttnSeg* segs;
+  const int32_t* cta_seg;
+  const bf16* pool;
+  float* part_m;
+  float* part_l;
+  float* part_o;
+  int* d_status;
+  int d_qk;
+  float scale_log2;
+};
+
+#ifdef FST_ATTN_TRACE
+#ifndef FST_TRACE_CTA
+#define FST_TRACE_CTA 0
+#endif
+// Tuning builds: [tile][event] SM-clock stamps of CTA FST_TRACE_CTA, and per-CTA {entry ns, start ns, exit ns, segments, entry clk, exit clk}.
+__device__ long long g_st_trace[64 * 16];
+__device__ long long g_st_cta[256 * 8];
+__device__ __forceinline__ long long st_gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define STRACE(tile, ev) do { if (blockIdx.x == FST_TRACE_CTA && (tile) < 64) g_st_trace[(tile) * 16 + (ev)] = clock64(); } while (0)
+#define ST_CTA(ev, val) do { if (threadIdx.x == 0 && blockIdx.x < 256) g_st_cta[blockIdx.x * 8 + (ev)] = (val); } while (0)
+#else
+#define STRACE(tile, ev) do { } while (0)
+#define ST_CTA(ev, val) do { } while (0)
+#endif
+
+struct StreamMisc {
+  uint64_t full_t[4][3]; // chunks 3i .. 3i+2 of tile g have landed: barrier [g & 3][i]
+  uint64_t o_done[4];    // the SV MMAs of tile g have retired (its ring slots are free): barrier g & 3
+  uint64_t q_ready;      // Q_eff of a segment written to tensor memory by the softmax threads
+  uint64_t s_full[2];    // both score partials of tile g are complete: barrier g & 1 (two commits)
+  uint64_t s_free[3];    // the softmax threads have read the partial in this score buffer
+  uint64_t p_full;       // the probabilities of a tile are written
+  uint32_t tmem_slot;
+  int abort_flag;
+  float pmax[2][2][HEADS];  // [tile parity][token half][head]: row maxima of the two warps of a quadrant
+  float lsum[2][HEADS];     // [token half][head]: row sums, in the epilogue
+};
+
+__device__ __forceinline__ float ex2f(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+// Barrier of the two warps of one quadrant (64 threads) that also ANDs a predicate.
+__device__ __forceinline__ bool quad_bar_and(int quad, bool v) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred q, r;\n\t"
+      "setp.ne.u32 q, %2, 0;\n\t"
+      "bar.red.and.pred r, %1, 64, q;\n\t"
+      "selp.u32 %0, 1, 0, r;\n\t}"
+      : "=r"(out)
+      : "r"(2 + quad), "r"((uint32_t)v)
+      : "memory");
+  return out != 0;
+}
+
+// 16-lane tensor-memory access (shape 16x32bx2): threads 0-15 of the warp address lanes
+// base .. base+15, columns [c, c+N/2); threads 16-31 address the SAME lanes, columns
+// [c+N/2, c+N), where N is 64 (x32) or 32 (x16).  Lanes base+16 .. base+31 are not touched.
+__device__ __forceinline__ void tmem_ld16x64(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile("tcgen05.ld.sync.aligned.16x32bx2.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32], 32;"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr)
+               : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st16x64(uint32_t taddr, const float* v) {
+  asm volatile("tcgen05.st.sync.aligned.16x32bx2.x32.b32 [%32], 32, {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+               ::"r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31])), "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16x32(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile("tcgen05.ld.sync.aligned.16x32bx2.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16], 16;"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr)
+               : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st16x32(uint32_t taddr, const float* v) {
+  asm volatile("tcgen05.st.sync.aligned.16x32bx2.x16.b32 [%16], 16, {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+               ::"r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+
+// Walks the tiles of a CTA's segment list in order: every role keeps one of these per stream
+// position it tracks, so that all roles agree on (segment, tile in segment, running tile index).
+struct TileCursor {
+  int si, seg_end;   // current segment, one past the CTA's last
+  int t, n_tiles;    // tile within the segment, tiles of the segment
+  int g;             // running tile index over the whole list
+  int sidx;          // running segment index
+  AttnSeg sg;
+  __device__ __forceinline__ void load(const AttnSeg* segs) {
+    if (si < seg_end) {
+      sg = segs[si];
+      n_tiles = (sg.kv_end - sg.kv_begin + TILE - 1) / TILE;
+    }
+  }
+  __device__ __forceinline__ void init(const AttnSeg* segs, int seg0, int seg1) {
+    si = seg0; seg_end = seg1; t = 0; g = 0; sidx = 0; n_tiles = 0;
+    load(segs);
+  }
+  __device__ __forceinline__ bool done() const { return si >= seg_end; }
+  __device__ __forceinline__ void next(const AttnSeg* segs) {
+    ++g;
+    if (++t == n_tiles) {
+      t = 0; ++si; ++sidx;
+      load(segs);
+    }
+  }
+};
+
+// The QK MMAs of chunks [C0, C1) of tile g: S_partial = Q[:, chunks] * K[:, chunks]^T.  Chunks land
+// in groups of three, each group with a barrier.
+template <int C0, int C1>
+__device__ __forceinline__ bool qk_chunks(StreamMisc* mi, int g, uint32_t d, uint32_t tmem, uint32_t frame16,
+                                          volatile int* abort_flag, int* d_status) {
+  constexpr uint32_t idesc_qk = tc::umma_idesc_bf16(HEADS, TILE, 0, 0);
+  const uint64_t k_major = tc::umma_desc_sw128(0, 16, 1024);
+#pragma unroll
+  for (int c = C0; c < C1; ++c) {
+    if (c == C0 || c % 3 == 0) {
+      if (!tc::mbar_wait(&mi->full_t[g & 3][c / 3], (g >> 2) & 1, abort_flag, d_status, ST_MMA_TIMEOUT)) return false;
+      if (c == 0) STRACE(g, 0);
+      tc::tc_fence_after();
+    }
+    const uint64_t db = k_major | (uint64_t)(frame16 + c * (CHUNK / 16));
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      umma_ts(d, tmem + COL_Q + c * 32 + k * 8, db + k * 2, idesc_qk, (c > C0 || k > 0) ? 1u : 0u);
+  }
+  return true;
+}
+
+// 14 warps are allocated as 16 (granularity four): 128 registers per thread
+template <int NCH>
+__global__ void __launch_bounds__(ST_THREADS, 1)
+k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* s_ring = smem;
+  unsigned char* s_p = smem + off_p(NCH);
+  StreamMisc* mi = reinterpret_cast<StreamMisc*>(smem + off_misc(NCH));
+  volatile int* abort_flag = &mi->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seg0 = p.cta_seg[blockIdx.x], seg1 = p.cta_seg[blockIdx.x + 1];
+#ifdef FST_ATTN_TRACE
+  ST_CTA(0, st_gtime());
+  ST_CTA(4, clock64());
+  ST_CTA(3, (long long)(seg1 - seg0));
+#endif
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 4; ++i) {
+      for (int j = 0; j < 3; ++j) tc::mbar_init(&mi->full_t[i][j], j < 2 ? 3 : NCH - 6);
+      tc::mbar_init(&mi->o_done[i], 1);
+    }
+    tc::mbar_init(&mi->q_ready, 256);
+    for (int i = 0; i < 2; ++i) tc::mbar_init(&mi->s_full[i], 2);
+    for (int i = 0; i < 3; ++i) tc::mbar_init(&mi->s_free[i], 256);
+    tc::mbar_init(&mi->p_full, 256);
+    mi->abort_flag = 0;
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) tc::tmem_alloc(&mi->tmem_slot, TMEM_COLS);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = mi->tmem_slot;
+  pdl_launch();
+  pdl_wait();  // Q_eff and the appended cache rows come from earlier kernels
+#ifdef FST_ATTN_TRACE
+  ST_CTA(1, st_gtime());
+#endif
+
+  if (warp == 0 || warp == 10 || warp == 11) {
+    // ---------------- TMA producers: lane 0 of warps 0, 10, 11 ----------------
+    // Tile g goes to ring frame g % 3, which is free once the SV MMAs of tile g-3 have retired;
+    // chunk c of the tile is copied by producer (g * NCH + c) % 3.  The chunks of a tile land in three groups (one
+    // chunk of each producer per group), each with its own barrier, so that the QK MMAs of the
+    // first group run while the rest of the tile is still on its way.
+    if (lane == 0) {
+      const int r = warp == 0 ? 0 : warp - 9;
+      if (r == 0) tc::tma_prefetch_desc(&tmKV);
+      TileCursor cur;
+      cur.init(p.segs, seg0, seg1);
+      bool ok = true;
+      while (!cur.done() && ok) {
+        const int32_t* table = p.tables + p.tok_table[cur.sg.tok];
+        const int row0 = table[(cur.sg.kv_begin >> 6) + cur.t] * TILE;
+        const int g = cur.g, j0 = g * NCH;
+        const int c0 = (r + 3 - j0 % 3) % 3;
+        if (r == 0) STRACE(g, 11);
+        if (g >= 3) {
+          ok = tc::mbar_wait(&mi->o_done[(g - 3) & 3], ((g - 3) >> 2) & 1, abort_flag, p.d_status, ST_TMA_TIMEOUT);
+          if (!ok) break;
+        }
+        for (int c = c0; c < NCH; c += 3) {
+          const int slot = (g % 3) * NCH + c;
+          tc::mbar_expect_tx(&mi->full_t[g & 3][c / 3], CHUNK);
+          tc::tma_load_3d(s_ring + slot * CHUNK, &tmKV, &mi->full_t[g & 3][c / 3], c * 64, row0, 0);
+        }
+        if (r == 0) STRACE(g, 12);
+#ifdef FST_ATTN_TRACE
+        if (r == 0) ST_CTA(6, (long long)(g + 1));
+#endif
+        cur.next(p.segs);
+      }
+    }
+  } else if (warp == 1 || warp == 13) {
+    // ---------------- QK issuers ----------------
+    // A thread issues a tcgen05.mma about every 50-80 cycles, whatever its size, and needs a few
+    // hundred cycles per barrier it waits on, so the 36 QK MMAs of a tile are split: warp 1
+    // accumulates chunks 0-4 and warp 13 chunks 5-8 into score buffers of their own (the
+    // softmax threads add the two).  Partial k = 2g + part lives in buffer k % 3.
+    if (lane == 0) {
+      const int part = warp == 1 ? 0 : 1;
+      const uint32_t ring16 = (tc::smem_u32(s_ring) & 0x3FFFFu) >> 4;
+      TileCursor cur;
+      cur.init(p.segs, seg0, seg1);
+      bool ok = true;
+      while (!cur.done() && ok) {
+        const int g = cur.g;
+        // both issuers wait for Q_eff of every segment
+        if (cur.t == 0) ok = tc::mbar_wait(&mi->q_ready, cur.sidx & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
+        const int k = 2 * g + part, buf = k % 3, use = k / 3;
+        // the softmax threads have read the previous partial in this buffer
+        if (ok && use >= 1) ok = tc::mbar_wait(&mi->s_free[buf], (use - 1) & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
+        if (!ok) break;
+        const uint32_t d = tmem + COL_S + buf * TILE;  // same lanes as the TMEM-resident A
+        const uint32_t frame16 = ring16 + (g % 3) * NCH * (CHUNK / 16);
+        if (part == 0) ok = qk_chunks<0, 5>(mi, g, d, tmem, frame16, abort_flag, p.d_status);
+        else ok = qk_chunks<5, NCH>(mi, g, d, tmem, frame16, abort_flag, p.d_status);
+        if (!ok) break;
+        tc::umma_commit(&mi->s_full[g & 1]);
+        if (part == 1) STRACE(g, 1);
+        cur.next(p.segs);
+      }
+    }
+  } else if (warp == 12) {
+    // ---------------- SV issuer ----------------
+    if (lane == 0) {
+      const uint64_t k_major = tc::umma_desc_sw128(0, 16, 1024);
+      const uint64_t v_desc = tc::umma_desc_sw128(0, CHUNK, 1024);  // MN-major: 64-column groups one slot apart
+      const uint32_t ring16 = (tc::smem_u32(s_ring) & 0x3FFFFu) >> 4, p16 = (tc::smem_u32(s_p) & 0x3FFFFu) >> 4;
+      constexpr uint32_t id256 = tc::umma_idesc_bf16(HEADS, 256, 0, 1);
+      TileCursor cur;
+      cur.init(p.segs, seg0, seg1);
+      bool ok = true;
+      while (!cur.done() && ok) {
+        const int g = cur.g;
+        ok = tc::mbar_wait(&mi->p_full, g & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
+        if (!ok) break;
+        STRACE(g, 3);
+        tc::tc_fence_after();
+        const uint64_t da = k_major | (uint64_t)p16;
+        const uint32_t acc0 = cur.t > 0 ? 1u : 0u;
+#pragma unroll
+        for (int nh = 0; nh < 2; ++nh) {
+          // latent columns 256*nh .. +255 are chunks 4nh .. 4nh+3 of the tile's frame
+          const uint32_t d = tmem + LANE16 + COL_O + nh * 256;
+          const uint64_t db = v_desc | (uint64_t)(ring16 + ((g % 3) * NCH + 4 * nh) * (CHUNK / 16));
+#pragma unroll
+          for (int k = 0; k < TILE / 16; ++k) tc::umma_bf16(d, da + k * 2, db + k * 128, id256, k > 0 ? 1u : acc0);
+        }
+        tc::umma_commit(&mi->o_done[g & 3]);
+        STRACE(g, 4);
+        cur.next(p.segs);
+      }
+    }
+  } else {
+    // ---------------- softmax / epilogue (warps 2-9) ----------------
+    // Quadrant q of tensor memory holds heads 16q .. 16q+15.  The two warps of a quadrant split a
+    // tile's 64 tokens; inside a warp, lanes 0-15 and 16-31 address the same 16 rows and split
+    // the warp's 32 tokens again, so a thread owns 16 scores of one head.
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int sub = lane >> 4;
+    const int row = quad * 16 + (lane & 15);
+    const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
+    // epilogue staging: half of the P rows of this quadrant (what the two warps of the quadrant
+    // write during the softmax, so the quadrant barrier orders the two uses)
+    unsigned char* stage = s_p + quad * 2048 + half * 1024;
+    // Q_eff of token `tok` -> tensor memory (bf16 pairs, two dims per column): all loads first,
+    // then the stores.  Every QK MMA of the previous segment must have retired (the caller saw
+    // s_full of its last tile).
+    auto write_q = [&](int tok, int g_trace) {
+      const unsigned char* qrow = reinterpret_cast<const unsigned char*>(p.q_eff + ((long long)tok * HEADS + row) * p.d_qk);
+      uint4 v[20];
+#pragma unroll
+      for (int gsel = 0; gsel < 2; ++gsel) {
+        const uint4* src = reinterpret_cast<const uint4*>(qrow + (half * 128 + gsel * 64 + sub * 32) * 4);
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) v[gsel * 8 + q4] = src[q4];
+      }
+      if (NCH == 9 && half == 1) {  // the 64 rope dims: columns [256, 288)
+        const uint4* src = reinterpret_cast<const uint4*>(qrow + (256 + sub * 16) * 4);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) v[16 + q4] = src[q4];
+      }
+#pragma unroll
+      for (int gsel = 0; gsel < 2; ++gsel) {
+        float w[32];
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          w[q4 * 4] = __uint_as_float(v[gsel * 8 + q4].x);
+          w[q4 * 4 + 1] = __uint_as_float(v[gsel * 8 + q4].y);
+          w[q4 * 4 + 2] = __uint_as_float(v[gsel * 8 + q4].z);
+          w[q4 * 4 + 3] = __uint_as_float(v[gsel * 8 + q4].w);
+        }
+        tmem_st16x64(lane_addr + COL_Q + half * 128 + gsel * 64, w);
+      }
+      if (NCH == 9 && half == 1) {
+        float w[16];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          w[q4 * 4] = __uint_as_float(v[16 + q4].x);
+          w[q4 * 4 + 1] = __uint_as_float(v[16 + q4].y);
+          w[q4 * 4 + 2] = __uint_as_float(v[16 + q4].z);
+          w[q4 * 4 + 3] = __uint_as_float(v[16 + q4].w);
+        }
+        tmem_st16x32(lane_addr + COL_Q + 256, w);
+      }
+      tmem_wait_st();
+      tc::tc_fence_before();
+      tc::mbar_arrive(&mi->q_ready);
+      if (threadIdx.x == 64) STRACE(g_trace, 15);
+    };
+    TileCursor cur;
+    cur.init(p.segs, seg0, seg1);
+    bool ok = true;
+    while (!cur.done() && ok) {
+      const AttnSeg sg = cur.sg;
+      const int n_tiles = cur.n_tiles;
+      // Q_eff of the first segment; later segments are written at the end of their predecessor
+      if (cur.sidx == 0) write_q(sg.tok, cur.g);
+      // bring the next segment's Q_eff rows into L2 meanwhile: by the time they are needed the
+      // cache stream has long evicted what the previous kernel wrote
+      const int next_tok = cur.si + 1 < cur.seg_end ? p.segs[cur.si + 1].tok : -1;
+      if (next_tok >= 0) {
+        const unsigned char* qrow = reinterpret_cast<const unsigned char*>(p.q_eff + ((long long)next_tok * HEADS + row) * p.d_qk);
+        const int off = (half * 2 + sub) * (NCH * 32);  // four threads share a row: a quarter each
+        for (int b = 0; b < NCH * 32; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(qrow + off + b));
+      }
+      float m_used = -INFINITY, l = 0.0f;
+      int g = cur.g;
+      for (int t = 0; t < n_tiles && ok; ++t, cur.next(p.segs)) {
+        g = cur.g;
+        ok = tc::mbar_wait(&mi->s_full[g & 1], (g >> 1) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
+        if (threadIdx.x == 64) STRACE(g, 8);
+        tc::tc_fence_after();
+        const int tok0 = sg.kv_begin + t * TILE + half * 32 + sub * 16;
+        float sc[16], sc2[16];
+        const int b0 = (2 * g) % 3, b1 = (2 * g + 1) % 3;
+        tmem_ld16x32(lane_addr + COL_S + b0 * TILE + half * 32, sc);
+        tmem_ld16x32(lane_addr + COL_S + b1 * TILE + half * 32, sc2);
+        tc::tc_fence_before();
+        tc::mbar_arrive(&mi->s_free[b0]);
+        tc::mbar_arrive(&mi->s_free[b1]);
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          sc[j] = tok0 + j < sg.kv_end ? (sc[j] + sc2[j]) * p.scale_log2 : -INFINITY;
+          mx = fmaxf(mx, sc[j]);
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        if (sub == 0) mi->pmax[g & 1][half][row] = mx;
+        ok = quad_bar_and(quad, ok);
+        if (!ok) break;
+        if (threadIdx.x == 64) STRACE(g, 9);
+        // the reference maximum moves only when the tile maximum exceeds it by more than 2^8
+        const float tm = fmaxf(mi->pmax[g & 1][0][row], mi->pmax[g & 1][1][row]);
+        float alpha = 1.0f;
+        if (tm > m_used + RESCALE_THRESHOLD) {  // also the first tile (m_used = -inf)
+          alpha = ex2f(m_used - tm);
+          m_used = tm;
+        }
+        float sum = 0.0f;
+        uint32_t packed[8];
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+          const float p0 = ex2f(sc[j] - m_used), p1 = ex2f(sc[j + 1] - m_used);  // masked: ex2(-inf) = 0
+          sum += p0 + p1;
+          __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+          packed[j / 2] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        l = l * alpha + sum;
+        // P (and O, if it is rescaled below) belong to the SV MMAs of tile g-1 until they retire
+        if (g >= 1) ok = tc::mbar_wait(&mi->o_done[(g - 1) & 3], ((g - 1) >> 2) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
+        {
+          // P[row, tokens 32*half + 16*sub .. +15]: two 16-byte units of the row, 128-byte swizzle
+          unsigned char* prow = s_p + row * 128;
+          const int u0 = half * 4 + sub * 2;
+          *reinterpret_cast<uint4*>(prow + (((u0) ^ (row & 7)) * 16)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          *reinterpret_cast<uint4*>(prow + (((u0 + 1) ^ (row & 7)) * 16)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        }
+        // O rows are scaled by their own alpha through the 16-lane access shape at lane offset 16
+        if (t > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+          tc::tc_fence_after();
+#pragma unroll 1
+          for (int cc = 0; cc < 4; ++cc) {
+            float o[32];
+            const uint32_t addr = lane_addr + LANE16 + COL_O + half * 256 + cc * 64;
+            tmem_ld16x64(addr, o);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] *= alpha;
+            tmem_st16x64(addr, o);
+          }
+          tmem_wait_st();
+        }
+        if (threadIdx.x == 64) STRACE(g, 10);
+        tc::fence_proxy_async();
+        tc::tc_fence_before();
+        tc::mbar_arrive(&mi->p_full);
+      }
+      if (!ok) break;
+      // Q_eff of the next segment goes in first, so that its QK MMAs run during the epilogue
+      if (next_tok >= 0) write_q(next_tok, g + 1);
+      // ---- epilogue of the segment: un-normalised partial (max, sum, O) ----
+      ok = tc::mbar_wait(&mi->o_done[g & 3], (g >> 2) & 1, abort_flag, p.d_status, ST_EPI_TIMEOUT);
+      tc::tc_fence_after();
+      if (threadIdx.x == 64) STRACE(g, 13);
+      l += __shfl_xor_sync(0xffffffffu, l, 16);
+      if (sub == 0) mi->lsum[half][row] = l;
+      ok = quad_bar_and(quad, ok);
+      if (!ok) break;
+      if (half == 0 && sub == 0) {
+        p.part_l[(long long)sg.part * HEADS + row] = mi->lsum[0][row] + mi->lsum[1][row];
+        p.part_m[(long long)sg.part * HEADS + row] = m_used * 0.6931471805599453f;  // back to ln units
+      }
+      {
+        // A 32-lane load hands lanes 16-31 the O rows of this quadrant (row lane-16), 32 columns
+        // at a time; this warp owns columns 256*half .. +255.  The rows go through shared memory
+        // so that every store instruction writes four full 128-byte lines.
+        float* po = p.part_o + ((long long)sg.part * HEADS + quad * 16) * D_V + half * 256;
+#pragma unroll 1
+        for (int cc = 0; cc < 8; ++cc) {
+          float o[32];
+          tc::tmem_ld32(lane_addr + COL_O + half * 256 + cc * 32, o);
+#pragma unroll
+          for (int h8 = 0; h8 < 2; ++h8) {  // eight rows at a time through the 1 KB staging area
+            if (sub == 1 && ((lane >> 3) & 1) == h8) {
+              const int rr = lane & 7;
+#pragma unroll
+              for (int u = 0; u < 8; ++u)
+                *reinterpret_cast<float4*>(stage + rr * 128 + ((u ^ rr) * 16)) = make_float4(o[u * 4], o[u * 4 + 1], o[u * 4 + 2], o[u * 4 + 3]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const int rr = i * 4 + (lane >> 3), u = lane & 7;
+              const float4 v = *reinterpret_cast<const float4*>(stage + rr * 128 + ((u ^ rr) * 16));
+              *reinterpret_cast<float4*>(po + (long long)(h8 * 8 + rr) * D_V + cc * 32 + u * 4) = v;
+            }
+            __syncwarp();
+          }
+        }
+      }
+      if (threadIdx.x == 64) STRACE(g, 14);
+      tc::tc_fence_before();
+      ok = quad_bar_and(quad, ok);  // lsum, the staging rows and O are reused by the next segment
+    }
+  }
+
+  tc::tc_fence_before();
+  __syncthreads();
+#ifdef FST_ATTN_TRACE
+  ST_CTA(2, st_gtime());
+  ST_CTA(5, clock64());
+#endif
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies and MMAs in flight settle
+  }
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+#ifdef FST_ATTN_TRACE
+extern "C" int fst_debug_read_stream_trace(long long* tiles, long long* ctas) {
+  cudaError_t e = cudaMemcpyFromSymbol(tiles, g_st_trace, sizeof(long long) * 64 * 16);
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(ctas, g_st_cta, sizeof(long long) * 256 * 8);
+  return (int)e;
+}
+#endif
+
+bool attn_stream_supported(const AttnArgs& a) {
+  return a.H == HEADS && a.d_v == D_V && a.page_tokens == TILE && a.row == a.d_qk &&
+         (a.d_qk == 576 || a.d_qk == 512) && a.pool_rows < (1ll << 31) &&
+         (reinterpret_cast<uintptr_t>(a.pool) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.q_eff) & 15) == 0;
+}
+
+cudaError_t launch_attn_stream(const AttnArgs& a, cudaStream_t st) {
+  static_assert(sizeof(StreamMisc) <= MISC_BYTES, "misc region too small");
+  static_assert(smem_total(9) <= 227 * 1024, "shared memory budget");
+  static_assert(COL_S + 3 * TILE <= TMEM_COLS, "tensor memory budget");
+  if (a.n_segs <= 0) return cudaSuccess;
+  CUtensorMap tmKV;
+  const char* err = nullptr;
+  if (!tc::cached_tmap(&tmKV, a.pool, (uint64_t)a.row, (uint64_t)a.pool_rows, 1, (uint64_t)a.row * 2,
+                       (uint64_t)a.row * 2 * (uint64_t)a.pool_rows, 64, TILE, 1, &err))
+    return cudaErrorInvalidValue;
+  StreamParams p;
+  p.q_eff = a.q_eff; p.tables = a.tables; p.tok_table = a.tok_table; p.segs = a.segs; p.cta_seg = a.cta_seg;
+  p.part_m = a.part_m; p.part_l = a.part_l; p.part_o = a.part_o; p.d_status = a.d_status;
+  p.pool = a.pool;
+  p.d_qk = a.d_qk;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(k_attn_stream<9>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_total(9));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_stream<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_total(8));
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  if (a.d_qk == 576) return launch_pdl(k_attn_stream<9>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(9), st, 1, tmKV, p);
+  return launch_pdl(k_attn_stream<8>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(8), st, 1, tmKV, p);
+}
+
+}  // namespace fst

@@ -92,9 +92,9 @@ void launch_attn_simt(const AttnArgs& a, cudaStream_t st);
 bool attn_tc_supported(const AttnArgs& a);
 cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st);
 size_t attn_tc_smem_bytes(const AttnArgs& a);
-// Second-generation kernel (Q_eff in tensor memory, ring of chunk slots): 576-wide rows only.
-bool attn_nat_supported(const AttnArgs& a);
-cudaError_t launch_attn_nat(const AttnArgs& a, cudaStream_t st);
+// Streaming kernel: 64-token tiles, Q_eff in tensor memory, ring of chunk slots.
+bool attn_stream_supported(const AttnArgs& a);
+cudaError_t launch_attn_stream(const AttnArgs& a, cudaStream_t st);
 
 // Log-sum-exp merge of each token's partial slots [tok_part[t], tok_part[t+1]).
 struct MergeArgs {

@@ -298,10 +298,10 @@ int run_attention(FstMlaCtx* c, int lid, const bf16* q_eff) {
   if (c->cfg.attn_impl == FST_MLA_IMPL_TENSOR && !tc_ok)
     return fail(FST_MLA_ERR_ARG, "this shape has no tcgen05 attention path");
   if (c->cfg.attn_impl != FST_MLA_IMPL_SIMT && tc_ok) {
-    // FST_MLA_ATTN_NAT in the environment selects the kernel that keeps Q_eff in tensor memory
-    // (576-wide rows only), for comparisons
-    static const bool nat = getenv("FST_MLA_ATTN_NAT") != nullptr;
-    cudaError_t e = (nat && attn_nat_supported(a)) ? launch_attn_nat(a, c->stream) : launch_attn_tc(a, c->stream);
+    // the streaming kernel; FST_MLA_ATTN_V1 in the environment selects the first-generation
+    // kernel (128-token tiles, Q_eff in shared memory), for comparisons
+    static const bool v1 = getenv("FST_MLA_ATTN_V1") != nullptr;
+    cudaError_t e = (!v1 && attn_stream_supported(a)) ? launch_attn_stream(a, c->stream) : launch_attn_tc(a, c->stream);
     if (e != cudaSuccess) return fail(FST_MLA_ERR_CUDA, "tcgen05 attention launch: %s", cudaGetErrorString(e));
   } else {
     launch_attn_simt(a, c->stream);
@@ -796,13 +796,19 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
   }
   if ((int)tables.size() > c->tables_cap) return fail(FST_MLA_ERR_CAPACITY, "block tables overflow");
 
-  // split-KV schedule: the concatenated ATTN_TILE-row tiles of all query tokens are cut into
-  // n_ctas contiguous, equally long runs; a run that crosses a token boundary yields one
-  // segment (and one partial) per token it touches.
-  long long total_tiles = 0, kv_rows = 0;
+  // split-KV schedule: the concatenated tiles of all query tokens are cut into n_ctas contiguous
+  // runs of about equal COST; a run that crosses a token boundary yields one segment (and one
+  // partial) per token it touches.  The unit is a cache page where pages hold 64 tokens, else
+  // ATTN_TILE rows.  Cost, in half units: 2 per tile plus SEG_COST2 per segment -- a segment
+  // pays for loading Q_eff, refilling the pipeline and writing its partial (about three
+  // 64-token tiles of the streaming kernel).
+  const int unit = c->cfg.page_tokens == 64 ? 64 : ATTN_TILE;
+  const long long SEG_COST2 = unit == 64 ? 6 : 3;
+  long long total_tiles = 0, kv_rows = 0, n_nonempty = 0;
   for (int i = 0; i < T; ++i) {
-    total_tiles += (kvlen[i] + ATTN_TILE - 1) / ATTN_TILE;
+    total_tiles += (kvlen[i] + unit - 1) / unit;
     kv_rows += kvlen[i];
+    n_nonempty += kvlen[i] > 0;
   }
   int max_ctas = c->n_sm;
   if (const char* e = getenv("FST_MLA_MAX_CTAS")) {  // tuning aid: fewer attention CTAs than SMs
@@ -810,12 +816,13 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
     if (v > 0 && v < max_ctas) max_ctas = v;
   }
   const int n_ctas = (int)std::min<long long>(max_ctas, std::max<long long>(total_tiles, 1));
+  const long long total2 = 2 * total_tiles + SEG_COST2 * (n_nonempty + n_ctas - 1);
   std::vector<AttnSeg> segs;
   std::vector<int32_t> cta_seg(n_ctas + 1, 0);
   {
     int tok = 0, tile_in_tok = 0, part = 0;
     tok_part[0] = 0;
-    auto tiles_of = [&](int i) { return (kvlen[i] + ATTN_TILE - 1) / ATTN_TILE; };
+    auto tiles_of = [&](int i) { return (kvlen[i] + unit - 1) / unit; };
     auto skip_empty = [&]() {
       while (tok < T && tile_in_tok >= tiles_of(tok)) {
         ++tok;
@@ -824,21 +831,23 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
       }
     };
     skip_empty();
-    long long given = 0;
+    long long spent = 0;
     for (int k = 0; k < n_ctas; ++k) {
       cta_seg[k] = (int)segs.size();
-      long long quota = (total_tiles * (k + 1)) / n_ctas - given;
-      given += quota;
-      while (quota > 0 && tok < T) {
-        const int take = (int)std::min<long long>(quota, tiles_of(tok) - tile_in_tok);
+      const bool last = k == n_ctas - 1;
+      const long long target = (total2 * (k + 1)) / n_ctas;  // cumulative cost through this CTA
+      while (tok < T) {
+        long long room = last ? (1ll << 40) : (target - spent - SEG_COST2) / 2;  // tiles that still fit
+        if (room < 1) break;
+        const int take = (int)std::min<long long>(room, tiles_of(tok) - tile_in_tok);
         AttnSeg sg;
         sg.tok = tok;
-        sg.kv_begin = tile_in_tok * ATTN_TILE;
-        sg.kv_end = std::min(kvlen[tok], (tile_in_tok + take) * ATTN_TILE);
+        sg.kv_begin = tile_in_tok * unit;
+        sg.kv_end = std::min(kvlen[tok], (tile_in_tok + take) * unit);
         sg.part = part++;
         segs.push_back(sg);
         tile_in_tok += take;
-        quota -= take;
+        spent += SEG_COST2 + 2 * take;
         skip_empty();
       }
     }
