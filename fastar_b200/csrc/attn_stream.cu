@@ -76,7 +76,7 @@ struct StreamParams {
 // Tuning builds: [tile][event] SM-clock stamps of CTA FST_TRACE_CTA, and per-CTA {entry ns, start ns, exit ns, segments, entry clk, exit clk}.
 __device__ long long g_st_trace[64 * 16];
 __device__ long long g_st_cta[256 * 8];
-__device__ __forceinline__ long long st_gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ long long st_gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t) : : "memory"); return t; }
 #define STRACE(tile, ev) do { if (blockIdx.x == FST_TRACE_CTA && (tile) < 64) g_st_trace[(tile) * 16 + (ev)] = clock64(); } while (0)
 #define ST_CTA(ev, val) do { if (threadIdx.x == 0 && blockIdx.x < 256) g_st_cta[blockIdx.x * 8 + (ev)] = (val); } while (0)
 #else
@@ -224,8 +224,10 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seg0 = p.cta_seg[blockIdx.x], seg1 = p.cta_seg[blockIdx.x + 1];
 #ifdef FST_ATTN_TRACE
-  ST_CTA(0, st_gtime());
-  ST_CTA(4, clock64());
+  if (threadIdx.x == 64 && blockIdx.x < 256) {
+    g_st_cta[blockIdx.x * 8 + 0] = st_gtime();
+    g_st_cta[blockIdx.x * 8 + 4] = clock64();
+  }
   ST_CTA(3, (long long)(seg1 - seg0));
 #endif
 
@@ -413,18 +415,19 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
       const int n_tiles = cur.n_tiles;
       // Q_eff of the first segment; later segments are written at the end of their predecessor
       if (cur.sidx == 0) write_q(sg.tok, cur.g);
-      // bring the next segment's Q_eff rows into L2 meanwhile: by the time they are needed the
-      // cache stream has long evicted what the previous kernel wrote
       const int next_tok = cur.si + 1 < cur.seg_end ? p.segs[cur.si + 1].tok : -1;
-      if (next_tok >= 0) {
-        const unsigned char* qrow = reinterpret_cast<const unsigned char*>(p.q_eff + ((long long)next_tok * HEADS + row) * p.d_qk);
-        const int off = (half * 2 + sub) * (NCH * 32);  // four threads share a row: a quarter each
-        for (int b = 0; b < NCH * 32; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(qrow + off + b));
-      }
       float m_used = -INFINITY, l = 0.0f;
       int g = cur.g;
       for (int t = 0; t < n_tiles && ok; ++t, cur.next(p.segs)) {
         g = cur.g;
+        if (next_tok >= 0 && t == max(n_tiles - 4, 0)) {
+          // bring the next segment's Q_eff rows into L2 a few tiles before they are needed (the
+          // cache stream has long evicted what the previous kernel wrote; any earlier and they
+          // would be evicted again).  Four threads share a row: a quarter each.
+          const unsigned char* qrow = reinterpret_cast<const unsigned char*>(p.q_eff + ((long long)next_tok * HEADS + row) * p.d_qk);
+          const int off = (half * 2 + sub) * (NCH * 32);
+          for (int b = 0; b < NCH * 32; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(qrow + off + b));
+        }
         ok = tc::mbar_wait(&mi->s_full[g & 1], (g >> 1) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
         if (threadIdx.x == 64) STRACE(g, 8);
         tc::tc_fence_after();
@@ -544,8 +547,11 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
   tc::tc_fence_before();
   __syncthreads();
 #ifdef FST_ATTN_TRACE
-  ST_CTA(2, st_gtime());
-  ST_CTA(5, clock64());
+  // (stamped by a softmax thread: what thread 0 writes here can land before the barrier)
+  if (threadIdx.x == 64 && blockIdx.x < 256) {
+    g_st_cta[blockIdx.x * 8 + 2] = st_gtime();
+    g_st_cta[blockIdx.x * 8 + 5] = clock64();
+  }
 #endif
   if (*abort_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies and MMAs in flight settle

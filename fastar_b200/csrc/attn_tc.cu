@@ -68,7 +68,7 @@ __device__ long long g_attn_trace[64 * 16];
 #define TRACE(tile, ev) do { if (blockIdx.x == 0 && (tile) < 64) g_attn_trace[(tile) * 16 + (ev)] = clock64(); } while (0)
 // Per-CTA summary: [cta][0..7] = global ns at entry, after the dependency wait, at exit; segments; SM clock at entry, exit.
 __device__ long long g_attn_cta[256 * 8];
-__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t) : : "memory"); return t; }
 #define CTA_TRACE(ev, val) do { if (threadIdx.x == 0 && blockIdx.x < 256) g_attn_cta[blockIdx.x * 8 + (ev)] = (val); } while (0)
 #else
 #define TRACE(tile, ev) do { } while (0)

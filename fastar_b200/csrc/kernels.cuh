@@ -1,13 +1,27 @@
 // Launchers of the MLA kernels.  All pointers are device pointers; bf16 unless noted.
 #pragma once
+#include <mutex>
+#include <set>
 #include "common.cuh"
 
 namespace fst {
+
+// Every kernel of the library asks for the largest shared-memory carve-out, whatever it uses:
+// an SM that has to change its L1 / shared split between two kernels drains first, and the
+// attention kernel (227 KB) would pay that after every GEMM.  Done once per kernel.
+inline void prefer_max_shared(const void* kernel) {
+  static std::mutex mu;
+  static std::set<const void*> done;
+  std::lock_guard<std::mutex> lk(mu);
+  if (done.insert(kernel).second)
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
 
 // Launch with programmatic stream serialisation (and an optional cluster along y).
 template <class... KArgs, class... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                               int cluster_y, Args&&... args) {
+  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

@@ -465,9 +465,22 @@ __device__ __forceinline__ void merge_row(int n_parts, GetPart get, const float*
   den_out = den;
 }
 
+#ifdef FST_ATTN_TRACE
+__device__ long long g_merge_stamp[4];
+extern "C" int fst_debug_read_merge_stamp(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_merge_stamp, sizeof(long long) * 4);
+}
+#endif
+
 __global__ void __launch_bounds__(MERGE_THREADS) k_merge(MergeArgs a) {
+#ifdef FST_ATTN_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g_merge_stamp[0]) : : "memory");
+#endif
   pdl_launch();
   pdl_wait();
+#ifdef FST_ATTN_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g_merge_stamp[1]) : : "memory");
+#endif
   __shared__ __align__(16) float s_acc[8 * 512];
   __shared__ float s_red[32];
   const int r = blockIdx.x, t = r / a.H, h = r % a.H;

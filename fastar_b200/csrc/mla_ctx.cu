@@ -800,10 +800,10 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
   // runs of about equal COST; a run that crosses a token boundary yields one segment (and one
   // partial) per token it touches.  The unit is a cache page where pages hold 64 tokens, else
   // ATTN_TILE rows.  Cost, in half units: 2 per tile plus SEG_COST2 per segment -- a segment
-  // pays for loading Q_eff, refilling the pipeline and writing its partial (about three
-  // 64-token tiles of the streaming kernel).
+  // pays for loading Q_eff, refilling the pipeline and writing its partial (measured: about
+  // five and a half 64-token tiles of the streaming kernel).
   const int unit = c->cfg.page_tokens == 64 ? 64 : ATTN_TILE;
-  const long long SEG_COST2 = unit == 64 ? 6 : 3;
+  const long long SEG_COST2 = unit == 64 ? 11 : 5;
   long long total_tiles = 0, kv_rows = 0, n_nonempty = 0;
   for (int i = 0; i < T; ++i) {
     total_tiles += (kvlen[i] + unit - 1) / unit;
@@ -816,7 +816,6 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
     if (v > 0 && v < max_ctas) max_ctas = v;
   }
   const int n_ctas = (int)std::min<long long>(max_ctas, std::max<long long>(total_tiles, 1));
-  const long long total2 = 2 * total_tiles + SEG_COST2 * (n_nonempty + n_ctas - 1);
   std::vector<AttnSeg> segs;
   std::vector<int32_t> cta_seg(n_ctas + 1, 0);
   {
@@ -831,14 +830,22 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
       }
     };
     skip_empty();
-    long long spent = 0;
+    long long tiles_left = total_tiles, toks_left = n_nonempty;  // tokens not yet started
     for (int k = 0; k < n_ctas; ++k) {
       cta_seg[k] = (int)segs.size();
       const bool last = k == n_ctas - 1;
-      const long long target = (total2 * (k + 1)) / n_ctas;  // cumulative cost through this CTA
+      // what is left, shared equally among the CTAs that are left: the tiles, a segment for
+      // every token still to start (and for the one this CTA resumes), and one more segment
+      // for every later CTA, which will most likely resume a token
+      const long long mid = tile_in_tok > 0 ? 1 : 0;
+      const long long left2 = 2 * tiles_left + SEG_COST2 * (toks_left + mid + (n_ctas - k - 1));
+      long long budget2 = left2 / (n_ctas - k);
       while (tok < T) {
-        long long room = last ? (1ll << 40) : (target - spent - SEG_COST2) / 2;  // tiles that still fit
-        if (room < 1) break;
+        long long room = last ? (1ll << 40) : (budget2 - SEG_COST2) / 2;  // tiles that still fit
+        if (room < 1) {
+          if (cta_seg[k] != (int)segs.size()) break;
+          room = 1;  // every CTA takes at least one tile
+        }
         const int take = (int)std::min<long long>(room, tiles_of(tok) - tile_in_tok);
         AttnSeg sg;
         sg.tok = tok;
@@ -846,8 +853,10 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
         sg.kv_end = std::min(kvlen[tok], (tile_in_tok + take) * unit);
         sg.part = part++;
         segs.push_back(sg);
+        if (tile_in_tok == 0) --toks_left;
         tile_in_tok += take;
-        spent += SEG_COST2 + 2 * take;
+        tiles_left -= take;
+        budget2 -= SEG_COST2 + 2 * take;
         skip_empty();
       }
     }
