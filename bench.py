@@ -391,7 +391,7 @@ def main():
             "e2e": {"value": e2e, "unit": "layer-tokens/s", "h2d_bytes_per_step": int(h_host.numel() * 2),
                     "d2h_bytes_per_step": int(out_host.numel() * 2)},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "kernel": "k_attn_tc (split-KV latent attention)", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": "k_attn_stream (split-KV latent attention)", "achieved": achieved,
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peak if achieved else None, "traffic": traffic,
                          "algorithmic_bytes_per_launch": kv_bytes, "launch_ms": attn_ms / max(attn_n, 1),

@@ -21,7 +21,7 @@ LIB_ENGINE = os.path.join(PKG, "libfst_engine.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-cudart", "static"]
-CUDA_SOURCES = ["mla_ctx.cu", "kernels_simt.cu", "gemm_tc.cu", "attn_tc.cu", "attn_stream.cu", "no_alloc.cu"]
+CUDA_SOURCES = ["mla_ctx.cu", "kernels_simt.cu", "gemm_tc.cu", "attn_stream.cu", "no_alloc.cu"]
 
 
 def _newer(target: str, deps: list[str]) -> bool:

@@ -103,10 +103,7 @@ struct AttnArgs {
   float scale;
 };
 void launch_attn_simt(const AttnArgs& a, cudaStream_t st);
-bool attn_tc_supported(const AttnArgs& a);
-cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st);
-size_t attn_tc_smem_bytes(const AttnArgs& a);
-// Streaming kernel: 64-token tiles, Q_eff in tensor memory, ring of chunk slots.
+// tcgen05 kernel: a stream of 64-token tiles, Q_eff in tensor memory, ring of three tile frames.
 bool attn_stream_supported(const AttnArgs& a);
 cudaError_t launch_attn_stream(const AttnArgs& a, cudaStream_t st);
 

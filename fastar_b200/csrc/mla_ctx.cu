@@ -1,5 +1,5 @@
 // Context, paged-cache bookkeeping, split-KV planning and the C ABI of the MLA path.
-// Host-side logic only; the kernels live in kernels_simt.cu, gemm_tc.cu and attn_tc.cu.
+// Host-side logic only; the kernels live in kernels_simt.cu, gemm_tc.cu and attn_stream.cu.
 #include <algorithm>
 #include <cmath>
 #include <cstdarg>
@@ -294,14 +294,11 @@ AttnArgs attn_args(FstMlaCtx* c, int lid, const bf16* q_eff) {
 int run_attention(FstMlaCtx* c, int lid, const bf16* q_eff) {
   if (c->n_segs == 0) return FST_MLA_OK;
   AttnArgs a = attn_args(c, lid, q_eff);
-  const bool tc_ok = attn_tc_supported(a);
+  const bool tc_ok = attn_stream_supported(a);
   if (c->cfg.attn_impl == FST_MLA_IMPL_TENSOR && !tc_ok)
     return fail(FST_MLA_ERR_ARG, "this shape has no tcgen05 attention path");
   if (c->cfg.attn_impl != FST_MLA_IMPL_SIMT && tc_ok) {
-    // the streaming kernel; FST_MLA_ATTN_V1 in the environment selects the first-generation
-    // kernel (128-token tiles, Q_eff in shared memory), for comparisons
-    static const bool v1 = getenv("FST_MLA_ATTN_V1") != nullptr;
-    cudaError_t e = (!v1 && attn_stream_supported(a)) ? launch_attn_stream(a, c->stream) : launch_attn_tc(a, c->stream);
+    cudaError_t e = launch_attn_stream(a, c->stream);
     if (e != cudaSuccess) return fail(FST_MLA_ERR_CUDA, "tcgen05 attention launch: %s", cudaGetErrorString(e));
   } else {
     launch_attn_simt(a, c->stream);
