@@ -32,6 +32,8 @@
 #include "kernels.cuh"
 #include "tc_common.cuh"
 
+FST_TL_DEFINE(attn)
+
 namespace fst {
 
 namespace {
@@ -221,6 +223,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
   StreamMisc* mi = reinterpret_cast<StreamMisc*>(smem + off_misc(NCH));
   volatile int* abort_flag = &mi->abort_flag;
 
+  FST_TL_BEGIN();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seg0 = p.cta_seg[blockIdx.x], seg1 = p.cta_seg[blockIdx.x + 1];
 #ifdef FST_ATTN_TRACE
@@ -229,6 +232,11 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
     g_st_cta[blockIdx.x * 8 + 4] = clock64();
   }
   ST_CTA(3, (long long)(seg1 - seg0));
+  {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    ST_CTA(7, (long long)smid);
+  }
 #endif
 
   if (threadIdx.x == 0) {
@@ -560,6 +568,8 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem, TMEM_COLS);
   }
+  __syncthreads();
+  FST_TL_END(attn, 4);
 }
 
 }  // namespace

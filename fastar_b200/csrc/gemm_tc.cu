@@ -18,6 +18,8 @@
 #include "kernels.cuh"
 #include "tc_common.cuh"
 
+FST_TL_DEFINE(gemm)
+
 namespace fst {
 
 namespace {
@@ -35,6 +37,11 @@ struct GemmTcParams {
   long long c_bs;
   int splits, kc_total, stages;
   int w_swap, a_swap;  // the batch index is the middle tensor-map coordinate (its stride is the smaller one)
+  // side job (GemmArgs::rope_*): null source = none
+  const bf16* rope_src;
+  const float* rope_lut;
+  bf16* rope_dst;
+  int rope_T, rope_H, rope_q_head, rope_nope, rope_dims, rope_d_qk;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -62,6 +69,7 @@ __device__ __forceinline__ float4 ld_peer_f32x4(uint32_t local_addr, uint32_t ra
 template <int NT, bool W_KN>
 __global__ void __launch_bounds__(GEMM_THREADS, 2)
 k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA, GemmTcParams p) {
+  FST_TL_BEGIN();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   constexpr int A_BYTES = NT * BK * 2;
   constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
@@ -168,6 +176,35 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
   } else {
     // epilogue warps: TMEM lane quadrant = warp % 4; thread = one weight row n
     pdl_wait();
+    if (p.rope_src && blockIdx.x == 0 && blockIdx.y == 0) {
+      // side job while the accumulator is being built: RoPE of head z's rope pairs, all tokens
+      const int half = p.rope_dims / 2, et = threadIdx.x - 64;  // 128 epilogue threads
+      const int n_items = p.rope_T * half;
+      for (int i0 = et; i0 < n_items; i0 += 8 * (GEMM_THREADS - 64)) {
+        // eight items per thread and round, all loads before the first store
+        __nv_bfloat162 x[8];
+        float2 cs[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * (GEMM_THREADS - 64);
+          if (i < n_items) {
+            const int t = i / half, pr = i % half;
+            x[u] = *reinterpret_cast<const __nv_bfloat162*>(p.rope_src + ((long long)t * p.rope_H + z) * p.rope_q_head + p.rope_nope + 2 * pr);
+            cs[u] = *reinterpret_cast<const float2*>(p.rope_lut + (long long)t * p.rope_dims + 2 * pr);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * (GEMM_THREADS - 64);
+          if (i < n_items) {
+            const int t = i / half, pr = i % half;
+            const float x0 = __low2float(x[u]), x1 = __high2float(x[u]);
+            *reinterpret_cast<__nv_bfloat162*>(p.rope_dst + ((long long)t * p.rope_H + z) * p.rope_d_qk + p.rope_d_qk - p.rope_dims + 2 * pr) =
+                __floats2bfloat162_rn(x0 * cs[u].x - x1 * cs[u].y, x0 * cs[u].y + x1 * cs[u].x);
+          }
+        }
+      }
+    }
     const int quad = warp & 3;
     bool ok = n_kc == 0 || tc::mbar_wait(acc_bar, 0, abort_flag, p.d_status, ST_EPI_TIMEOUT);
     ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
@@ -243,6 +280,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem, TMEM_COLS);
   }
+  FST_TL_END(gemm, 100000 + p.N);
 }
 
 int pick_nt(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
@@ -317,6 +355,9 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, int* d_status, cudaStream_t st) {
   p.C = g.C; p.d_status = d_status;
   p.M = g.M; p.N = g.N; p.K = g.K; p.ldc = g.ldc; p.c_bs = g.c_bs;
   p.splits = splits; p.kc_total = kc_total; p.w_swap = w_swap; p.a_swap = a_swap;
+  p.rope_src = g.rope_src; p.rope_lut = g.rope_lut; p.rope_dst = g.rope_dst;
+  p.rope_T = g.rope_T; p.rope_H = g.rope_H; p.rope_q_head = g.rope_q_head; p.rope_nope = g.rope_nope;
+  p.rope_dims = g.rope_dims; p.rope_d_qk = g.rope_d_qk;
   const int stage_bytes = W_BYTES + NT * BK * 2;
   p.stages = std::max(2, std::min(8, (96 * 1024) / stage_bytes));
   const size_t ring = (size_t)p.stages * stage_bytes, red = splits > 1 ? (size_t)NT * W_TILE * 4 : 0;

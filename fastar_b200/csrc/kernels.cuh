@@ -54,6 +54,15 @@ struct GemmArgs {
   int batch;
   long long a_bs, b_bs, c_bs;  // element strides between batch members
   int b_kn;
+  // Optional side job of the tcgen05 kernel (null: none): while the tensor pipe works, the idle
+  // epilogue warps of batch member z's first CTA rotate the rope pairs of head z for every
+  // token: src[(t*H + z)*q_head + nope + 2p ..] -> dst[(t*H + z)*d_qk + d_qk - rope + 2p ..].
+  // This is the BASELINE q_pe RoPE (reference src/fst_engine.cpp:2025-2058), which depends on
+  // the same input as the absorb GEMM and writes other columns of the same output.
+  const bf16* rope_src = nullptr;
+  const float* rope_lut = nullptr;  // [T, rope] (cos, sin) pairs
+  bf16* rope_dst = nullptr;
+  int rope_T = 0, rope_H = 0, rope_q_head = 0, rope_nope = 0, rope_dims = 0, rope_d_qk = 0;
 };
 void launch_gemm_simt(const GemmArgs& g, cudaStream_t st);
 // tcgen05 path: B in [N, K] layout only, K % 64 == 0, N % 128 == 0, 16-byte aligned rows.

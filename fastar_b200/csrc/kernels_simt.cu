@@ -3,6 +3,8 @@
 // kernels do not apply (odd shapes, the [K,N] absorb operand) and for bisecting.
 #include "kernels.cuh"
 
+FST_TL_DEFINE(simt)
+
 namespace fst {
 
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
@@ -117,55 +119,83 @@ void launch_gemm_simt(const GemmArgs& g, cudaStream_t st) {
 // ---- q_norm / kv_norm / key RoPE / cache append -------------------------------------------
 // Reference src/fst_engine.cpp:3385-3394 (norms), 3504-3517 (RoPE on the key), 3534-3544
 // (cache push).  One block per new token.  RMSNorm follows rms_cpu (89-91).
+// Every global load of a block (its row of the compressed activations, the norm weights, the RoPE
+// table, the destination) is issued before anything is reduced, and the two sums of squares
+// share one exchange: the kernel is one memory round trip and one block reduction long.
 __global__ void __launch_bounds__(256) k_norm_append(NormAppendArgs a) {
+  FST_TL_BEGIN();
   pdl_launch();
   pdl_wait();
   extern __shared__ float s_row[];  // [row]
-  __shared__ float scratch[32];
-  const int t = blockIdx.x;
+  __shared__ float scratch[2][32];
+  constexpr int QMAX = 8, KMAX = 4;  // q_lora <= 2048, row <= 1024 (checked by the launcher)
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
   const bf16* in = a.cmp + (long long)t * (a.q_lora + a.row);
-  // q_norm
-  float ss = 0.0f;
-  for (int j = threadIdx.x; j < a.q_lora; j += blockDim.x) {
-    const float x = bf2f(in[j]);
-    ss += x * x;
-  }
-  ss = block_sum(ss, scratch);
-  float r = 1.0f / sqrtf(ss / (float)a.q_lora + a.eps);
-  for (int j = threadIdx.x; j < a.q_lora; j += blockDim.x) {
-    const float x = bf2f(in[j]);
-    a.qc[(long long)t * a.q_lora + j] = f2bf(a.q_norm ? x * r * bf2f(a.q_norm[j]) : x);
-  }
-  // kv_norm over the kv_lora latent; trailing dims (BASELINE k_pe) pass through
   const bf16* kin = in + a.q_lora;
-  ss = 0.0f;
-  for (int j = threadIdx.x; j < a.kv_lora; j += blockDim.x) {
-    const float x = bf2f(kin[j]);
-    ss += x * x;
+  float xq[QMAX], wq[QMAX], xk[KMAX], wk[KMAX];
+#pragma unroll
+  for (int i = 0; i < QMAX; ++i) {
+    const int j = tid + i * 256;
+    xq[i] = j < a.q_lora ? bf2f(in[j]) : 0.0f;
+    wq[i] = (j < a.q_lora && a.q_norm) ? bf2f(a.q_norm[j]) : 1.0f;
   }
-  ss = block_sum(ss, scratch);
-  r = 1.0f / sqrtf(ss / (float)a.kv_lora + a.eps);
-  for (int j = threadIdx.x; j < a.row; j += blockDim.x) {
-    const float x = bf2f(kin[j]);
-    s_row[j] = (j < a.kv_lora && a.kv_norm) ? rbf(x * r * bf2f(a.kv_norm[j])) : x;
+#pragma unroll
+  for (int i = 0; i < KMAX; ++i) {
+    const int j = tid + i * 256;
+    xk[i] = j < a.row ? bf2f(kin[j]) : 0.0f;
+    wk[i] = (j < a.kv_lora && a.kv_norm) ? bf2f(a.kv_norm[j]) : 1.0f;
+  }
+  const float* lut = a.lut + (long long)t * a.rope;
+  float lc = 0.0f, ls = 0.0f;
+  if (tid < a.rope / 2) {
+    lc = lut[2 * tid];
+    ls = lut[2 * tid + 1];
+  }
+  const long long dst = a.dst_row[t];
+  // sums of squares: q over q_lora, kv over the kv_lora latent (trailing dims pass through)
+  float sq = 0.0f, sk = 0.0f;
+#pragma unroll
+  for (int i = 0; i < QMAX; ++i) sq += xq[i] * xq[i];  // absent elements are 0
+#pragma unroll
+  for (int i = 0; i < KMAX; ++i)
+    if (tid + i * 256 < a.kv_lora) sk += xk[i] * xk[i];
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  if (lane == 0) {
+    scratch[0][wid] = sq;
+    scratch[1][wid] = sk;
+  }
+  __syncthreads();
+  sq = warp_sum(lane < nw ? scratch[0][lane] : 0.0f);
+  sk = warp_sum(lane < nw ? scratch[1][lane] : 0.0f);
+  const float rq = 1.0f / sqrtf(sq / (float)a.q_lora + a.eps);
+  const float rk = 1.0f / sqrtf(sk / (float)a.kv_lora + a.eps);
+#pragma unroll
+  for (int i = 0; i < QMAX; ++i) {
+    const int j = tid + i * 256;
+    if (j < a.q_lora) a.qc[(long long)t * a.q_lora + j] = f2bf(a.q_norm ? xq[i] * rq * wq[i] : xq[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < KMAX; ++i) {
+    const int j = tid + i * 256;
+    if (j < a.row) s_row[j] = (j < a.kv_lora && a.kv_norm) ? rbf(xk[i] * rk * wk[i]) : xk[i];
   }
   __syncthreads();
   // RoPE on the last `rope` dims of the row, interleaved pairs (ew_rope,
   // reference kernels/fst_ew_unified_kernel.cc:200-217)
-  const float* lut = a.lut + (long long)t * a.rope;
-  for (int p = threadIdx.x; p < a.rope / 2; p += blockDim.x) {
-    const int j = a.row - a.rope + 2 * p;
-    const float c = lut[2 * p], s = lut[2 * p + 1], x0 = s_row[j], x1 = s_row[j + 1];
-    s_row[j] = x0 * c - x1 * s;
-    s_row[j + 1] = x0 * s + x1 * c;
+  if (tid < a.rope / 2) {
+    const int j = a.row - a.rope + 2 * tid;
+    const float x0 = s_row[j], x1 = s_row[j + 1];
+    s_row[j] = x0 * lc - x1 * ls;
+    s_row[j + 1] = x0 * ls + x1 * lc;
   }
   __syncthreads();
-  const long long dst = a.dst_row[t];
-  for (int j = threadIdx.x; j < a.row; j += blockDim.x) {
+  for (int j = tid; j < a.row; j += blockDim.x) {
     const bf16 v = f2bf(s_row[j]);
     a.kv_new[(long long)t * a.row + j] = v;
     if (dst >= 0) a.pool[dst + j] = v;
   }
+  FST_TL_END(simt, 1);
 }
 
 void launch_norm_append(const NormAppendArgs& a, cudaStream_t st) {
@@ -178,6 +208,7 @@ void launch_norm_append(const NormAppendArgs& a, cudaStream_t st) {
 // (rope_qpe_all_heads, reference src/fst_engine.cpp:2025-2058; the absorb GEMM fills the rest).
 // V4: per-head weightless RMSNorm (3487-3495), then the tail rotation (3503).
 __global__ void __launch_bounds__(128) k_q_prep(QPrepArgs a) {
+  FST_TL_BEGIN();
   pdl_launch();
   pdl_wait();
   __shared__ float scratch[32];
@@ -212,11 +243,36 @@ __global__ void __launch_bounds__(128) k_q_prep(QPrepArgs a) {
       out[a.d_qk - a.rope + 2 * p + 1] = f2bf(x0 * s + x1 * c);
     }
   }
+  FST_TL_END(simt, 2);
+}
+
+// BASELINE only: one block per token rotates the rope pairs of all its heads (a pair per thread
+// and step) -- a handful of fat blocks instead of T * H blocks of 32 busy threads.
+__global__ void __launch_bounds__(256) k_q_rope_token(QPrepArgs a) {
+  FST_TL_BEGIN();
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x, half = a.rope / 2;
+  const float* lut = a.lut + (long long)t * a.rope;
+  for (int i = threadIdx.x; i < a.H * half; i += blockDim.x) {
+    const int h = i / half, p = i % half;
+    const bf16* in = a.q_full + ((long long)t * a.H + h) * a.q_head + a.nope + 2 * p;
+    bf16* out = a.q_eff + ((long long)t * a.H + h) * a.d_qk + a.d_qk - a.rope + 2 * p;
+    const float c = lut[2 * p], s = lut[2 * p + 1];
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(in);
+    const float x0 = __low2float(x), x1 = __high2float(x);
+    *reinterpret_cast<__nv_bfloat162*>(out) = __floats2bfloat162_rn(x0 * c - x1 * s, x0 * s + x1 * c);
+  }
+  FST_TL_END(simt, 2);
 }
 
 void launch_q_prep(const QPrepArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
-  launch_pdl(k_q_prep, dim3(a.T * a.H), dim3(128), 0, st, 1, a);
+  // (pair accesses need even offsets: q_head, nope, d_qk and rope are even in both presets)
+  if (!a.v4 && a.q_head % 2 == 0 && a.nope % 2 == 0 && a.d_qk % 2 == 0 && a.rope % 2 == 0)
+    launch_pdl(k_q_rope_token, dim3(a.T), dim3(256), 0, st, 1, a);
+  else
+    launch_pdl(k_q_prep, dim3(a.T * a.H), dim3(128), 0, st, 1, a);
 }
 
 // ---- split-KV attention on CUDA cores -----------------------------------------------------
@@ -473,6 +529,7 @@ extern "C" int fst_debug_read_merge_stamp(long long* out) {
 #endif
 
 __global__ void __launch_bounds__(MERGE_THREADS) k_merge(MergeArgs a) {
+  FST_TL_BEGIN();
 #ifdef FST_ATTN_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g_merge_stamp[0]) : : "memory");
 #endif
@@ -503,10 +560,100 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge(MergeArgs a) {
   const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
   for (int j = threadIdx.x; j < a.d_v; j += blockDim.x) s_acc[j] = rbf(s_acc[j] * inv);
   finish_row(s_acc, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope, a.inv_rope);
+  FST_TL_END(simt, 3);
+}
+
+// Rows with few parts: one WARP per query row (token, head), eight rows per block, nothing
+// shared.  A lane owns columns lane*4 + 128*j and walks the parts in order, so the arithmetic per
+// column is that of the 128-thread mode of merge_row.
+__global__ void __launch_bounds__(256) k_merge_rows(MergeArgs a) {
+  FST_TL_BEGIN();
+  pdl_launch();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + warp;
+  if (r < a.T * a.H) {
+    const int t = r / a.H, h = r % a.H;
+    const int p0 = a.tok_part[t], n_parts = a.tok_part[t + 1] - p0;
+    const bool sk = a.sinks != nullptr;
+    float M = sk ? a.sinks[h] : -INFINITY;
+    for (int p = 0; p < n_parts; ++p) M = fmaxf(M, a.part_m[(long long)(p0 + p) * a.H + h]);
+    float den = sk ? expf(a.sinks[h] - M) : 0.0f;
+    float acc[16];
+#pragma unroll
+    for (int c = 0; c < 16; ++c) acc[c] = 0.0f;
+    for (int p = 0; p < n_parts; ++p) {
+      const long long i = (long long)(p0 + p) * a.H + h;
+      const float m = a.part_m[i];
+      if (m == -INFINITY) continue;
+      const float w = expf(m - M);
+      den += w * a.part_l[i];
+      const float* o = a.part_o + i * a.d_v;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int col = lane * 4 + 128 * j;
+        if (col < a.d_v) {
+          const float4 v = *reinterpret_cast<const float4*>(o + col);
+          acc[4 * j] = fmaf(w, v.x, acc[4 * j]);
+          acc[4 * j + 1] = fmaf(w, v.y, acc[4 * j + 1]);
+          acc[4 * j + 2] = fmaf(w, v.z, acc[4 * j + 2]);
+          acc[4 * j + 3] = fmaf(w, v.w, acc[4 * j + 3]);
+        }
+      }
+    }
+    if (a.mode == 1) {
+      float* o = a.rank_partial + (long long)r * (2 + a.d_v);
+      if (lane == 0) {
+        o[0] = M;
+        o[1] = den;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int col = lane * 4 + 128 * j;
+        if (col < a.d_v) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[2 + col + e] = acc[4 * j + e];
+        }
+      }
+    } else {
+      const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
+      const float* lut = a.lut + (long long)t * a.rope;
+      bf16* o_row = a.o_lat + (long long)r * a.d_v;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int col = lane * 4 + 128 * j;
+        if (col < a.d_v) {
+          float v[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[e] = rbf(acc[4 * j + e] * inv);
+          if (a.inv_rope && col >= a.d_v - a.rope) {
+            // inverse RoPE of the rounded output tail (reference src/fst_engine.cpp:3716)
+#pragma unroll
+            for (int e = 0; e < 4; e += 2) {
+              const int pr = (col + e - (a.d_v - a.rope)) / 2;
+              const float c = lut[2 * pr], s = -lut[2 * pr + 1], x0 = v[e], x1 = v[e + 1];
+              v[e] = x0 * c - x1 * s;
+              v[e + 1] = x0 * s + x1 * c;
+            }
+          }
+          __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+          uint2 pk;
+          pk.x = *reinterpret_cast<uint32_t*>(&lo);
+          pk.y = *reinterpret_cast<uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(o_row + col) = pk;
+        }
+      }
+    }
+  }
+  FST_TL_END(simt, 3);
 }
 
 void launch_merge(const MergeArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
+  if (a.threads == 128 && a.d_v <= 512 && a.d_v % 4 == 0 && (a.rope % 2) == 0 && ((a.d_v - a.rope) % 4) == 0) {
+    launch_pdl(k_merge_rows, dim3((a.T * a.H + 7) / 8), dim3(256), 0, st, 1, a);
+    return;
+  }
   launch_pdl(k_merge, dim3(a.T * a.H), dim3(a.threads == 128 ? 128 : MERGE_THREADS), 0, st, 1, a);
 }
 

@@ -330,9 +330,10 @@ int run_front(FstMlaCtx* c, int lid, const bf16* h_in) {
   qp.q_full = c->d_qfull; qp.lut = c->d_lut; qp.q_eff = c->d_qeff;
   qp.T = T; qp.H = d.H; qp.q_head = d.q_head; qp.nope = d.nope; qp.rope = d.rope; qp.d_qk = d.d_qk;
   qp.v4 = d.v4; qp.eps = c->cfg.rms_eps;
-  launch_q_prep(qp, c->stream);
-  c->launches += 1;
-  if (!d.v4) {
+  if (d.v4) {
+    launch_q_prep(qp, c->stream);
+    c->launches += 1;
+  } else {
     // q_lat[h] = q_nope[h] (128) * W_UK[h] ([128, 512], a [K, N] operand), one batch member per head
     GemmArgs g;
     g.A = c->d_qfull; g.B = w.wkv_b; g.C = c->d_qeff;
@@ -340,6 +341,17 @@ int run_front(FstMlaCtx* c, int lid, const bf16* h_in) {
     g.lda = d.H * d.q_head; g.ldb = d.kv_lora; g.ldc = d.H * d.d_qk;
     g.batch = d.H; g.a_bs = d.q_head; g.b_bs = (long long)(d.nope + d.v_head) * d.kv_lora; g.c_bs = d.d_qk;
     g.b_kn = 1;
+    const bool even = d.q_head % 2 == 0 && d.nope % 2 == 0 && d.d_qk % 2 == 0 && d.rope % 2 == 0;
+    if (use_tc_gemm(c, g) && even) {
+      // the q_pe RoPE rides in the same kernel: it reads the same input and fills the other
+      // columns of q_eff, and a kernel boundary costs more than the rotation itself
+      g.rope_src = c->d_qfull; g.rope_lut = c->d_lut; g.rope_dst = c->d_qeff;
+      g.rope_T = T; g.rope_H = d.H; g.rope_q_head = d.q_head; g.rope_nope = d.nope; g.rope_dims = d.rope;
+      g.rope_d_qk = d.d_qk;
+    } else {
+      launch_q_prep(qp, c->stream);
+      c->launches += 1;
+    }
     if ((rc = run_gemm(c, g))) return rc;
   }
   return FST_MLA_OK;
@@ -417,6 +429,8 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
   Dims d = dims_of(c);
   if (d.row % 8 || d.d_qk % 8 || d.d_v % 64 || d.d_v > 512 || d.q_head > 1024 || d.row > 1024)
     return fail(FST_MLA_ERR_ARG, "row width must be a multiple of 8 and d_v a multiple of 64 (<= 512)");
+  if (c.q_lora > 2048 || c.qk_rope > 512)
+    return fail(FST_MLA_ERR_ARG, "q_lora above 2048 or rope dims above 512: beyond the register tile of the norm kernel");
   if (c.softmax_scale <= 0)
     c.softmax_scale = 1.0f / std::sqrt((float)(d.v4 ? c.kv_lora : c.qk_nope + c.qk_rope));
   if (c.rope_theta <= 0) c.rope_theta = 10000.0f;
