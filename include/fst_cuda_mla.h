@@ -175,7 +175,9 @@ int fst_cuda_mla_plan(FstMlaCtx* ctx, const FstMlaSeqStep* steps, int32_t n_seqs
 int fst_cuda_mla_run_device(FstMlaCtx* ctx, int lid, const void* d_h_in, void* d_h_out);
 /* process_mla with host buffers, as the engine calls it: plan + H2D + run + D2H + sync.
  * h_in / h_out are host bf16 [sum q_lens, hidden] (may alias: the reference works in place,
- * src/fst_engine.cpp:3889).  Rows are written at pos0[b] .. pos0[b]+q_lens[b]-1. */
+ * src/fst_engine.cpp:3889).  Rows are written at pos0[b] .. pos0[b]+q_lens[b]-1.
+ * Page-locked buffers (cudaHostAlloc / cudaHostRegister) are copied directly; pageable ones
+ * go through a page-locked staging buffer of the context, which costs two extra memcpy. */
 int fst_cuda_mla_forward(FstMlaCtx* ctx, int lid, const uint16_t* h_in, uint16_t* h_out,
                          const int32_t* seq_ids, const int32_t* pos0, const int32_t* q_lens,
                          int32_t n_seqs, int32_t causal);
