@@ -98,6 +98,7 @@ struct FstMlaCtx {
 
   int64_t launches = 0;
   bool profiling = false;
+  bool compress_done = false;  // fst_cuda_mla_forward has launched the compress GEMM of this call already
   std::vector<EventSet> ev_pool;
   int ev_used = 0;
   float k_ms[FST_MLA_K_COUNT] = {0};
@@ -313,7 +314,8 @@ int run_front(FstMlaCtx* c, int lid, const bf16* h_in) {
   const int T = c->T;
   int rc;
   prof_mark(c, FST_MLA_K_COMPRESS);
-  if ((rc = run_gemm(c, plain_gemm(h_in, w.w_cmp, c->d_cmp, T, d.cmp_n, d.hidden)))) return rc;
+  if (!c->compress_done && (rc = run_gemm(c, plain_gemm(h_in, w.w_cmp, c->d_cmp, T, d.cmp_n, d.hidden)))) return rc;
+  c->compress_done = false;
   prof_mark(c, FST_MLA_K_NORM_APPEND);
   NormAppendArgs na;
   na.cmp = c->d_cmp; na.q_norm = w.q_norm; na.kv_norm = w.kv_norm; na.lut = c->d_lut;
@@ -949,12 +951,11 @@ int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* 
   if (!c || !h_in || !h_out || !seq_ids || !pos0 || !q_lens) return fail(FST_MLA_ERR_ARG, "null argument");
   if (n_seqs < 0) return fail(FST_MLA_ERR_ARG, "negative sequence count");
   std::vector<FstMlaSeqStep> steps(n_seqs);
-  for (int b = 0; b < n_seqs; ++b) steps[b] = FstMlaSeqStep{seq_ids[b], pos0[b], q_lens[b], -1, 1};
-  int rc = fst_cuda_mla_plan(c, steps.data(), n_seqs, causal);
-  if (rc) return rc;
-  if ((rc = check_run(c, lid))) return rc;
-  if (c->T == 0) return FST_MLA_OK;
-  const size_t bytes = (size_t)c->T * c->d.hidden * sizeof(uint16_t);
+  long long T_in = 0;
+  for (int b = 0; b < n_seqs; ++b) {
+    steps[b] = FstMlaSeqStep{seq_ids[b], pos0[b], q_lens[b], -1, 1};
+    if (q_lens[b] > 0) T_in += q_lens[b];
+  }
   // page-locked caller buffers are copied directly; pageable ones go through the context's
   // page-locked staging buffer (an asynchronous copy from pageable memory is neither)
   auto page_locked = [](const void* p) {
@@ -965,9 +966,32 @@ int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* 
     }
     return at.type == cudaMemoryTypeHost;
   };
+  // the input rows start their way to the device before the plan is built (the plan takes tens
+  // of microseconds of host time and does not depend on them)
+  const bool early = T_in > 0 && T_in <= c->cfg.max_tokens;
+  const size_t bytes_in = (size_t)T_in * c->d.hidden * sizeof(uint16_t);
   const bool in_direct = page_locked(h_in), out_direct = page_locked(h_out);
-  if (!in_direct) memcpy(c->h_pinned, h_in, bytes);
-  CU(cudaMemcpyAsync(c->d_h, in_direct ? (const void*)h_in : (const void*)c->h_pinned, bytes, cudaMemcpyHostToDevice, c->stream));
+  c->compress_done = false;
+  if (early) {
+    CU(cudaSetDevice(c->cfg.device));
+    if (!in_direct) memcpy(c->h_pinned, h_in, bytes_in);
+    CU(cudaMemcpyAsync(c->d_h, in_direct ? (const void*)h_in : (const void*)c->h_pinned, bytes_in, cudaMemcpyHostToDevice, c->stream));
+    // ... and so does the first GEMM of the layer (q / kv compression), which needs the rows and
+    // the weights but nothing of the plan
+    if (!c->profiling && lid >= 0 && lid < c->cfg.n_layers && c->layers[lid].set) {
+      int rc0 = run_gemm(c, plain_gemm(c->d_h, c->layers[lid].w_cmp, c->d_cmp, (int)T_in, c->d.cmp_n, c->d.hidden));
+      if (rc0) return rc0;
+      c->compress_done = true;
+    }
+  }
+  int rc = fst_cuda_mla_plan(c, steps.data(), n_seqs, causal);
+  if (rc) {
+    c->compress_done = false;
+    return rc;
+  }
+  if ((rc = check_run(c, lid))) return rc;
+  if (c->T == 0) return FST_MLA_OK;
+  const size_t bytes = (size_t)c->T * c->d.hidden * sizeof(uint16_t);
   if ((rc = fst_cuda_mla_run_device(c, lid, c->d_h, c->d_out))) return rc;
   CU(cudaMemcpyAsync(out_direct ? (void*)h_out : (void*)c->h_pinned, c->d_out, bytes, cudaMemcpyDeviceToHost, c->stream));
   if ((rc = fst_cuda_mla_sync(c))) return rc;
