@@ -70,6 +70,10 @@ bool gemm_tc_supported(const GemmArgs& g);
 // Returns cudaSuccess or the error of building the tensor maps / launching.
 cudaError_t launch_gemm_tc(const GemmArgs& g, int* d_status, cudaStream_t st);
 
+// y[t] = x[t] * w / sqrt(mean(x[t]^2) + eps) over `dim` (<= 8192) elements, rounded to bf16: the
+// attn_norm of process_layer (reference src/fst_engine.cpp:2687-2688).
+void launch_rmsnorm_rows(const bf16* x, const bf16* w, bf16* y, int T, int dim, float eps, cudaStream_t st);
+
 // RMSNorm(q) -> qc; RMSNorm(latent) (+ RoPE on the key's rope dims) -> kv_new and the cache row.
 struct NormAppendArgs {
   const bf16* cmp;      // [T, q_lora + row]

@@ -116,6 +116,37 @@ void launch_gemm_simt(const GemmArgs& g, cudaStream_t st) {
     launch_pdl(k_gemm_nk<false>, grid, dim3(128), 0, st, 1, g);
 }
 
+// ---- attn_norm ---------------------------------------------------------------------------------
+// One block per row; the row is loaded once (up to 32 elements per thread) and reduced once.
+__global__ void __launch_bounds__(256) k_rmsnorm_rows(const bf16* x, const bf16* w, bf16* y, int dim, float eps) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const bf16* in = x + (long long)t * dim;
+  float v[32], g[32];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int j = tid + i * 256;
+    v[i] = j < dim ? bf2f(in[j]) : 0.0f;
+    g[i] = j < dim ? bf2f(w[j]) : 0.0f;
+    ss += v[i] * v[i];
+  }
+  ss = block_sum(ss, scratch);
+  const float r = 1.0f / sqrtf(ss / (float)dim + eps);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int j = tid + i * 256;
+    if (j < dim) y[(long long)t * dim + j] = f2bf(v[i] * r * g[i]);
+  }
+}
+
+void launch_rmsnorm_rows(const bf16* x, const bf16* w, bf16* y, int T, int dim, float eps, cudaStream_t st) {
+  if (T <= 0) return;
+  launch_pdl(k_rmsnorm_rows, dim3(T), dim3(256), 0, st, 1, x, w, y, dim, eps);
+}
+
 // ---- q_norm / kv_norm / key RoPE / cache append -------------------------------------------
 // Reference src/fst_engine.cpp:3385-3394 (norms), 3504-3517 (RoPE on the key), 3534-3544
 // (cache push).  One block per new token.  RMSNorm follows rms_cpu (89-91).

@@ -44,6 +44,7 @@ struct Dims {
 struct LayerW {
   bf16 *w_cmp = nullptr, *wq_b = nullptr, *wkv_b = nullptr, *wo_a = nullptr, *wo_b = nullptr;
   bf16 *q_norm = nullptr, *kv_norm = nullptr;
+  bf16* attn_norm = nullptr;  // [hidden] or null: the norm in front of the layer
   float* sinks = nullptr;
   bool set = false;
 };
@@ -73,6 +74,7 @@ struct FstMlaCtx {
   std::vector<char> live;
 
   // workspaces
+  bf16* d_an = nullptr;  // [T, hidden] rows after attn_norm (layers that carry the weight)
   bf16 *d_h = nullptr, *d_cmp = nullptr, *d_qc = nullptr, *d_kvnew = nullptr, *d_qfull = nullptr;
   bf16 *d_qeff = nullptr, *d_olat = nullptr, *d_low = nullptr, *d_out = nullptr;
   float *d_part_m = nullptr, *d_part_l = nullptr, *d_part_o = nullptr;
@@ -314,6 +316,12 @@ int run_front(FstMlaCtx* c, int lid, const bf16* h_in) {
   const int T = c->T;
   int rc;
   prof_mark(c, FST_MLA_K_COMPRESS);
+  if (w.attn_norm && !c->compress_done) {
+    // attn_norm of process_layer (reference 2687-2688) in front of the compressions
+    launch_rmsnorm_rows(h_in, w.attn_norm, c->d_an, T, d.hidden, c->cfg.rms_eps, c->stream);
+    c->launches += 1;
+    h_in = c->d_an;
+  }
   if (!c->compress_done && (rc = run_gemm(c, plain_gemm(h_in, w.w_cmp, c->d_cmp, T, d.cmp_n, d.hidden)))) return rc;
   c->compress_done = false;
   prof_mark(c, FST_MLA_K_NORM_APPEND);
@@ -430,8 +438,8 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
   Dims d = dims_of(c);
   if (d.row % 8 || d.d_qk % 8 || d.d_v % 64 || d.d_v > 512 || d.q_head > 1024 || d.row > 1024)
     return fail(FST_MLA_ERR_ARG, "row width must be a multiple of 8 and d_v a multiple of 64 (<= 512)");
-  if (c.q_lora > 2048 || c.qk_rope > 512)
-    return fail(FST_MLA_ERR_ARG, "q_lora above 2048 or rope dims above 512: beyond the register tile of the norm kernel");
+  if (c.q_lora > 2048 || c.qk_rope > 512 || c.hidden > 8192)
+    return fail(FST_MLA_ERR_ARG, "q_lora above 2048, rope dims above 512 or hidden above 8192: beyond the register tiles of the norm kernels");
   if (c.softmax_scale <= 0)
     c.softmax_scale = 1.0f / std::sqrt((float)(d.v4 ? c.kv_lora : c.qk_nope + c.qk_rope));
   if (c.rope_theta <= 0) c.rope_theta = 10000.0f;
@@ -474,6 +482,7 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
   x->max_parts = x->n_sm + (int)T;
   if (!rc) rc = dev_alloc(&x->d_h, T * d.hidden);
   if (!rc) rc = dev_alloc(&x->d_cmp, T * d.cmp_n);
+  if (!rc) rc = dev_alloc(&x->d_an, T * d.hidden);
   if (!rc) rc = dev_alloc(&x->d_qc, T * d.q_lora);
   if (!rc) rc = dev_alloc(&x->d_kvnew, T * d.row);
   if (!rc) rc = dev_alloc(&x->d_qfull, T * d.H * d.q_head);
@@ -514,9 +523,10 @@ void fst_cuda_mla_destroy(FstMlaCtx* c) {
   cudaDeviceSynchronize();
   for (auto& l : c->layers) {
     cudaFree(l.w_cmp); cudaFree(l.wq_b); cudaFree(l.wkv_b); cudaFree(l.wo_a); cudaFree(l.wo_b);
-    cudaFree(l.q_norm); cudaFree(l.kv_norm); cudaFree(l.sinks);
+    cudaFree(l.q_norm); cudaFree(l.kv_norm); cudaFree(l.sinks); cudaFree(l.attn_norm);
   }
   for (auto p : c->pools) cudaFree(p);
+  cudaFree(c->d_an);
   cudaFree(c->d_h); cudaFree(c->d_cmp); cudaFree(c->d_qc); cudaFree(c->d_kvnew); cudaFree(c->d_qfull);
   cudaFree(c->d_qeff); cudaFree(c->d_olat); cudaFree(c->d_low); cudaFree(c->d_out);
   cudaFree(c->d_part_m); cudaFree(c->d_part_l); cudaFree(c->d_part_o);
@@ -585,6 +595,12 @@ int fst_cuda_mla_set_layer_weights(FstMlaCtx* c, int lid, const FstMlaWeights* w
   } else if (L.kv_norm) {
     cudaFree(L.kv_norm);
     L.kv_norm = nullptr;
+  }
+  if (w->attn_norm) {
+    if ((rc = up(&L.attn_norm, w->attn_norm, d.hidden))) return rc;
+  } else if (L.attn_norm) {
+    cudaFree(L.attn_norm);
+    L.attn_norm = nullptr;
   }
   if (d.v4) {
     if (!L.sinks && (rc = dev_alloc(&L.sinks, (size_t)d.H))) return rc;
@@ -978,7 +994,7 @@ int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* 
     CU(cudaMemcpyAsync(c->d_h, in_direct ? (const void*)h_in : (const void*)c->h_pinned, bytes_in, cudaMemcpyHostToDevice, c->stream));
     // ... and so does the first GEMM of the layer (q / kv compression), which needs the rows and
     // the weights but nothing of the plan
-    if (!c->profiling && lid >= 0 && lid < c->cfg.n_layers && c->layers[lid].set) {
+    if (!c->profiling && lid >= 0 && lid < c->cfg.n_layers && c->layers[lid].set && !c->layers[lid].attn_norm) {
       int rc0 = run_gemm(c, plain_gemm(c->d_h, c->layers[lid].w_cmp, c->d_cmp, (int)T_in, c->d.cmp_n, c->d.hidden));
       if (rc0) return rc0;
       c->compress_done = true;

@@ -72,6 +72,7 @@ void FSTEngine::preload_all_layers() {
     fw.q_norm = p(w.q_norm);
     fw.kv_norm = p(w.kv_norm);
     fw.attn_sinks = w.attn_sinks.empty() ? nullptr : w.attn_sinks.data();
+    fw.attn_norm = p(w.attn_norm);
     check(fst_cuda_mla_set_layer_weights(ctx_, l, &fw), "set_layer_weights");
   }
 }

@@ -41,6 +41,8 @@ struct LayerWeightsC {
   std::vector<bf16_t> q_norm, kv_norm, wq_a, wq_b, wkv, wo_a, wo_b;
   std::vector<bf16_t> wkv_b;        // BASELINE preset: per head W_UK rows then W_UV rows
   std::vector<float> attn_sinks;    // per-head sink logit (empty: 0, src/fst_engine.cpp:3623)
+  std::vector<bf16_t> attn_norm;    // [hidden]; when set, process_mla takes the rows BEFORE the norm
+                                    // of process_layer (src/fst_engine.cpp:2687-2688) and applies it
 };
 
 struct RandmatResult {  // one line of randmat_test (src/fst_engine.cpp:586-685)

@@ -43,7 +43,7 @@ FSTEngine* fst_engine_create(int preset, int n_layers, int max_seq, int max_seqs
 }
 void fst_engine_destroy(FSTEngine* e) { delete e; }
 
-// name: one of wq_a wq_b wkv wkv_b wo_a wo_b q_norm kv_norm; n elements of bf16 bits.
+// name: one of wq_a wq_b wkv wkv_b wo_a wo_b q_norm kv_norm attn_norm; n elements of bf16 bits.
 int fst_engine_set_weight(FSTEngine* e, int lid, const char* name, const uint16_t* data, size_t n) {
   return guard([&] {
     LayerWeightsC& w = e->shared_.at(lid);
@@ -56,6 +56,7 @@ int fst_engine_set_weight(FSTEngine* e, int lid, const char* name, const uint16_
     else if (s == "wo_a") dst = &w.wo_a;
     else if (s == "wo_b") dst = &w.wo_b;
     else if (s == "q_norm") dst = &w.q_norm;
+    else if (s == "attn_norm") dst = &w.attn_norm;
     else if (s == "kv_norm") dst = &w.kv_norm;
     else throw std::runtime_error("unknown weight " + s);
     dst->assign(data, data + n);

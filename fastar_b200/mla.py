@@ -46,7 +46,7 @@ class Config(C.Structure):
 class Weights(C.Structure):
     _fields_ = [(n, C.POINTER(C.c_uint16)) for n in
                 ("wq_a", "wq_b", "wkv_a", "wkv_b", "wo_a", "wo_b", "q_norm", "kv_norm")] + \
-               [("attn_sinks", C.POINTER(C.c_float))]
+               [("attn_sinks", C.POINTER(C.c_float)), ("attn_norm", C.POINTER(C.c_uint16))]
 
 
 class SeqStep(C.Structure):

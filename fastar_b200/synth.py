@@ -10,7 +10,7 @@ import numpy as np
 
 from . import mla
 
-_TENSOR_IDS = {"wq_a": 1, "wq_b": 2, "wkv_a": 3, "wkv_b": 4, "wo_a": 5, "wo_b": 6, "attn_sinks": 7,
+_TENSOR_IDS = {"wq_a": 1, "wq_b": 2, "wkv_a": 3, "wkv_b": 4, "wo_a": 5, "wo_b": 6, "attn_sinks": 7, "attn_norm": 8,
                "x": 20, "cache": 21, "lens": 22, "perm": 23}
 
 

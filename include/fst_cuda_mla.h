@@ -79,7 +79,10 @@ typedef struct FstMlaConfig {
  *           wo_b[hidden,H*v_head] q_norm[q_lora] kv_norm[kv_lora]
  * V4 (LayerWeightsC, include/fst_engine.h:165-188): wq_a wq_b[H*512,q_lora] wkv_a = wkv[512,hidden]
  *           wo_a[o_groups*o_lora, H*512/o_groups] wo_b[hidden,o_groups*o_lora]
- *           q_norm kv_norm attn_sinks[H] (NULL: sink logit 0, src/fst_engine.cpp:3623) */
+ *           q_norm kv_norm attn_sinks[H] (NULL: sink logit 0, src/fst_engine.cpp:3623)
+ * attn_norm[hidden] (either preset, may be NULL): the weight of the RMSNorm that process_layer
+ * applies in front of process_mla (src/fst_engine.cpp:2687-2689).  When it is set the layer call
+ * takes the rows BEFORE that norm and applies it on the device. */
 typedef struct FstMlaWeights {
   const uint16_t* wq_a;
   const uint16_t* wq_b;
@@ -90,6 +93,7 @@ typedef struct FstMlaWeights {
   const uint16_t* q_norm;
   const uint16_t* kv_norm;
   const float* attn_sinks;
+  const uint16_t* attn_norm;
 } FstMlaWeights;
 
 /* One sequence's share of a layer call.  The reference passes this implicitly as

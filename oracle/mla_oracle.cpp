@@ -343,6 +343,14 @@ int fst_oracle_mla_forward(const FstOracleCfg* c, const FstOracleWeights* w, con
   if (M == 0) return 0;
   const bool v4 = c->preset == FST_ORACLE_PRESET_FASTAR_V4;
 
+  /* attn_norm of process_layer (2687-2688), when its weight is given: an = rmsnorm(h) * w. */
+  std::vector<float> an;
+  if (w->attn_norm) {
+    an.resize((size_t)M * d.hidden);
+    fst_oracle_rmsnorm(h, w->attn_norm, an.data(), M, d.hidden, c->rms_eps, rb);
+    h = an.data();
+  }
+
   /* q compress (3362-3364) + q_norm (3385-3389). */
   std::vector<float> qc((size_t)M * d.q_lora);
   fst_oracle_gemm(h, w->wq_a, qc.data(), M, d.q_lora, d.hidden, 0, rb, nt);

@@ -53,7 +53,10 @@ typedef struct {
  *           wo_b[hidden,H*v_head] q_norm[q_lora] kv_norm[kv_lora]
  * V4:       wq_a[q_lora,hidden] wq_b[H*512,q_lora] wkv_a[512,hidden]
  *           wo_a[o_groups*o_lora, H*512/o_groups] wo_b[hidden,o_groups*o_lora]
- *           q_norm kv_norm attn_sinks[H] */
+ *           q_norm kv_norm attn_sinks[H]
+ * attn_norm[hidden] (either preset, may be NULL): the weighted RMSNorm that process_layer applies
+ * to the rows before it calls process_mla (reference src/fst_engine.cpp:2687-2689); when set,
+ * `h` holds the rows before that norm. */
 typedef struct {
   const float* wq_a;
   const float* wq_b;
@@ -64,6 +67,7 @@ typedef struct {
   const float* q_norm;
   const float* kv_norm;
   const float* attn_sinks;
+  const float* attn_norm;
 } FstOracleWeights;
 
 /* Optional per-stage dumps (the FST_MLA_TRACE stage list, reference

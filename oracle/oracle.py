@@ -41,7 +41,7 @@ class OracleCfg(C.Structure):
 
 class _Weights(C.Structure):
     _fields_ = [(n, C.POINTER(C.c_float)) for n in
-                ("wq_a", "wq_b", "wkv_a", "wkv_b", "wo_a", "wo_b", "q_norm", "kv_norm", "attn_sinks")]
+                ("wq_a", "wq_b", "wkv_a", "wkv_b", "wo_a", "wo_b", "q_norm", "kv_norm", "attn_sinks", "attn_norm")]
 
 
 class _Trace(C.Structure):

@@ -14,16 +14,20 @@ IMPLS = [("simt", mla.IMPL_SIMT, mla.IMPL_SIMT), ("tensor", mla.IMPL_TENSOR, mla
 _W = {}
 
 
-def weights_for(preset):
-    """Seed-0 weights of the preset at full size, as bits (GPU) and rounded fp32 (oracle)."""
-    if preset not in _W:
+def weights_for(preset, attn_norm=False):
+    """Seed-0 weights of the preset at full size, as bits (GPU) and rounded fp32 (oracle).
+    attn_norm: also the weight of the RMSNorm in front of the layer, N(1, 0.1^2)."""
+    key = (preset, attn_norm)
+    if key not in _W:
         cfg = mla.make_config(preset)
         w = synth.layer_weights_f32(cfg, 0, 0)
-        _W[preset] = (synth.weights_to_bits(w), synth.weights_rounded(w))
-    return _W[preset]
+        if attn_norm:
+            w["attn_norm"] = 1.0 + synth.normal_f32(0, "attn_norm", (cfg.hidden,), 0.1, (0,))
+        _W[key] = (synth.weights_to_bits(w), synth.weights_rounded(w))
+    return _W[key]
 
 
-def run_layer(preset, impl, lens, q_len, causal, seed=0, steps=1, ulps=0):
+def run_layer(preset, impl, lens, q_len, causal, seed=0, steps=1, ulps=0, attn_norm=False):
     """`steps` consecutive layer calls (each appends q_len tokens per sequence); every call is
     compared with the oracle, and so is the cache content afterwards."""
     attn_impl, gemm_impl = impl[1], impl[2]
@@ -31,7 +35,7 @@ def run_layer(preset, impl, lens, q_len, causal, seed=0, steps=1, ulps=0):
     n_pages = sum((L + q_len * steps + 63) // 64 for L in lens) + 4
     cfg = mla.make_config(preset, n_pages=n_pages, max_tokens=B * q_len, max_seqs=B, attn_impl=attn_impl,
                           gemm_impl=gemm_impl)
-    bits, rounded = weights_for(preset)
+    bits, rounded = weights_for(preset, attn_norm)
     ocfg = oracle_cfg(cfg)
     d = mla.dims_of(cfg)
     H = cfg.n_heads
@@ -107,3 +111,12 @@ def test_fastar_v4_preset(impl):
     # the live engine's form: 512-wide rows, per-head q norm, sink, inverse RoPE, grouped wo_a
     # (its outputs reach several units: the absolute bound is two bf16 steps at that magnitude)
     run_layer(mla.PRESET_FASTAR_V4, impl, [100, 0, 129], 2, True, seed=4, steps=2, ulps=2)
+
+
+@pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
+@pytest.mark.parametrize("preset", [mla.PRESET_BASELINE, mla.PRESET_FASTAR_V4], ids=["baseline", "v4"])
+def test_attn_norm_in_front_of_the_layer(impl, preset):
+    # process_layer's attention half (src/fst_engine.cpp:2687-2689): the layer call takes the rows
+    # before attn_norm and applies it itself; inputs with a row scale far from 1 so that a missing
+    # norm cannot pass
+    run_layer(preset, impl, [300, 65], 2, True, seed=5, steps=2, ulps=2, attn_norm=True)

@@ -118,3 +118,25 @@ def test_attention_matches_sparse_attn(golden):
     o = np.stack([p[2] for p in parts])
     merged = O.merge_partials(cfg, m, l, o, sinks=sink)
     assert np.max(np.abs(merged.reshape(want.shape) - want)) < 2e-5
+
+
+def test_attn_norm_is_rmsnorm_in_front_of_the_layer():
+    """The oracle with an attn_norm weight equals the oracle fed with rms_cpu-normed rows
+    (process_layer calls npu_rmsnorm_weighted and then process_mla, src/fst_engine.cpp:2687-2689)."""
+    cfg = O.make_cfg(O.PRESET_BASELINE, hidden=256, n_heads=4, q_lora=64, kv_lora=64, qk_nope=32, qk_rope=16,
+                     v_head=32, round_bf16=True)
+    rng = np.random.default_rng(7)
+    d = O.dims_of(cfg) if hasattr(O, "dims_of") else None
+    shapes = {"wq_a": (64, 256), "wq_b": (4 * 48, 64), "wkv_a": (80, 256), "wkv_b": (4 * 64, 64),
+              "wo_b": (256, 4 * 32), "q_norm": (64,), "kv_norm": (64,)}
+    w = {k: O.bf16_round((rng.standard_normal(s) * (1.0 if "norm" in k else 0.05)).astype(np.float32)) for k, s in shapes.items()}
+    g = O.bf16_round((1.0 + 0.2 * rng.standard_normal(256)).astype(np.float32))
+    h = O.bf16_round((3.0 * rng.standard_normal((3, 256))).astype(np.float32))
+    cache_a = np.zeros((8, 80), np.float32)
+    cache_b = np.zeros((8, 80), np.float32)
+    fused = O.mla_forward(cfg, dict(w, attn_norm=g), h, 0, cache_a, causal=True)
+    normed = O.rmsnorm(h, g, round_bf16=True)
+    plain = O.mla_forward(cfg, w, normed, 0, cache_b, causal=True)
+    assert np.array_equal(fused.out.view(np.uint32), plain.out.view(np.uint32))
+    assert np.array_equal(cache_a.view(np.uint32), cache_b.view(np.uint32))
+    assert not np.array_equal(fused.out, O.mla_forward(cfg, w, h, 0, np.zeros((8, 80), np.float32), causal=True).out)
