@@ -138,3 +138,18 @@ def test_constant_cache_returns_the_row(impl):
         assert np.max(np.abs(out - want)) <= 2.0 ** -7 * np.max(np.abs(want))
     finally:
         ctx.close()
+
+
+def test_many_short_segments_per_cta():
+    # 240 sequences of 1 .. 200 tokens: more segments than SMs, so every CTA of the tcgen05 kernel
+    # runs several one- to three-tile segments back to back (Q_eff replaced in tensor memory and a
+    # partial written at every boundary) and the merge sees one part for almost every row
+    rng = np.random.default_rng(11)
+    lens = [int(x) for x in rng.integers(1, 201, size=240)]
+    run_case(mla.PRESET_BASELINE, mla.IMPL_TENSOR, lens, seed=11, ulps=1)
+
+
+def test_long_and_short_sequences_mixed():
+    # one 20 000-token sequence among short ones: its tiles spread over most CTAs while the short
+    # sequences share the remaining ones; the long row's parts are merged from ~140 partials
+    run_case(mla.PRESET_BASELINE, mla.IMPL_TENSOR, [20000, 3, 64, 130, 65, 1], seed=12, ulps=1)
