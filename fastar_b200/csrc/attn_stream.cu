@@ -523,26 +523,52 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
         // at a time; this warp owns columns 256*half .. +255.  The rows go through shared memory
         // so that every store instruction writes four full 128-byte lines.
         float* po = p.part_o + ((long long)sg.part * HEADS + quad * 16) * D_V + half * 256;
+        if (cur.done()) {
+          // The CTA's last segment: every tile has retired, so the ring is idle and each warp
+          // stages its whole 16 x 256 block there (16 KB) -- all tensor-memory loads first, one
+          // warp barrier, then the stores back to back instead of 16 small round trips.
+          unsigned char* big = s_ring + (warp - 2) * 16384;
 #pragma unroll 1
-        for (int cc = 0; cc < 8; ++cc) {
-          float o[32];
-          tc::tmem_ld32(lane_addr + COL_O + half * 256 + cc * 32, o);
-#pragma unroll
-          for (int h8 = 0; h8 < 2; ++h8) {  // eight rows at a time through the 1 KB staging area
-            if (sub == 1 && ((lane >> 3) & 1) == h8) {
-              const int rr = lane & 7;
+          for (int cc = 0; cc < 8; ++cc) {
+            float o[32];
+            tc::tmem_ld32(lane_addr + COL_O + half * 256 + cc * 32, o);
+            if (sub == 1) {
+              const int rr = lane - 16;
 #pragma unroll
               for (int u = 0; u < 8; ++u)
-                *reinterpret_cast<float4*>(stage + rr * 128 + ((u ^ rr) * 16)) = make_float4(o[u * 4], o[u * 4 + 1], o[u * 4 + 2], o[u * 4 + 3]);
+                *reinterpret_cast<float4*>(big + cc * 2048 + rr * 128 + ((u ^ (rr & 7)) * 16)) =
+                    make_float4(o[u * 4], o[u * 4 + 1], o[u * 4 + 2], o[u * 4 + 3]);
             }
-            __syncwarp();
+          }
+          __syncwarp();
+#pragma unroll 4
+          for (int i = 0; i < 32; ++i) {
+            const int cc = i >> 2, rr = (i & 3) * 4 + (lane >> 3), u = lane & 7;
+            const float4 v = *reinterpret_cast<const float4*>(big + cc * 2048 + rr * 128 + ((u ^ (rr & 7)) * 16));
+            *reinterpret_cast<float4*>(po + (long long)rr * D_V + cc * 32 + u * 4) = v;
+          }
+        } else {
+#pragma unroll 1
+          for (int cc = 0; cc < 8; ++cc) {
+            float o[32];
+            tc::tmem_ld32(lane_addr + COL_O + half * 256 + cc * 32, o);
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              const int rr = i * 4 + (lane >> 3), u = lane & 7;
-              const float4 v = *reinterpret_cast<const float4*>(stage + rr * 128 + ((u ^ rr) * 16));
-              *reinterpret_cast<float4*>(po + (long long)(h8 * 8 + rr) * D_V + cc * 32 + u * 4) = v;
+            for (int h8 = 0; h8 < 2; ++h8) {  // eight rows at a time through the 1 KB staging area
+              if (sub == 1 && ((lane >> 3) & 1) == h8) {
+                const int rr = lane & 7;
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                  *reinterpret_cast<float4*>(stage + rr * 128 + ((u ^ rr) * 16)) = make_float4(o[u * 4], o[u * 4 + 1], o[u * 4 + 2], o[u * 4 + 3]);
+              }
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const int rr = i * 4 + (lane >> 3), u = lane & 7;
+                const float4 v = *reinterpret_cast<const float4*>(stage + rr * 128 + ((u ^ rr) * 16));
+                *reinterpret_cast<float4*>(po + (long long)(h8 * 8 + rr) * D_V + cc * 32 + u * 4) = v;
+              }
+              __syncwarp();
             }
-            __syncwarp();
           }
         }
       }

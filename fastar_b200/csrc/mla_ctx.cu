@@ -93,6 +93,10 @@ struct FstMlaCtx {
   unsigned char *d_plan = nullptr, *h_plan = nullptr;
   size_t plan_cap = 0;
   cudaEvent_t plan_ev = nullptr;
+  // RoPE table rows by position, direct-mapped: one step of a model asks for the same positions
+  // in every layer, and a decode step for the positions right after the previous step's
+  std::vector<float> lut_rows;
+  std::vector<int32_t> lut_tag;
   // plan (host)
   bool planned = false;
   int T = 0, n_segs = 0, n_parts = 0, n_ctas = 0;
@@ -165,6 +169,25 @@ void rope_lut_row(float* lut, int pos, int rope_dim, float theta, bool yarn) {
     sincosf(ang, &lut[dd + 1], &lut[dd]);  // bit-identical to sinf / cosf (checked over 25.6 M angles), one call
     th *= theta_scale;
   }
+}
+
+constexpr int LUT_CACHE_ROWS = 4096;  // power of two
+
+// the RoPE row of one position, computed on its first use and kept until another position maps to
+// the same slot
+const float* lut_row_cached(FstMlaCtx* c, int pos) {
+  const int rope = c->d.rope;
+  if (c->lut_tag.empty()) {
+    c->lut_tag.assign(LUT_CACHE_ROWS, -1);
+    c->lut_rows.resize((size_t)LUT_CACHE_ROWS * rope);
+  }
+  const int slot = pos & (LUT_CACHE_ROWS - 1);
+  float* row = &c->lut_rows[(size_t)slot * rope];
+  if (c->lut_tag[slot] != pos) {
+    rope_lut_row(row, pos, rope, c->cfg.rope_theta, c->cfg.rope_yarn != 0);
+    c->lut_tag[slot] = pos;
+  }
+  return row;
 }
 
 bool seq_ok(const FstMlaCtx* c, int32_t s) { return s >= 0 && s < c->cfg.max_seqs && c->live[s]; }
@@ -814,7 +837,7 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
     tables.insert(tables.end(), c->tables[s.seq].begin(), c->tables[s.seq].end());
     const int rp0 = s.rope_pos0 >= 0 ? s.rope_pos0 : s.pos0;
     for (int i = 0; i < s.q_len; ++i, ++t) {
-      rope_lut_row(&lut[(size_t)t * d.rope], rp0 + i, d.rope, c->cfg.rope_theta, c->cfg.rope_yarn != 0);
+      memcpy(&lut[(size_t)t * d.rope], lut_row_cached(c, rp0 + i), (size_t)d.rope * sizeof(float));
       dst[t] = s.append ? row_offset(c, s.seq, s.pos0 + i) : -1;
       tok_table[t] = toff;
       int len = s.append ? s.pos0 + s.q_len : s.pos0;
@@ -1010,6 +1033,10 @@ int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* 
   const size_t bytes = (size_t)c->T * c->d.hidden * sizeof(uint16_t);
   if ((rc = fst_cuda_mla_run_device(c, lid, c->d_h, c->d_out))) return rc;
   CU(cudaMemcpyAsync(out_direct ? (void*)h_out : (void*)c->h_pinned, c->d_out, bytes, cudaMemcpyDeviceToHost, c->stream));
+  // while the device works: the RoPE rows of the positions that a decode step asks for next
+  for (int b = 0; b < n_seqs; ++b)
+    if (q_lens[b] > 0 && q_lens[b] <= 4)
+      for (int i = 0; i < q_lens[b]; ++i) lut_row_cached(c, pos0[b] + q_lens[b] + i);
   if ((rc = fst_cuda_mla_sync(c))) return rc;
   if (!out_direct) memcpy(h_out, c->h_pinned, bytes);
   return FST_MLA_OK;
