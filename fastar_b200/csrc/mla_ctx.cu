@@ -98,6 +98,10 @@ struct FstMlaCtx {
   std::vector<float> lut_rows;
   std::vector<int32_t> lut_tag;
   // plan (host)
+  std::vector<FstMlaSeqStep> last_steps;  // what the valid plan was built from (every layer of a
+  int last_causal = 0;                    // model step asks for the same plan again)
+  bool plan_reuse = true;
+  int64_t plans_built = 0, plans_reused = 0;
   bool planned = false;
   int T = 0, n_segs = 0, n_parts = 0, n_ctas = 0;
   long long kv_rows = 0;
@@ -801,6 +805,13 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
   if (n_seqs < 0) return fail(FST_MLA_ERR_ARG, "negative sequence count");
   const Dims& d = c->d;
   const int pt = c->cfg.page_tokens;
+  // The same steps on unchanged sequences (anything that touches a sequence clears `planned`):
+  // the plan on the device is still the right one -- layers 2 .. L of a model step.
+  if (c->planned && c->plan_reuse && causal == c->last_causal && (size_t)n_seqs == c->last_steps.size() &&
+      (n_seqs == 0 || memcmp(steps, c->last_steps.data(), (size_t)n_seqs * sizeof(FstMlaSeqStep)) == 0)) {
+    ++c->plans_reused;
+    return FST_MLA_OK;
+  }
   c->planned = false;
   long long T = 0;
   for (int b = 0; b < n_seqs; ++b) {
@@ -854,7 +865,11 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
   // pays for loading Q_eff, refilling the pipeline and writing its partial (measured: about
   // five and a half 64-token tiles of the streaming kernel).
   const int unit = c->cfg.page_tokens == 64 ? 64 : ATTN_TILE;
-  const long long SEG_COST2 = unit == 64 ? 11 : 5;
+  long long SEG_COST2 = unit == 64 ? 11 : 5;
+  if (const char* e = getenv("FST_MLA_SEG_COST")) {  // tuning aid: the segment's cost in half tiles
+    const int v = atoi(e);
+    if (v > 0 && v < 64) SEG_COST2 = v;
+  }
   long long total_tiles = 0, kv_rows = 0, n_nonempty = 0;
   for (int i = 0; i < T; ++i) {
     total_tiles += (kvlen[i] + unit - 1) / unit;
@@ -946,7 +961,23 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
   c->n_parts = (int)segs.size();
   c->n_ctas = n_ctas;
   c->kv_rows = kv_rows;
+  c->last_steps.assign(steps, steps + n_seqs);
+  c->last_causal = causal;
+  ++c->plans_built;
   c->planned = true;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_set_plan_reuse(FstMlaCtx* c, int32_t on) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  c->plan_reuse = on != 0;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_plan_counts(FstMlaCtx* c, int64_t* built, int64_t* reused) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (built) *built = c->plans_built;
+  if (reused) *reused = c->plans_reused;
   return FST_MLA_OK;
 }
 

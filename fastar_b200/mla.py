@@ -109,6 +109,8 @@ def load_library() -> C.CDLL:
     L.fst_cuda_mla_set_profiling.argtypes = [vp, C.c_int]
     L.fst_cuda_mla_kernel_times.argtypes = [vp, C.POINTER(C.c_float), i32p]
     L.fst_cuda_mla_plan_info.argtypes = [vp, i32p, i32p, C.POINTER(i64)]
+    L.fst_cuda_mla_set_plan_reuse.argtypes = [vp, i32]
+    L.fst_cuda_mla_plan_counts.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
     L.fst_cuda_mla_attention_noalloc.argtypes = [vp, vp, i32, i32, i32, i32, C.c_float, vp, vp]
     _lib = L
     return L
@@ -269,6 +271,15 @@ class MlaContext:
         t = C.c_int32()
         self._check(self.lib.fst_cuda_mla_plan_tokens(self._h, C.byref(t)))
         return t.value
+
+    def set_plan_reuse(self, on: bool) -> None:
+        """Whether a plan request equal to the valid plan keeps it (default) or rebuilds it."""
+        self._check(self.lib.fst_cuda_mla_set_plan_reuse(self._h, 1 if on else 0))
+
+    def plan_counts(self) -> dict:
+        built, reused = C.c_int64(0), C.c_int64(0)
+        self._check(self.lib.fst_cuda_mla_plan_counts(self._h, C.byref(built), C.byref(reused)))
+        return {"built": built.value, "reused": reused.value}
 
     def plan_info(self) -> dict:
         a, b, c = C.c_int32(), C.c_int32(), C.c_int64()

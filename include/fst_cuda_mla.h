@@ -174,6 +174,12 @@ int fst_cuda_mla_pool_read(FstMlaCtx* ctx, int lid, uint16_t* out, size_t bytes)
  * and the split-KV schedule, and uploads them.  A plan stays valid for every layer of the
  * same step (process_layer calls process_mla once per layer with the same seq_pos_). */
 int fst_cuda_mla_plan(FstMlaCtx* ctx, const FstMlaSeqStep* steps, int32_t n_seqs, int32_t causal);
+/* A plan request equal to the valid plan (same steps, same causal flag, no sequence touched in
+ * between) returns at once and keeps the tables that are on the device: that is what layers
+ * 2 .. L of a step see, also through fst_cuda_mla_forward.  on = 0 rebuilds every time. */
+int fst_cuda_mla_set_plan_reuse(FstMlaCtx* ctx, int32_t on);
+/* Plans built and plan requests answered by the valid plan, since the context was created. */
+int fst_cuda_mla_plan_counts(FstMlaCtx* ctx, int64_t* built, int64_t* reused);
 /* Enqueue the layer for the current plan; h_in / h_out are device bf16 [T, hidden]
  * (may alias).  No host synchronisation. */
 int fst_cuda_mla_run_device(FstMlaCtx* ctx, int lid, const void* d_h_in, void* d_h_out);

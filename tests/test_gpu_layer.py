@@ -120,3 +120,48 @@ def test_attn_norm_in_front_of_the_layer(impl, preset):
     # before attn_norm and applies it itself; inputs with a row scale far from 1 so that a missing
     # norm cannot pass
     run_layer(preset, impl, [300, 65], 2, True, seed=5, steps=2, ulps=2, attn_norm=True)
+
+
+def test_plan_is_kept_across_the_layers_of_a_step():
+    """process_layer calls process_mla once per layer with the same seq_pos_ (src/fst_engine.cpp:2687):
+    the second request for the same steps keeps the plan that is on the device, gives the same bits as
+    a rebuilt plan, and anything that touches a sequence makes the next request build a new one."""
+    lens, B = [130, 64, 700], 3
+    cfg = mla.make_config(mla.PRESET_BASELINE, n_pages=sum((L + 66) // 64 for L in lens) + 4, max_tokens=B,
+                          max_seqs=B, n_layers=2)
+    bits, _ = weights_for(mla.PRESET_BASELINE)
+    with mla.MlaContext(cfg) as ctx:
+        for lid in range(2):
+            ctx.set_layer_weights(lid, bits)
+        seqs = []
+        for b, L in enumerate(lens):
+            s = ctx.seq_alloc()
+            rows = synth.to_bf16_bits(synth.cache_rows_f32(cfg, 0, b, L))
+            for lid in range(2):
+                ctx.cache_write(lid, s, 0, rows)
+            seqs.append(s)
+        h = synth.to_bf16_bits(synth.hidden_f32(cfg, 0, B, (0,)))
+        c0 = ctx.plan_counts()
+        out0 = ctx.forward(0, h, seqs, lens, [1] * B)        # layer 0 of the step: builds
+        out1 = ctx.forward(1, h, seqs, lens, [1] * B)        # layer 1: same steps, plan kept
+        c1 = ctx.plan_counts()
+        assert (c1["built"] - c0["built"], c1["reused"] - c0["reused"]) == (1, 1)
+        assert np.array_equal(out0, out1)                    # same weights, same cache rows in both layers
+        ctx.set_plan_reuse(False)
+        out2 = ctx.forward(1, h, seqs, lens, [1] * B)        # rebuilt: same bits
+        c2 = ctx.plan_counts()
+        assert (c2["built"] - c1["built"], c2["reused"] - c1["reused"]) == (1, 0)
+        assert np.array_equal(out1, out2)
+        ctx.set_plan_reuse(True)
+        # the next step (positions moved on) and a rollback both ask for a new plan
+        nxt = [L + 1 for L in lens]
+        ctx.forward(0, h, seqs, nxt, [1] * B)
+        c3 = ctx.plan_counts()
+        assert c3["built"] - c2["built"] == 1
+        ctx.seq_truncate(seqs[0], lens[0])
+        ctx.seq_truncate(seqs[1], lens[1])
+        ctx.seq_truncate(seqs[2], lens[2])
+        out3 = ctx.forward(0, h, seqs, lens, [1] * B)
+        c4 = ctx.plan_counts()
+        assert (c4["built"] - c3["built"], c4["reused"] - c3["reused"]) == (1, 0)
+        assert np.array_equal(out0, out3)
