@@ -164,25 +164,30 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
 
 // Walks the tiles of a CTA's segment list in order: every role keeps one of these per stream
 // position it tracks, so that all roles agree on (segment, tile in segment, running tile index).
+// The ring carries SLOTS: every segment puts its Q_eff block (64 heads x d_qk, the geometry of a
+// page) into one slot, followed by one slot per tile.
 struct TileCursor {
   int si, seg_end;   // current segment, one past the CTA's last
   int t, n_tiles;    // tile within the segment, tiles of the segment
-  int g;             // running tile index over the whole list
+  int g;             // running slot index over the whole list (ring frame g % 3)
+  int gq;            // slot of the current segment's Q_eff block
+  int n;             // running tile index (slots that are tiles)
   int sidx;          // running segment index
   AttnSeg sg;
   __device__ __forceinline__ void load(const AttnSeg* segs) {
     if (si < seg_end) {
       sg = segs[si];
       n_tiles = (sg.kv_end - sg.kv_begin + TILE - 1) / TILE;
+      gq = g++;
     }
   }
   __device__ __forceinline__ void init(const AttnSeg* segs, int seg0, int seg1) {
-    si = seg0; seg_end = seg1; t = 0; g = 0; sidx = 0; n_tiles = 0;
+    si = seg0; seg_end = seg1; t = 0; g = 0; gq = 0; n = 0; sidx = 0; n_tiles = 0;
     load(segs);
   }
   __device__ __forceinline__ bool done() const { return si >= seg_end; }
   __device__ __forceinline__ void next(const AttnSeg* segs) {
-    ++g;
+    ++g; ++n;
     if (++t == n_tiles) {
       t = 0; ++si; ++sidx;
       load(segs);
@@ -215,7 +220,7 @@ __device__ __forceinline__ bool qk_chunks(StreamMisc* mi, int g, uint32_t d, uin
 // 14 warps are allocated as 16 (granularity four): 128 registers per thread
 template <int NCH>
 __global__ void __launch_bounds__(ST_THREADS, 1)
-k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
+k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ CUtensorMap tmQ, StreamParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* s_ring = smem;
@@ -270,28 +275,38 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
     // first group run while the rest of the tile is still on its way.
     if (lane == 0) {
       const int r = warp == 0 ? 0 : warp - 9;
-      if (r == 0) tc::tma_prefetch_desc(&tmKV);
+      if (r == 0) {
+        tc::tma_prefetch_desc(&tmKV);
+        tc::tma_prefetch_desc(&tmQ);
+      }
       TileCursor cur;
       cur.init(p.segs, seg0, seg1);
       bool ok = true;
-      while (!cur.done() && ok) {
-        const int32_t* table = p.tables + p.tok_table[cur.sg.tok];
-        const int row0 = table[(cur.sg.kv_begin >> 6) + cur.t] * TILE;
-        const int g = cur.g, j0 = g * NCH;
-        const int c0 = (r + 3 - j0 % 3) % 3;
-        if (r == 0) STRACE(g, 11);
-        if (g >= 3) {
-          ok = tc::mbar_wait(&mi->o_done[(g - 3) & 3], ((g - 3) >> 2) & 1, abort_flag, p.d_status, ST_TMA_TIMEOUT);
-          if (!ok) break;
-        }
+      // the chunks of slot g that this producer copies, from rows row0 .. row0+63 of `map`
+      auto fill = [&](int g, const CUtensorMap* map, int row0) -> bool {
+        const int c0 = (r + 3 - (g * NCH) % 3) % 3;
+        if (g >= 3 && !tc::mbar_wait(&mi->o_done[(g - 3) & 3], ((g - 3) >> 2) & 1, abort_flag, p.d_status, ST_TMA_TIMEOUT))
+          return false;
         for (int c = c0; c < NCH; c += 3) {
           const int slot = (g % 3) * NCH + c;
           tc::mbar_expect_tx(&mi->full_t[g & 3][c / 3], CHUNK);
-          tc::tma_load_3d(s_ring + slot * CHUNK, &tmKV, &mi->full_t[g & 3][c / 3], c * 64, row0, 0);
+          tc::tma_load_3d(s_ring + slot * CHUNK, map, &mi->full_t[g & 3][c / 3], c * 64, row0, 0);
         }
-        if (r == 0) STRACE(g, 12);
+        return true;
+      };
+      while (!cur.done() && ok) {
+        // a segment opens with the Q_eff block of its token (64 rows of q_eff)
+        if (cur.t == 0) {
+          ok = fill(cur.gq, &tmQ, cur.sg.tok * HEADS);
+          if (!ok) break;
+        }
+        const int32_t* table = p.tables + p.tok_table[cur.sg.tok];
+        const int row0 = table[(cur.sg.kv_begin >> 6) + cur.t] * TILE;
+        if (r == 0) STRACE(cur.n, 11);
+        ok = fill(cur.g, &tmKV, row0);
+        if (r == 0) STRACE(cur.n, 12);
 #ifdef FST_ATTN_TRACE
-        if (r == 0) ST_CTA(6, (long long)(g + 1));
+        if (r == 0) ST_CTA(6, (long long)(cur.n + 1));
 #endif
         cur.next(p.segs);
       }
@@ -309,10 +324,14 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
       cur.init(p.segs, seg0, seg1);
       bool ok = true;
       while (!cur.done() && ok) {
-        const int g = cur.g;
-        // both issuers wait for Q_eff of every segment
-        if (cur.t == 0) ok = tc::mbar_wait(&mi->q_ready, cur.sidx & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
-        const int k = 2 * g + part, buf = k % 3, use = k / 3;
+        const int g = cur.g, n = cur.n;
+        // both issuers wait for Q_eff of every segment; all softmax threads have read the block's
+        // frame by then, which is what the producers wait for before they reuse it
+        if (cur.t == 0) {
+          ok = tc::mbar_wait(&mi->q_ready, cur.sidx & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
+          if (ok && part == 0) tc::mbar_arrive(&mi->o_done[cur.gq & 3]);
+        }
+        const int k = 2 * n + part, buf = k % 3, use = k / 3;
         // the softmax threads have read the previous partial in this buffer
         if (ok && use >= 1) ok = tc::mbar_wait(&mi->s_free[buf], (use - 1) & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
         if (!ok) break;
@@ -321,8 +340,8 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
         if (part == 0) ok = qk_chunks<0, 5>(mi, g, d, tmem, frame16, abort_flag, p.d_status);
         else ok = qk_chunks<5, NCH>(mi, g, d, tmem, frame16, abort_flag, p.d_status);
         if (!ok) break;
-        tc::umma_commit(&mi->s_full[g & 1]);
-        if (part == 1) STRACE(g, 1);
+        tc::umma_commit(&mi->s_full[n & 1]);
+        if (part == 1) STRACE(n, 1);
         cur.next(p.segs);
       }
     }
@@ -338,9 +357,9 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
       bool ok = true;
       while (!cur.done() && ok) {
         const int g = cur.g;
-        ok = tc::mbar_wait(&mi->p_full, g & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
+        ok = tc::mbar_wait(&mi->p_full, cur.n & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
         if (!ok) break;
-        STRACE(g, 3);
+        STRACE(cur.n, 3);
         tc::tc_fence_after();
         const uint64_t da = k_major | (uint64_t)p16;
         const uint32_t acc0 = cur.t > 0 ? 1u : 0u;
@@ -353,7 +372,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
           for (int k = 0; k < TILE / 16; ++k) tc::umma_bf16(d, da + k * 2, db + k * 128, id256, k > 0 ? 1u : acc0);
         }
         tc::umma_commit(&mi->o_done[g & 3]);
-        STRACE(g, 4);
+        STRACE(cur.n, 4);
         cur.next(p.segs);
       }
     }
@@ -370,50 +389,48 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
     // epilogue staging: half of the P rows of this quadrant (what the two warps of the quadrant
     // write during the softmax, so the quadrant barrier orders the two uses)
     unsigned char* stage = s_p + quad * 2048 + half * 1024;
-    // Q_eff of token `tok` -> tensor memory (bf16 pairs, two dims per column): all loads first,
-    // then the stores.  Every QK MMA of the previous segment must have retired (the caller saw
-    // s_full of its last tile).
-    auto write_q = [&](int tok, int g_trace) {
-      const unsigned char* qrow = reinterpret_cast<const unsigned char*>(p.q_eff + ((long long)tok * HEADS + row) * p.d_qk);
-      uint4 v[20];
+    // The Q_eff block in ring slot gq -> tensor memory (bf16 pairs, two dims per column).  The block
+    // came through the ring like a tile, ahead of the segment's first tile, so it does not queue
+    // behind the tiles in flight as loads by these threads would.  Every QK MMA of the previous
+    // segment must have retired (the caller saw s_full of its last tile).
+    auto write_q = [&](int gq, int n_trace) -> bool {
+      for (int i = 0; i < 3; ++i)
+        if (!tc::mbar_wait(&mi->full_t[gq & 3][i], (gq >> 2) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT)) return false;
+      const unsigned char* frame = s_ring + (gq % 3) * (NCH * CHUNK);
+      // head `row`, dims 256*half + 128*gsel + 64*sub .. +63: row `row` of chunk 4*half + 2*gsel + sub
+      // (128 bytes, eight 16-byte units, unit u at position u ^ (row & 7))
 #pragma unroll
       for (int gsel = 0; gsel < 2; ++gsel) {
-        const uint4* src = reinterpret_cast<const uint4*>(qrow + (half * 128 + gsel * 64 + sub * 32) * 4);
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) v[gsel * 8 + q4] = src[q4];
-      }
-      if (NCH == 9 && half == 1) {  // the 64 rope dims: columns [256, 288)
-        const uint4* src = reinterpret_cast<const uint4*>(qrow + (256 + sub * 16) * 4);
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) v[16 + q4] = src[q4];
-      }
-#pragma unroll
-      for (int gsel = 0; gsel < 2; ++gsel) {
+        const unsigned char* crow = frame + (half * 4 + gsel * 2 + sub) * CHUNK + row * 128;
         float w[32];
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          w[q4 * 4] = __uint_as_float(v[gsel * 8 + q4].x);
-          w[q4 * 4 + 1] = __uint_as_float(v[gsel * 8 + q4].y);
-          w[q4 * 4 + 2] = __uint_as_float(v[gsel * 8 + q4].z);
-          w[q4 * 4 + 3] = __uint_as_float(v[gsel * 8 + q4].w);
+        for (int u = 0; u < 8; ++u) {
+          const uint4 v = *reinterpret_cast<const uint4*>(crow + ((u ^ (row & 7)) * 16));
+          w[u * 4] = __uint_as_float(v.x);
+          w[u * 4 + 1] = __uint_as_float(v.y);
+          w[u * 4 + 2] = __uint_as_float(v.z);
+          w[u * 4 + 3] = __uint_as_float(v.w);
         }
         tmem_st16x64(lane_addr + COL_Q + half * 128 + gsel * 64, w);
       }
-      if (NCH == 9 && half == 1) {
+      if (NCH == 9 && half == 1) {  // the 64 rope dims (chunk 8): columns [256, 288)
+        const unsigned char* crow = frame + 8 * CHUNK + row * 128;
         float w[16];
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          w[q4 * 4] = __uint_as_float(v[16 + q4].x);
-          w[q4 * 4 + 1] = __uint_as_float(v[16 + q4].y);
-          w[q4 * 4 + 2] = __uint_as_float(v[16 + q4].z);
-          w[q4 * 4 + 3] = __uint_as_float(v[16 + q4].w);
+        for (int u = 0; u < 4; ++u) {
+          const uint4 v = *reinterpret_cast<const uint4*>(crow + (((sub * 4 + u) ^ (row & 7)) * 16));
+          w[u * 4] = __uint_as_float(v.x);
+          w[u * 4 + 1] = __uint_as_float(v.y);
+          w[u * 4 + 2] = __uint_as_float(v.z);
+          w[u * 4 + 3] = __uint_as_float(v.w);
         }
         tmem_st16x32(lane_addr + COL_Q + 256, w);
       }
       tmem_wait_st();
       tc::tc_fence_before();
       tc::mbar_arrive(&mi->q_ready);
-      if (threadIdx.x == 64) STRACE(g_trace, 15);
+      if (threadIdx.x == 64) STRACE(n_trace, 15);
+      return true;
     };
     TileCursor cur;
     cur.init(p.segs, seg0, seg1);
@@ -422,26 +439,18 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
       const AttnSeg sg = cur.sg;
       const int n_tiles = cur.n_tiles;
       // Q_eff of the first segment; later segments are written at the end of their predecessor
-      if (cur.sidx == 0) write_q(sg.tok, cur.g);
-      const int next_tok = cur.si + 1 < cur.seg_end ? p.segs[cur.si + 1].tok : -1;
+      if (cur.sidx == 0) ok = write_q(cur.gq, cur.n);
       float m_used = -INFINITY, l = 0.0f;
       int g = cur.g;
       for (int t = 0; t < n_tiles && ok; ++t, cur.next(p.segs)) {
         g = cur.g;
-        if (next_tok >= 0 && t == max(n_tiles - 4, 0)) {
-          // bring the next segment's Q_eff rows into L2 a few tiles before they are needed (the
-          // cache stream has long evicted what the previous kernel wrote; any earlier and they
-          // would be evicted again).  Four threads share a row: a quarter each.
-          const unsigned char* qrow = reinterpret_cast<const unsigned char*>(p.q_eff + ((long long)next_tok * HEADS + row) * p.d_qk);
-          const int off = (half * 2 + sub) * (NCH * 32);
-          for (int b = 0; b < NCH * 32; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(qrow + off + b));
-        }
-        ok = tc::mbar_wait(&mi->s_full[g & 1], (g >> 1) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
-        if (threadIdx.x == 64) STRACE(g, 8);
+        const int n = cur.n;
+        ok = tc::mbar_wait(&mi->s_full[n & 1], (n >> 1) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
+        if (threadIdx.x == 64) STRACE(n, 8);
         tc::tc_fence_after();
         const int tok0 = sg.kv_begin + t * TILE + half * 32 + sub * 16;
         float sc[16], sc2[16];
-        const int b0 = (2 * g) % 3, b1 = (2 * g + 1) % 3;
+        const int b0 = (2 * n) % 3, b1 = (2 * n + 1) % 3;
         tmem_ld16x32(lane_addr + COL_S + b0 * TILE + half * 32, sc);
         tmem_ld16x32(lane_addr + COL_S + b1 * TILE + half * 32, sc2);
         tc::tc_fence_before();
@@ -454,12 +463,12 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
           mx = fmaxf(mx, sc[j]);
         }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-        if (sub == 0) mi->pmax[g & 1][half][row] = mx;
+        if (sub == 0) mi->pmax[n & 1][half][row] = mx;
         ok = quad_bar_and(quad, ok);
         if (!ok) break;
-        if (threadIdx.x == 64) STRACE(g, 9);
+        if (threadIdx.x == 64) STRACE(n, 9);
         // the reference maximum moves only when the tile maximum exceeds it by more than 2^8
-        const float tm = fmaxf(mi->pmax[g & 1][0][row], mi->pmax[g & 1][1][row]);
+        const float tm = fmaxf(mi->pmax[n & 1][0][row], mi->pmax[n & 1][1][row]);
         float alpha = 1.0f;
         if (tm > m_used + RESCALE_THRESHOLD) {  // also the first tile (m_used = -inf)
           alpha = ex2f(m_used - tm);
@@ -475,8 +484,9 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
           packed[j / 2] = *reinterpret_cast<uint32_t*>(&b);
         }
         l = l * alpha + sum;
-        // P (and O, if it is rescaled below) belong to the SV MMAs of tile g-1 until they retire
-        if (g >= 1) ok = tc::mbar_wait(&mi->o_done[(g - 1) & 3], ((g - 1) >> 2) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
+        // P (and O, if it is rescaled below) belong to the SV MMAs of the previous tile until they
+        // retire (before a segment's first tile the epilogue has waited for them already)
+        if (t > 0) ok = tc::mbar_wait(&mi->o_done[(g - 1) & 3], ((g - 1) >> 2) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
         {
           // P[row, tokens 32*half + 16*sub .. +15]: two 16-byte units of the row, 128-byte swizzle
           unsigned char* prow = s_p + row * 128;
@@ -498,18 +508,19 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
           }
           tmem_wait_st();
         }
-        if (threadIdx.x == 64) STRACE(g, 10);
+        if (threadIdx.x == 64) STRACE(n, 10);
         tc::fence_proxy_async();
         tc::tc_fence_before();
         tc::mbar_arrive(&mi->p_full);
       }
       if (!ok) break;
       // Q_eff of the next segment goes in first, so that its QK MMAs run during the epilogue
-      if (next_tok >= 0) write_q(next_tok, g + 1);
+      if (!cur.done()) ok = write_q(cur.gq, cur.n);
+      if (!ok) break;
       // ---- epilogue of the segment: un-normalised partial (max, sum, O) ----
       ok = tc::mbar_wait(&mi->o_done[g & 3], (g >> 2) & 1, abort_flag, p.d_status, ST_EPI_TIMEOUT);
       tc::tc_fence_after();
-      if (threadIdx.x == 64) STRACE(g, 13);
+      if (threadIdx.x == 64) STRACE(cur.n - 1, 13);
       l += __shfl_xor_sync(0xffffffffu, l, 16);
       if (sub == 0) mi->lsum[half][row] = l;
       ok = quad_bar_and(quad, ok);
@@ -572,7 +583,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, StreamParams p) {
           }
         }
       }
-      if (threadIdx.x == 64) STRACE(g, 14);
+      if (threadIdx.x == 64) STRACE(cur.n - 1, 14);
       tc::tc_fence_before();
       ok = quad_bar_and(quad, ok);  // lsum, the staging rows and O are reused by the next segment
     }
@@ -624,6 +635,11 @@ cudaError_t launch_attn_stream(const AttnArgs& a, cudaStream_t st) {
   if (!tc::cached_tmap(&tmKV, a.pool, (uint64_t)a.row, (uint64_t)a.pool_rows, 1, (uint64_t)a.row * 2,
                        (uint64_t)a.row * 2 * (uint64_t)a.pool_rows, 64, TILE, 1, &err))
     return cudaErrorInvalidValue;
+  // Q_eff has the geometry of the pool: rows of d_qk values, a token's 64 heads are one "page"
+  CUtensorMap tmQ;
+  if (!tc::cached_tmap(&tmQ, a.q_eff, (uint64_t)a.d_qk, (uint64_t)a.q_rows, 1, (uint64_t)a.d_qk * 2,
+                       (uint64_t)a.d_qk * 2 * (uint64_t)a.q_rows, 64, HEADS, 1, &err))
+    return cudaErrorInvalidValue;
   StreamParams p;
   p.q_eff = a.q_eff; p.tables = a.tables; p.tok_table = a.tok_table; p.segs = a.segs; p.cta_seg = a.cta_seg;
   p.part_m = a.part_m; p.part_l = a.part_l; p.part_o = a.part_o; p.d_status = a.d_status;
@@ -637,8 +653,8 @@ cudaError_t launch_attn_stream(const AttnArgs& a, cudaStream_t st) {
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  if (a.d_qk == 576) return launch_pdl(k_attn_stream<9>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(9), st, 1, tmKV, p);
-  return launch_pdl(k_attn_stream<8>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(8), st, 1, tmKV, p);
+  if (a.d_qk == 576) return launch_pdl(k_attn_stream<9>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(9), st, 1, tmKV, tmQ, p);
+  return launch_pdl(k_attn_stream<8>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(8), st, 1, tmKV, tmQ, p);
 }
 
 }  // namespace fst

@@ -862,10 +862,10 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
   // runs of about equal COST; a run that crosses a token boundary yields one segment (and one
   // partial) per token it touches.  The unit is a cache page where pages hold 64 tokens, else
   // ATTN_TILE rows.  Cost, in half units: 2 per tile plus SEG_COST2 per segment -- a segment
-  // pays for loading Q_eff, refilling the pipeline and writing its partial (measured: about
-  // five and a half 64-token tiles of the streaming kernel).
+  // pays for its Q_eff block (one ring slot), refilling the pipeline and writing its partial
+  // (measured: about four 64-token tiles of the streaming kernel).
   const int unit = c->cfg.page_tokens == 64 ? 64 : ATTN_TILE;
-  long long SEG_COST2 = unit == 64 ? 11 : 5;
+  long long SEG_COST2 = unit == 64 ? 8 : 5;
   if (const char* e = getenv("FST_MLA_SEG_COST")) {  // tuning aid: the segment's cost in half tiles
     const int v = atoi(e);
     if (v > 0 && v < 64) SEG_COST2 = v;
