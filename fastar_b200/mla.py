@@ -313,6 +313,18 @@ class MlaContext:
         self._check(self.lib.fst_cuda_mla_forward(self._h, lid, _u16(h), _u16(out), _i32(s), _i32(p), _i32(q),
                                                   len(s), int(causal)))
 
+    def bind_forward(self, lid: int, h: np.ndarray, out: np.ndarray, s, p, q, causal: bool = False):
+        """forward_into() with the argument conversion done once: returns a callable that makes
+        exactly the C call (for loops that reuse the same page-locked buffers, as a host that
+        calls the C ABI directly would)."""
+        keep = (h, out, s, p, q)  # the arrays must outlive the pointers
+        args = (self._h, lid, _u16(h), _u16(out), _i32(s), _i32(p), _i32(q), len(s), int(causal))
+        fn, check = self.lib.fst_cuda_mla_forward, self._check
+
+        def call(_keep=keep):
+            check(fn(*args))
+        return call
+
     def attention_only(self, lid: int, q_eff: np.ndarray) -> np.ndarray:
         q_eff = np.ascontiguousarray(q_eff, np.uint16)
         T = self.plan_tokens()
