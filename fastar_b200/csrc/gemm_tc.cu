@@ -262,9 +262,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
       }
       if (m0 + col < p.M) {
         bf16* c = p.C + z * p.c_bs + (long long)(m0 + col) * p.ldc + n0 + row;
+        if (n0 + row + 3 < p.N && (reinterpret_cast<uintptr_t>(c) & 7) == 0) {
+          // one 8-byte store (the output may be page-locked host memory: fewer, fuller writes)
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0], acc[1]), hi = __floats2bfloat162_rn(acc[2], acc[3]);
+          *reinterpret_cast<uint2*>(c) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (n0 + row + j < p.N) c[j] = f2bf(acc[j]);
+          for (int j = 0; j < 4; ++j)
+            if (n0 + row + j < p.N) c[j] = f2bf(acc[j]);
+        }
       }
     }
     cluster_sync_all();  // nobody leaves while a peer still reads its shared memory

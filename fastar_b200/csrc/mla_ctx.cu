@@ -81,6 +81,8 @@ struct FstMlaCtx {
   int max_parts = 0;
   uint16_t* h_pinned = nullptr;  // [max_tokens, hidden] staging for the host-buffer entry point
   int* d_status = nullptr;
+  const bf16* out_src = nullptr;  // where the last layer call left its output rows
+  bool out_zero_copy = true;
   int* h_status = nullptr;  // page-locked copy of the status word, fetched on the stream before a sync
 
   // plan (device)
@@ -536,6 +538,7 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
   if (!rc && cudaHostAlloc((void**)&x->h_status, sizeof(int), cudaHostAllocDefault) != cudaSuccess)
     rc = fail(FST_MLA_ERR_CUDA, "cudaHostAlloc failed");
   if (!rc) *x->h_status = 0;
+  if (const char* e = getenv("FST_MLA_ZERO_COPY_OUT")) x->out_zero_copy = atoi(e) != 0;  // tuning aid
   if (!rc && cudaHostAlloc((void**)&x->h_pinned, T * d.hidden * sizeof(uint16_t), cudaHostAllocDefault) != cudaSuccess)
     rc = fail(FST_MLA_ERR_CUDA, "cudaHostAlloc failed");
   if (rc) {
@@ -1034,19 +1037,21 @@ int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* 
   }
   // page-locked caller buffers are copied directly; pageable ones go through the context's
   // page-locked staging buffer (an asynchronous copy from pageable memory is neither)
-  auto page_locked = [](const void* p) {
+  void* out_mapped = nullptr;  // the device's address of a page-locked, mapped h_out
+  auto page_locked = [](const void* p, void** mapped) {
     cudaPointerAttributes at;
     if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
       cudaGetLastError();
       return false;
     }
+    if (mapped && at.type == cudaMemoryTypeHost) *mapped = at.devicePointer;
     return at.type == cudaMemoryTypeHost;
   };
   // the input rows start their way to the device before the plan is built (the plan takes tens
   // of microseconds of host time and does not depend on them)
   const bool early = T_in > 0 && T_in <= c->cfg.max_tokens;
   const size_t bytes_in = (size_t)T_in * c->d.hidden * sizeof(uint16_t);
-  const bool in_direct = page_locked(h_in), out_direct = page_locked(h_out);
+  const bool in_direct = page_locked(h_in, nullptr), out_direct = page_locked(h_out, &out_mapped);
   c->compress_done = false;
   if (early) {
     CU(cudaSetDevice(c->cfg.device));
@@ -1068,8 +1073,13 @@ int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* 
   if ((rc = check_run(c, lid))) return rc;
   if (c->T == 0) return FST_MLA_OK;
   const size_t bytes = (size_t)c->T * c->d.hidden * sizeof(uint16_t);
-  if ((rc = fst_cuda_mla_run_device(c, lid, c->d_h, c->d_out))) return rc;
-  CU(cudaMemcpyAsync(out_direct ? (void*)h_out : (void*)c->h_pinned, c->d_out, bytes, cudaMemcpyDeviceToHost, c->stream));
+  // A page-locked output buffer that the device can address is written by the last GEMM itself
+  // (512 KB of posted writes spread over the kernel) instead of by a copy behind it.
+  const bool zero_copy = out_direct && out_mapped && c->out_zero_copy && !c->profiling;
+  c->out_src = zero_copy ? (const bf16*)out_mapped : c->d_out;
+  if ((rc = fst_cuda_mla_run_device(c, lid, c->d_h, zero_copy ? out_mapped : (void*)c->d_out))) return rc;
+  if (!zero_copy)
+    CU(cudaMemcpyAsync(out_direct ? (void*)h_out : (void*)c->h_pinned, c->d_out, bytes, cudaMemcpyDeviceToHost, c->stream));
   // while the device works: the RoPE rows of the positions that a decode step asks for next
   for (int b = 0; b < n_seqs; ++b)
     if (q_lens[b] > 0 && q_lens[b] <= 4)
@@ -1149,13 +1159,13 @@ int fst_cuda_mla_get_stage(FstMlaCtx* c, int stage, uint16_t* host_out, size_t b
     case FST_MLA_STAGE_QEFF: src = c->d_qeff; n = (size_t)c->T * d.H * d.d_qk; break;
     case FST_MLA_STAGE_OLAT: src = c->d_olat; n = (size_t)c->T * d.H * d.d_v; break;
     case FST_MLA_STAGE_LOW: src = c->d_low; n = (size_t)c->T * d.low; break;
-    case FST_MLA_STAGE_OUT: src = c->d_out; n = (size_t)c->T * d.hidden; break;
+    case FST_MLA_STAGE_OUT: src = c->out_src ? c->out_src : c->d_out; n = (size_t)c->T * d.hidden; break;
     default: return fail(FST_MLA_ERR_ARG, "unknown stage %d", stage);
   }
   if (bytes != n * 2) return fail(FST_MLA_ERR_ARG, "stage %d holds %zu bytes, caller asked for %zu", stage, n * 2, bytes);
   CU(cudaSetDevice(c->cfg.device));
   CU(cudaStreamSynchronize(c->stream));
-  CU(cudaMemcpy(host_out, src, bytes, cudaMemcpyDeviceToHost));
+  CU(cudaMemcpy(host_out, src, bytes, cudaMemcpyDefault));
   return FST_MLA_OK;
 }
 

@@ -187,7 +187,9 @@ int fst_cuda_mla_run_device(FstMlaCtx* ctx, int lid, const void* d_h_in, void* d
  * h_in / h_out are host bf16 [sum q_lens, hidden] (may alias: the reference works in place,
  * src/fst_engine.cpp:3889).  Rows are written at pos0[b] .. pos0[b]+q_lens[b]-1.
  * Page-locked buffers (cudaHostAlloc / cudaHostRegister) are copied directly; pageable ones
- * go through a page-locked staging buffer of the context, which costs two extra memcpy. */
+ * go through a page-locked staging buffer of the context, which costs two extra memcpy.  A
+ * page-locked h_out that the device can address (cudaHostAlloc memory is) receives its rows
+ * from the last GEMM itself, with no copy behind the layer. */
 int fst_cuda_mla_forward(FstMlaCtx* ctx, int lid, const uint16_t* h_in, uint16_t* h_out,
                          const int32_t* seq_ids, const int32_t* pos0, const int32_t* q_lens,
                          int32_t n_seqs, int32_t causal);

@@ -165,3 +165,31 @@ def test_plan_is_kept_across_the_layers_of_a_step():
         c4 = ctx.plan_counts()
         assert (c4["built"] - c3["built"], c4["reused"] - c3["reused"]) == (1, 0)
         assert np.array_equal(out0, out3)
+
+
+def test_page_locked_buffers_take_the_direct_paths():
+    """fst_cuda_mla_forward with page-locked, device-addressable buffers (input copied straight from
+    the caller's buffer, output rows written by the last GEMM itself) gives the bits of the same call
+    with pageable buffers (staged copies)."""
+    import torch
+    lens, B = [200, 1, 64, 513], 4
+    cfg = mla.make_config(mla.PRESET_BASELINE, n_pages=sum((L + 65) // 64 for L in lens) + 4, max_tokens=B, max_seqs=B)
+    bits, _ = weights_for(mla.PRESET_BASELINE)
+    with mla.MlaContext(cfg) as ctx:
+        ctx.set_layer_weights(0, bits)
+        seqs = []
+        for b, L in enumerate(lens):
+            s = ctx.seq_alloc()
+            ctx.cache_write(0, s, 0, synth.to_bf16_bits(synth.cache_rows_f32(cfg, 0, b, L)))
+            seqs.append(s)
+        h = synth.to_bf16_bits(synth.hidden_f32(cfg, 0, B, (0,)))
+        ref = ctx.forward(0, h, seqs, lens, [1] * B)
+        for s, L in zip(seqs, lens):
+            ctx.seq_truncate(s, L)
+        h_pin = torch.from_numpy(h.view(np.int16).copy()).pin_memory()
+        out_pin = torch.zeros_like(h_pin).pin_memory()
+        call = ctx.bind_forward(0, h_pin.numpy().view(np.uint16), out_pin.numpy().view(np.uint16),
+                                np.array(seqs, np.int32), np.array(lens, np.int32), np.ones(B, np.int32))
+        call()
+        assert np.array_equal(out_pin.numpy().view(np.uint16), ref)
+        assert np.array_equal(ctx.get_stage(mla.STAGE_OUT), ref)
