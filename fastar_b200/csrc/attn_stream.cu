@@ -177,7 +177,8 @@ struct TileCursor {
   __device__ __forceinline__ void load(const AttnSeg* segs) {
     if (si < seg_end) {
       sg = segs[si];
-      n_tiles = (sg.kv_end - sg.kv_begin + TILE - 1) / TILE;
+      // kv_begin is page aligned except at the edge of a sliding window
+      n_tiles = (sg.kv_end - (sg.kv_begin & ~(TILE - 1)) + TILE - 1) / TILE;
       gq = g++;
     }
   }
@@ -438,6 +439,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
     while (!cur.done() && ok) {
       const AttnSeg sg = cur.sg;
       const int n_tiles = cur.n_tiles;
+      const unsigned span = (unsigned)(sg.kv_end - sg.kv_begin);
       // Q_eff of the first segment; later segments are written at the end of their predecessor
       if (cur.sidx == 0) ok = write_q(cur.gq, cur.n);
       float m_used = -INFINITY, l = 0.0f;
@@ -448,7 +450,8 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
         ok = tc::mbar_wait(&mi->s_full[n & 1], (n >> 1) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
         if (threadIdx.x == 64) STRACE(n, 8);
         tc::tc_fence_after();
-        const int tok0 = sg.kv_begin + t * TILE + half * 32 + sub * 16;
+        // this thread's first token, relative to the first visible row; visible: [0, span)
+        const int rel0 = (sg.kv_begin & ~(TILE - 1)) - sg.kv_begin + t * TILE + half * 32 + sub * 16;
         float sc[16], sc2[16];
         const int b0 = (2 * n) % 3, b1 = (2 * n + 1) % 3;
         tmem_ld16x32(lane_addr + COL_S + b0 * TILE + half * 32, sc);
@@ -459,7 +462,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
         float mx = -INFINITY;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          sc[j] = tok0 + j < sg.kv_end ? (sc[j] + sc2[j]) * p.scale_log2 : -INFINITY;
+          sc[j] = (unsigned)(rel0 + j) < span ? (sc[j] + sc2[j]) * p.scale_log2 : -INFINITY;
           mx = fmaxf(mx, sc[j]);
         }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));

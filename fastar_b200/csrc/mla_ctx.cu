@@ -104,6 +104,7 @@ struct FstMlaCtx {
   std::vector<FstMlaSeqStep> last_steps;  // what the valid plan was built from (every layer of a
   int last_causal = 0;                    // model step asks for the same plan again)
   bool plan_reuse = true;
+  int32_t window = 0;  // sliding window applied by fst_cuda_mla_forward (0: none)
   int64_t plans_built = 0, plans_reused = 0;
   bool planned = false;
   int T = 0, n_segs = 0, n_parts = 0, n_ctas = 0;
@@ -849,7 +850,7 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
 
   std::vector<float> lut((size_t)T * d.rope);
   std::vector<long long> dst(T);
-  std::vector<int32_t> tok_table(T), tables, kvlen(T), tok_part(T + 1);
+  std::vector<int32_t> tok_table(T), tables, kvlen(T), kvlo(T), tok_part(T + 1);
   int t = 0;
   for (int b = 0; b < n_seqs; ++b) {
     const FstMlaSeqStep& s = steps[b];
@@ -863,6 +864,9 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
       int len = s.append ? s.pos0 + s.q_len : s.pos0;
       if (causal && s.append) len = std::min(len, s.pos0 + i + 1);  // drop s > seq_pos_ + m (3626)
       kvlen[t] = len;
+      // sliding window (the draft model's attention, src/fst_engine.cpp:2534-2576 keeps the last
+      // `window_size` rows in a ring): the last `window` rows of what the token may see
+      kvlo[t] = s.window > 0 ? std::max(0, len - s.window) : 0;
     }
   }
   if ((int)tables.size() > c->tables_cap) return fail(FST_MLA_ERR_CAPACITY, "block tables overflow");
@@ -880,9 +884,12 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
     if (v > 0 && v < 64) SEG_COST2 = v;
   }
   long long total_tiles = 0, kv_rows = 0, n_nonempty = 0;
+  // tiles are counted from the tile that holds the first visible row
+  auto tile0_of = [&](int i) { return kvlo[i] / unit; };
+  auto tiles_of = [&](int i) { return (kvlen[i] + unit - 1) / unit - tile0_of(i); };
   for (int i = 0; i < T; ++i) {
-    total_tiles += (kvlen[i] + unit - 1) / unit;
-    kv_rows += kvlen[i];
+    total_tiles += tiles_of(i);
+    kv_rows += kvlen[i] - kvlo[i];
     n_nonempty += kvlen[i] > 0;
   }
   int max_ctas = c->n_sm;
@@ -896,7 +903,6 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
   {
     int tok = 0, tile_in_tok = 0, part = 0;
     tok_part[0] = 0;
-    auto tiles_of = [&](int i) { return (kvlen[i] + unit - 1) / unit; };
     auto skip_empty = [&]() {
       while (tok < T && tile_in_tok >= tiles_of(tok)) {
         ++tok;
@@ -924,8 +930,8 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
         const int take = (int)std::min<long long>(room, tiles_of(tok) - tile_in_tok);
         AttnSeg sg;
         sg.tok = tok;
-        sg.kv_begin = tile_in_tok * unit;
-        sg.kv_end = std::min(kvlen[tok], (tile_in_tok + take) * unit);
+        sg.kv_begin = std::max(kvlo[tok], (tile0_of(tok) + tile_in_tok) * unit);  // unaligned only at a window's edge
+        sg.kv_end = std::min(kvlen[tok], (tile0_of(tok) + tile_in_tok + take) * unit);
         sg.part = part++;
         segs.push_back(sg);
         if (tile_in_tok == 0) --toks_left;
@@ -983,6 +989,13 @@ int fst_cuda_mla_set_plan_reuse(FstMlaCtx* c, int32_t on) {
   return FST_MLA_OK;
 }
 
+int fst_cuda_mla_set_window(FstMlaCtx* c, int32_t window) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (window < 0) return fail(FST_MLA_ERR_ARG, "negative window");
+  c->window = window;
+  return FST_MLA_OK;
+}
+
 int fst_cuda_mla_plan_counts(FstMlaCtx* c, int64_t* built, int64_t* reused) {
   if (!c) return fail(FST_MLA_ERR_ARG, "null context");
   if (built) *built = c->plans_built;
@@ -1032,7 +1045,7 @@ int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* 
   std::vector<FstMlaSeqStep> steps(n_seqs);
   long long T_in = 0;
   for (int b = 0; b < n_seqs; ++b) {
-    steps[b] = FstMlaSeqStep{seq_ids[b], pos0[b], q_lens[b], -1, 1};
+    steps[b] = FstMlaSeqStep{seq_ids[b], pos0[b], q_lens[b], -1, 1, c->window};
     if (q_lens[b] > 0) T_in += q_lens[b];
   }
   // page-locked caller buffers are copied directly; pageable ones go through the context's

@@ -100,6 +100,8 @@ void FSTEngine::reset_session() {
   is_prefill_ = true;
 }
 
+void FSTEngine::set_window(int window) { check(fst_cuda_mla_set_window(ctx_, window), "set_window"); }
+
 void FSTEngine::rollback(int keep_len) {
   int32_t len = 0;
   check(fst_cuda_mla_seq_len(ctx_, seq_, &len), "seq_len");

@@ -85,6 +85,9 @@ class FSTEngine {
   bool is_prefill() const { return is_prefill_; }
   // Speculative-decoding rollback (6132-6147): forget rows >= keep_len of the current sequence.
   void rollback(int keep_len);
+  // Sliding window of the draft model's attention (draft_cfg_.window_size, 2534-2576): process_mla
+  // attends to the last `window` rows only; 0 switches it off.
+  void set_window(int window);
 
   // Extra sequences for batched decode.
   int new_sequence();

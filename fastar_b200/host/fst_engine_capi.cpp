@@ -76,6 +76,7 @@ int fst_engine_seq_pos(FSTEngine* e) { return e->seq_pos(); }
 void fst_engine_advance(FSTEngine* e, int n) { e->advance(n); }
 void fst_engine_set_prefill(FSTEngine* e, int p) { e->set_prefill(p != 0); }
 int fst_engine_rollback(FSTEngine* e, int keep) { return guard([&] { e->rollback(keep); }); }
+int fst_engine_set_window(FSTEngine* e, int window) { return guard([&] { e->set_window(window); }); }
 int fst_engine_new_sequence(FSTEngine* e) {
   int s = -1;
   guard([&] { s = e->new_sequence(); });

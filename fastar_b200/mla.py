@@ -51,7 +51,7 @@ class Weights(C.Structure):
 
 class SeqStep(C.Structure):
     _fields_ = [("seq", C.c_int32), ("pos0", C.c_int32), ("q_len", C.c_int32),
-                ("rope_pos0", C.c_int32), ("append", C.c_int32)]
+                ("rope_pos0", C.c_int32), ("append", C.c_int32), ("window", C.c_int32)]
 
 
 def make_config(preset=PRESET_BASELINE, *, n_layers=1, n_pages=256, max_seqs=64, max_tokens=64, device=0,
@@ -110,6 +110,7 @@ def load_library() -> C.CDLL:
     L.fst_cuda_mla_kernel_times.argtypes = [vp, C.POINTER(C.c_float), i32p]
     L.fst_cuda_mla_plan_info.argtypes = [vp, i32p, i32p, C.POINTER(i64)]
     L.fst_cuda_mla_set_plan_reuse.argtypes = [vp, i32]
+    L.fst_cuda_mla_set_window.argtypes = [vp, i32]
     L.fst_cuda_mla_plan_counts.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
     L.fst_cuda_mla_attention_noalloc.argtypes = [vp, vp, i32, i32, i32, i32, C.c_float, vp, vp]
     _lib = L
@@ -259,11 +260,12 @@ class MlaContext:
 
     # -- the layer --
     def plan(self, steps, causal: bool = False) -> int:
-        """steps: iterable of (seq, pos0, q_len[, rope_pos0[, append]]).  Returns T."""
+        """steps: iterable of (seq, pos0, q_len[, rope_pos0[, append[, window]]]).  Returns T."""
         arr = (SeqStep * len(steps))()
         for i, s in enumerate(steps):
             s = tuple(s)
-            arr[i] = SeqStep(s[0], s[1], s[2], s[3] if len(s) > 3 else -1, s[4] if len(s) > 4 else 1)
+            arr[i] = SeqStep(s[0], s[1], s[2], s[3] if len(s) > 3 else -1, s[4] if len(s) > 4 else 1,
+                             s[5] if len(s) > 5 else 0)
         self._check(self.lib.fst_cuda_mla_plan(self._h, arr, len(steps), int(causal)))
         return self.plan_tokens()
 
@@ -275,6 +277,10 @@ class MlaContext:
     def set_plan_reuse(self, on: bool) -> None:
         """Whether a plan request equal to the valid plan keeps it (default) or rebuilds it."""
         self._check(self.lib.fst_cuda_mla_set_plan_reuse(self._h, 1 if on else 0))
+
+    def set_window(self, window: int) -> None:
+        """Sliding window that forward() applies to every sequence (0: none)."""
+        self._check(self.lib.fst_cuda_mla_set_window(self._h, int(window)))
 
     def plan_counts(self) -> dict:
         built, reused = C.c_int64(0), C.c_int64(0)

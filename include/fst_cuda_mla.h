@@ -105,6 +105,9 @@ typedef struct FstMlaSeqStep {
   int32_t rope_pos0; /* RoPE position of the first new token; < 0: same as pos0 */
   int32_t append;    /* 1: write the new rows and attend to [0, pos0+q_len);
                         0: attend to [0, pos0) only (a KV slice that does not own them) */
+  int32_t window;    /* > 0: every new token attends only to the last `window` rows it may see
+                        (the draft model's sliding window, src/fst_engine.cpp:2534-2576 keeps
+                        window_size rows in a ring); <= 0: to all of them */
 } FstMlaSeqStep;
 
 /* Intermediate buffers of the last run, the stage list of FST_MLA_TRACE
@@ -178,6 +181,8 @@ int fst_cuda_mla_plan(FstMlaCtx* ctx, const FstMlaSeqStep* steps, int32_t n_seqs
  * between) returns at once and keeps the tables that are on the device: that is what layers
  * 2 .. L of a step see, also through fst_cuda_mla_forward.  on = 0 rebuilds every time. */
 int fst_cuda_mla_set_plan_reuse(FstMlaCtx* ctx, int32_t on);
+/* Sliding window that fst_cuda_mla_forward applies to every sequence of its calls (0: none). */
+int fst_cuda_mla_set_window(FstMlaCtx* ctx, int32_t window);
 /* Plans built and plan requests answered by the valid plan, since the context was created. */
 int fst_cuda_mla_plan_counts(FstMlaCtx* ctx, int64_t* built, int64_t* reused);
 /* Enqueue the layer for the current plan; h_in / h_out are device bf16 [T, hidden]

@@ -229,6 +229,21 @@ def merge_partials(cfg, m, l, o, sinks=None):
     return out
 
 
+def attention_window(cfg, q_eff, cache, kv_len, n_q, window, pos0=0, causal=False, sinks=None):
+    """Sliding-window attention (the draft model keeps only the last `window_size` rows, reference
+    src/fst_engine.cpp:2534-2576): query token i sees the last `window` rows of what attention()
+    lets it see.  A composition of attention_partial over [lo, hi) and merge_partials, per token."""
+    H = cfg.n_heads
+    q_eff = _f(q_eff)
+    out = np.empty((n_q * H, dims(cfg)["d_v"]), np.float32)
+    for i in range(n_q):
+        hi = min(kv_len, pos0 + i + 1) if causal else kv_len
+        lo = max(0, hi - window) if window > 0 else 0
+        m, l, o = attention_partial(cfg, q_eff[i * H:(i + 1) * H], cache, lo, hi, 1)
+        out[i * H:(i + 1) * H] = merge_partials(cfg, m[None], l[None], o[None], sinks)
+    return out
+
+
 @dataclass
 class ForwardResult:
     out: np.ndarray

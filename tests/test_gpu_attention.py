@@ -153,3 +153,54 @@ def test_long_and_short_sequences_mixed():
     # one 20 000-token sequence among short ones: its tiles spread over most CTAs while the short
     # sequences share the remaining ones; the long row's parts are merged from ~140 partials
     run_case(mla.PRESET_BASELINE, mla.IMPL_TENSOR, [20000, 3, 64, 130, 65, 1], seed=12, ulps=1)
+
+
+@pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
+@pytest.mark.parametrize("preset", PRESETS, ids=[p[0] for p in PRESETS])
+def test_sliding_window(preset, impl):
+    """FstMlaSeqStep.window: every query token sees only the last `window` rows of what it may see
+    (the draft model's window, src/fst_engine.cpp:2534-2576).  Windows that start inside a page, on
+    a page boundary, cover the whole context, and a causal block whose window moves with the token;
+    different windows in one batch."""
+    preset, impl = preset[1], impl[1]
+    cases = [(300, 1, False, 100), (300, 1, False, 128), (640, 1, False, 64), (70, 1, False, 4096),
+             (5000, 1, False, 1000), (513, 1, False, 1), (200, 5, True, 128), (1000, 16, True, 130)]
+    n_pages = sum((L + q + 63) // 64 for L, q, _, _ in cases) + 8
+    for causal in (False, True):
+        sub = [c for c in cases if c[2] == causal]
+        groups = {}
+        for c in sub:
+            groups.setdefault(c[1], []).append(c)
+        for q_len, grp in groups.items():
+            B = len(grp)
+            cfg, ctx = setup_ctx(preset, impl, n_pages, B * q_len, max_seqs=B + 8)
+            try:
+                d, H = mla.dims_of(cfg), cfg.n_heads
+                rng = np.random.default_rng(11)
+                sinks = rng.standard_normal(H).astype(np.float32) if preset == mla.PRESET_FASTAR_V4 else None
+                ctx.set_layer_weights(0, dummy_weights(cfg, sinks))
+                seqs, caches = [], []
+                for b, (L, _, _, _) in enumerate(grp):
+                    s = ctx.seq_alloc()
+                    rows = synth.to_bf16_bits(synth.cache_rows_f32(cfg, 3, b, L + q_len))
+                    ctx.cache_write(0, s, 0, rows)
+                    seqs.append(s)
+                    caches.append(synth.from_bf16_bits(rows))
+                T = ctx.plan([(s, L, q_len, -1, 1 if causal else 0, W) for s, (L, _, _, W) in zip(seqs, grp)], causal=causal)
+                assert T == B * q_len
+                info = ctx.plan_info()
+                want_rows = sum(sum(min(W, (L + i + 1) if causal else L) for i in range(q_len)) for L, _, _, W in grp)
+                assert info["kv_rows"] == want_rows
+                q = synth.to_bf16_bits(rng.standard_normal((T * H, d["d_qk"])).astype(np.float32))
+                got = ctx.attention_only(0, q)
+                ocfg, qf = oracle_cfg(cfg), synth.from_bf16_bits(q)
+                for b, (L, _, _, W) in enumerate(grp):
+                    kv_len = L + q_len if causal else L
+                    want = O.attention_window(ocfg, qf[b * q_len * H:(b + 1) * q_len * H], caches[b], kv_len, q_len, W,
+                                              pos0=L, causal=causal, sinks=sinks)
+                    if preset == mla.PRESET_FASTAR_V4:
+                        for r in range(q_len * H):
+                            want[r, -64:] = O.rope_apply(want[r, -64:], L + r // H, inverse=True, round_bf16=True)
+                    check_close(got[b * q_len * H:(b + 1) * q_len * H], want, f"L={L} q={q_len} W={W}")
+            finally:
+                ctx.close()

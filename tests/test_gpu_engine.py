@@ -33,6 +33,7 @@ def load():
     L.fst_engine_advance.argtypes = [C.c_void_p, C.c_int]
     L.fst_engine_set_prefill.argtypes = [C.c_void_p, C.c_int]
     L.fst_engine_rollback.argtypes = [C.c_void_p, C.c_int]
+    L.fst_engine_set_window.argtypes = [C.c_void_p, C.c_int]
     L.fst_engine_randmat_test.argtypes = [C.c_void_p] + [C.POINTER(C.c_double)] * 3 + [C.c_int]
     return L
 
@@ -99,6 +100,11 @@ def test_prefill_then_decode_like_the_engine(preset):
         got = process(L, e, h)
         want = O.mla_forward(ocfg, rounded, synth.from_bf16_bits(h), 26, cache, causal=False, want_trace=False).out
         check_close(got, want, "decode after rollback", ulps=ulps)
+        # a window that covers the whole context changes nothing; a negative one is an error
+        assert L.fst_engine_set_window(e, 4096) == 0
+        check_close(process(L, e, h), want, "window over the whole context", ulps=ulps)
+        assert L.fst_engine_set_window(e, -1) != 0
+        assert L.fst_engine_set_window(e, 0) == 0
         # the reference asserts seq_pos_ + M <= max_seq: here it is an error, not a crash
         L.fst_engine_advance(e, 128)
         buf = np.zeros((1, 4096), np.uint16)

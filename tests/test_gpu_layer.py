@@ -193,3 +193,36 @@ def test_page_locked_buffers_take_the_direct_paths():
         call()
         assert np.array_equal(out_pin.numpy().view(np.uint16), ref)
         assert np.array_equal(ctx.get_stage(mla.STAGE_OUT), ref)
+
+
+def test_forward_with_a_window_set_on_the_context():
+    """fst_cuda_mla_set_window: process_mla attends to the last `window` rows only.  Checked on the
+    attention stage: the oracle's windowed attention of the Q_eff the GPU produced; the appended row
+    and the other stages do not depend on the window."""
+    lens, B, W = [300, 64, 1000], 3, 100
+    cfg = mla.make_config(mla.PRESET_BASELINE, n_pages=sum((L + 65) // 64 for L in lens) + 4, max_tokens=B, max_seqs=B)
+    bits, _ = weights_for(mla.PRESET_BASELINE)
+    ocfg, H = oracle_cfg(cfg), cfg.n_heads
+    with mla.MlaContext(cfg) as ctx:
+        ctx.set_layer_weights(0, bits)
+        seqs = []
+        for b, L in enumerate(lens):
+            s = ctx.seq_alloc()
+            ctx.cache_write(0, s, 0, synth.to_bf16_bits(synth.cache_rows_f32(cfg, 0, b, L)))
+            seqs.append(s)
+        h = synth.to_bf16_bits(synth.hidden_f32(cfg, 0, B, (0,)))
+        ctx.set_window(W)
+        out_w = ctx.forward(0, h, seqs, lens, [1] * B)
+        q_eff = synth.from_bf16_bits(ctx.get_stage(mla.STAGE_QEFF))
+        o_lat = ctx.get_stage(mla.STAGE_OLAT)
+        for b, (s, L) in enumerate(zip(seqs, lens)):
+            cache = synth.from_bf16_bits(ctx.cache_read(0, s, 0, L + 1))
+            want = O.attention_window(ocfg, q_eff[b * H:(b + 1) * H], cache, L + 1, 1, W)
+            check_close(o_lat[b * H:(b + 1) * H], want, f"window, seq {b}")
+        for s, L in zip(seqs, lens):
+            ctx.seq_truncate(s, L)
+        ctx.set_window(0)
+        out_full = ctx.forward(0, h, seqs, lens, [1] * B)
+        assert not np.array_equal(out_w[0], out_full[0])      # 301 rows against the last 100
+        # 65 rows: the window covers them all (the split into partials differs, so not bit for bit)
+        check_close(out_w[1:2], synth.from_bf16_bits(out_full[1:2]), "window covers the context")

@@ -140,3 +140,21 @@ def test_attn_norm_is_rmsnorm_in_front_of_the_layer():
     assert np.array_equal(fused.out.view(np.uint32), plain.out.view(np.uint32))
     assert np.array_equal(cache_a.view(np.uint32), cache_b.view(np.uint32))
     assert not np.array_equal(fused.out, O.mla_forward(cfg, w, h, 0, np.zeros((8, 80), np.float32), causal=True).out)
+
+
+def test_window_attention_is_attention_over_the_last_rows():
+    """attention_window: a window that covers everything equals attention(); a shorter one equals
+    attention() over a cache cut to the window's rows (softmax does not care where the rows sit).
+    Outputs are bf16-rounded and the partial + merge route rounds P against a per-slice maximum, so
+    the two may differ by one bf16 step (values here are below 4: 2^-6 = 1.6e-2)."""
+    cfg = O.make_cfg(O.PRESET_BASELINE)
+    rng = np.random.default_rng(5)
+    H, L = cfg.n_heads, 300
+    cache = O.bf16_round(rng.standard_normal((L, 576)).astype(np.float32))
+    q = O.bf16_round(rng.standard_normal((H, 576)).astype(np.float32))
+    full = O.attention(cfg, q, cache, L, 1)
+    assert np.allclose(O.attention_window(cfg, q, cache, L, 1, 0), full, atol=1.6e-2)
+    assert np.allclose(O.attention_window(cfg, q, cache, L, 1, 4096), full, atol=1.6e-2)
+    for W in (1, 63, 64, 100, 299):
+        cut = np.ascontiguousarray(cache[L - W:])
+        assert np.allclose(O.attention_window(cfg, q, cache, L, 1, W), O.attention(cfg, q, cut, W, 1), atol=1.6e-2), W
