@@ -29,7 +29,7 @@ def dummy_weights(cfg, sinks=None):
     return w
 
 
-def run_case(preset, impl, lens, q_len=1, causal=False, seed=0, q_std=1.0, shuffle_pages=True, ulps=0):
+def run_case(preset, impl, lens, q_len=1, causal=False, seed=0, q_std=1.0, shuffle_pages=True, ulps=0, windows=None):
     n_pages = sum((L + q_len + 63) // 64 for L in lens) + 8
     B = len(lens)
     cfg, ctx = setup_ctx(preset, impl, n_pages, B * q_len, max_seqs=B + 8)
@@ -53,7 +53,8 @@ def run_case(preset, impl, lens, q_len=1, causal=False, seed=0, q_std=1.0, shuff
             ctx.cache_write(0, s, 0, rows)
             seqs.append(s)
             caches.append(synth.from_bf16_bits(rows))
-        T = ctx.plan([(s, L, q_len, -1, 0 if not causal else 1) for s, L in zip(seqs, lens)], causal=causal)
+        windows = windows or [0] * B
+        T = ctx.plan([(s, L, q_len, -1, 0 if not causal else 1, W) for s, L, W in zip(seqs, lens, windows)], causal=causal)
         assert T == B * q_len
         q = synth.to_bf16_bits((rng.standard_normal((T * H, d["d_qk"])) * q_std).astype(np.float32))
         got = ctx.attention_only(0, q)
@@ -61,8 +62,12 @@ def run_case(preset, impl, lens, q_len=1, causal=False, seed=0, q_std=1.0, shuff
         qf = synth.from_bf16_bits(q)
         for b, L in enumerate(lens):
             kv_len = L + q_len if causal else L
-            want = O.attention(ocfg, qf[b * q_len * H:(b + 1) * q_len * H], caches[b], kv_len, q_len, pos0=L,
-                               causal=causal, sinks=sinks)
+            if windows[b] > 0:
+                want = O.attention_window(ocfg, qf[b * q_len * H:(b + 1) * q_len * H], caches[b], kv_len, q_len,
+                                          windows[b], pos0=L, causal=causal, sinks=sinks)
+            else:
+                want = O.attention(ocfg, qf[b * q_len * H:(b + 1) * q_len * H], caches[b], kv_len, q_len, pos0=L,
+                                   causal=causal, sinks=sinks)
             if preset == mla.PRESET_FASTAR_V4:
                 # the V4 output stage carries the inverse RoPE of the tail (src/fst_engine.cpp:3716)
                 for r in range(q_len * H):
@@ -204,3 +209,20 @@ def test_sliding_window(preset, impl):
                     check_close(got[b * q_len * H:(b + 1) * q_len * H], want, f"L={L} q={q_len} W={W}")
             finally:
                 ctx.close()
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_shapes(seed):
+    """Seeded random batches through the tcgen05 kernel: ragged contexts (empty ones included), one
+    token or a causal block per sequence, some sequences with a sliding window, both presets."""
+    rng = np.random.default_rng(1000 + seed)
+    preset = PRESETS[seed % 2][1]
+    B = int(rng.integers(1, 7))
+    q_len = int(rng.choice([1, 1, 1, 2, 5, 16]))
+    causal = q_len > 1
+    lens = [int(x) for x in rng.choice([0, 1, 63, 64, 65, 500, 1500, 3000], size=B)]
+    lens = [max(L + int(rng.integers(-3, 4)), 0) for L in lens]
+    if not causal:
+        lens = [max(L, 1) for L in lens]  # a token that sees nothing has no softmax
+    windows = [int(rng.choice([0, 0, 1, 64, 100, 777])) for _ in range(B)]
+    run_case(preset, mla.IMPL_TENSOR, lens, q_len=q_len, causal=causal, seed=seed, windows=windows, ulps=1)
