@@ -1,0 +1,130 @@
+"""The `.fst` reader for MLA tensors (fastar_b200/fst_file.py) against fixtures written with the
+reference's own converter primitives (tests/golden/make_fst_fixture.py; format and loader:
+scripts/fst_converter.py:173-176, 511-546, 685-716, 1464-1500; src/fst_engine.cpp:1503-1642,
+1873-1900).  The fixture's float values are seeded, so they are rebuilt here and compared."""
+import os
+import shutil
+
+import numpy as np
+import pytest
+
+from fastar_b200 import fst_file as F
+from fastar_b200 import mla
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+MAIN, SIDE = os.path.join(GOLD, "tiny_mla.fst"), os.path.join(GOLD, "tiny_mla.fst.norm")
+N_LAYERS, HIDDEN, HEADS, Q_LORA, KV, HEAD_DIM, O_LOW = 2, 64, 4, 32, 24, 24, 48
+
+
+def main_values(seed=0):
+    """The generator's sequence of draws, in its order: {(layer, name): float32 array}."""
+    rng = np.random.default_rng(seed)
+    n = lambda *s: rng.standard_normal(s).astype(np.float32)  # noqa: E731
+    out = {}
+    for l in range(N_LAYERS):
+        out[l, "attn_norm"] = 1.0 + 0.1 * n(HIDDEN)
+        out[l, "moe_norm"] = 1.0 + 0.1 * n(HIDDEN)
+        out[l, "wq_a"] = 0.05 * n(Q_LORA, HIDDEN)
+        out[l, "wq_b"] = 0.05 * n(HEADS * HEAD_DIM, Q_LORA)
+        out[l, "wkv_a"] = 0.05 * n(KV, HIDDEN)
+        out[l, "wo_a"] = 0.05 * n(O_LOW, HEADS * HEAD_DIM // 2)
+        out[l, "wo_b"] = 0.05 * n(HIDDEN, O_LOW)
+        out[l, "q_norm"] = 1.0 + 0.1 * n(Q_LORA)
+        out[l, "kv_norm"] = 1.0 + 0.1 * n(KV)
+        out[l, "attn_sinks"] = n(HEADS)
+    return out
+
+
+def side_values(seed=1):
+    rng = np.random.default_rng(seed)
+    n = lambda *s: rng.standard_normal(s).astype(np.float32)  # noqa: E731
+    out = {}
+    for l in range(N_LAYERS):
+        out[l, "attn_norm"] = 1.2 + 0.1 * n(HIDDEN)
+        out[l, "q_norm"] = 0.9 + 0.1 * n(Q_LORA)
+        out[l, "kv_norm"] = 1.1 + 0.1 * n(KV)
+        out[l, "attn_sinks"] = n(HEADS)
+    return out
+
+
+def trunc_bits(x):
+    return (np.ascontiguousarray(x, np.float32).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def from_bits(b):
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def test_header_and_directory():
+    h = F.read_header(MAIN)
+    assert (h.version, h.hidden_dim, h.n_layers, h.n_q_heads, h.head_dim, h.vocab_size) == (2, 64, 2, 4, 24, 100)
+    assert h.rope_freq_base == 10000.0 and abs(h.rms_eps - 1e-6) < 1e-12
+    assert (h.dir_offset, h.dir_count) == (4096, 20)
+    es = F.read_directory(MAIN)
+    assert len(es) == 20 and all(e.offset % 4096 == 0 for e in es)   # page-aligned payloads
+    e = F.find(es, F.TID_Q_PROJ, 1, 1)
+    assert (e.layer, e.qtype, e.shape) == (1, F.QTYPE_Q8_0, (96, 32)) and e.size == 96 * 32 // 32 * 34
+    assert F.find(es, 4, 0).shape == (64,) and F.find(es, 99, 0) is None
+
+
+def test_bf16_and_f32_tensors_are_the_stored_bits():
+    want = main_values()
+    for l in range(N_LAYERS):
+        w = F.load_mla_layer(MAIN, l)
+        for name in ("wq_a", "wkv_a", "wo_b", "q_norm", "kv_norm", "attn_norm"):
+            assert w[name].dtype == np.uint16 and np.array_equal(w[name], trunc_bits(want[l, name])), (l, name)
+        assert w["attn_sinks"].dtype == np.float32 and np.array_equal(w["attn_sinks"], want[l, "attn_sinks"])
+        assert "moe_norm" not in w   # TID 4 is not the attention's
+
+
+def test_q8_0_tensors_expand_as_the_engine_does():
+    """All fp16 scales first, then the int8 values; value * scale, truncated to bf16: within half a
+    quantisation step (+ the bf16 truncation) of the float the converter was given."""
+    want = main_values()
+    for l in range(N_LAYERS):
+        w = F.load_mla_layer(MAIN, l)
+        for name in ("wq_b", "wo_a"):
+            x = want[l, name]
+            got = from_bits(w[name])
+            assert got.shape == x.shape
+            step = (np.abs(x.reshape(-1, 32)).max(axis=1) / 127.0)[:, None]
+            err = np.abs(got.reshape(-1, 32) - x.reshape(-1, 32))
+            assert (err <= 0.51 * step + 2.0 ** -7 * np.abs(x.reshape(-1, 32)) + 1e-7).all(), (l, name, err.max())
+            assert np.corrcoef(got.ravel(), x.ravel())[0, 1] > 0.9999
+
+
+def test_norm_sidecar_overrides_norms_and_sinks_only():
+    main, side = main_values(), side_values()
+    for l in range(N_LAYERS):
+        w = F.load_mla_layer(MAIN, l, norm_path=SIDE)
+        for name in ("attn_norm", "q_norm", "kv_norm"):
+            assert np.array_equal(w[name], trunc_bits(side[l, name]))
+        assert np.array_equal(w["attn_sinks"], side[l, "attn_sinks"])
+        assert np.array_equal(w["wq_a"], trunc_bits(main[l, "wq_a"]))
+
+
+def test_shapes_against_a_configuration():
+    cfg = mla.make_config(mla.PRESET_FASTAR_V4, hidden=HIDDEN, n_heads=HEADS, q_lora=Q_LORA, kv_lora=KV, qk_rope=8,
+                          o_groups=2, o_lora=O_LOW // 2)
+    w = F.load_mla_layer(MAIN, 0)
+    F.check_mla_shapes(w, mla.weight_shapes(cfg))
+    bad = mla.make_config(mla.PRESET_FASTAR_V4, hidden=HIDDEN, n_heads=HEADS, q_lora=Q_LORA * 2, kv_lora=KV, qk_rope=8,
+                          o_groups=2, o_lora=O_LOW // 2)
+    with pytest.raises(F.FstFormatError, match="wq_a"):
+        F.check_mla_shapes(w, mla.weight_shapes(bad))
+
+
+def test_malformed_files_are_errors(tmp_path):
+    p = tmp_path / "bad.fst"
+    p.write_bytes(b"nope" + bytes(200))
+    with pytest.raises(F.FstFormatError, match="magic"):
+        F.read_header(str(p))
+    p.write_bytes(b"FST")
+    with pytest.raises(F.FstFormatError, match="header"):
+        F.read_header(str(p))
+    cut = tmp_path / "cut.fst"
+    shutil.copy(MAIN, cut)
+    with open(cut, "r+b") as f:
+        f.truncate(20000)   # the directory survives, most payloads do not
+    with pytest.raises(F.FstFormatError, match="out of bounds"):
+        F.read_directory(str(cut))
