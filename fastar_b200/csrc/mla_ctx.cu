@@ -100,7 +100,16 @@ struct FstMlaCtx {
   // in every layer, and a decode step for the positions right after the previous step's
   std::vector<float> lut_rows;
   std::vector<int32_t> lut_tag;
-  // plan (host)
+  // plan (host): the per-token arrays live here between the two phases of a plan
+  std::vector<float> pl_lut;
+  std::vector<long long> pl_dst;
+  std::vector<int32_t> pl_tok_table, pl_tables, pl_kvlen, pl_kvlo, pl_tok_part;
+  std::vector<FstMlaSeqStep> pl_steps;
+  int pl_causal = 0;
+  size_t pl_off_b = 0;          // where the second part of the blob starts
+  bool front_uploaded = false;  // the first part (RoPE rows, append addresses) went ahead on its own
+  cudaStream_t copy_stream = nullptr;  // carries the second part while the front kernels run
+  cudaEvent_t plan_ev_b = nullptr, fwd_ev = nullptr;
   std::vector<FstMlaSeqStep> last_steps;  // what the valid plan was built from (every layer of a
   int last_causal = 0;                    // model step asks for the same plan again)
   bool plan_reuse = true;
@@ -532,8 +541,12 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
   if (!rc) rc = dev_alloc(&x->d_plan, x->plan_cap);
   if (!rc && cudaHostAlloc((void**)&x->h_plan, x->plan_cap, cudaHostAllocDefault) != cudaSuccess)
     rc = fail(FST_MLA_ERR_CUDA, "cudaHostAlloc(plan) failed");
-  if (!rc && cudaEventCreateWithFlags(&x->plan_ev, cudaEventDisableTiming) != cudaSuccess)
+  if (!rc && (cudaEventCreateWithFlags(&x->plan_ev, cudaEventDisableTiming) != cudaSuccess ||
+              cudaEventCreateWithFlags(&x->plan_ev_b, cudaEventDisableTiming) != cudaSuccess ||
+              cudaEventCreateWithFlags(&x->fwd_ev, cudaEventDisableTiming) != cudaSuccess))
     rc = fail(FST_MLA_ERR_CUDA, "cudaEventCreate failed");
+  if (!rc && cudaStreamCreateWithFlags(&x->copy_stream, cudaStreamNonBlocking) != cudaSuccess)
+    rc = fail(FST_MLA_ERR_CUDA, "cudaStreamCreate failed");
   if (!rc) rc = dev_alloc(&x->d_status, 1);
   if (!rc && cudaMemset(x->d_status, 0, sizeof(int)) != cudaSuccess) rc = fail(FST_MLA_ERR_CUDA, "cudaMemset failed");
   if (!rc && cudaHostAlloc((void**)&x->h_status, sizeof(int), cudaHostAllocDefault) != cudaSuccess)
@@ -569,6 +582,9 @@ void fst_cuda_mla_destroy(FstMlaCtx* c) {
   if (c->h_status) cudaFreeHost(c->h_status);
   if (c->h_plan) cudaFreeHost(c->h_plan);
   if (c->plan_ev) cudaEventDestroy(c->plan_ev);
+  if (c->plan_ev_b) cudaEventDestroy(c->plan_ev_b);
+  if (c->fwd_ev) cudaEventDestroy(c->fwd_ev);
+  if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
   if (c->h_pinned) cudaFreeHost(c->h_pinned);
   for (auto& es : c->ev_pool)
     for (auto& e : es.ev) cudaEventDestroy(e);
@@ -810,16 +826,27 @@ int fst_cuda_mla_pool_read(FstMlaCtx* c, int lid, uint16_t* out, size_t bytes) {
 }
 
 /* ---- planning ------------------------------------------------------------------------- */
-int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, int32_t causal) {
+}  // extern "C"
+
+namespace {
+
+// A plan has two parts.  The first is per token: RoPE rows and the addresses of the appended rows
+// -- all that the kernels in front of the attention need.  The second is the split-KV schedule
+// with the block tables.  fst_cuda_mla_forward uploads the first, launches the front kernels and
+// builds the second while they run; fst_cuda_mla_plan does both at once with one copy.
+// *reused: the valid plan answers the request, nothing was built.
+int plan_tokens_part(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, int32_t causal, bool upload_now,
+                     bool* reused) {
+  *reused = false;
   if (!c || (!steps && n_seqs > 0)) return fail(FST_MLA_ERR_ARG, "null argument");
   if (n_seqs < 0) return fail(FST_MLA_ERR_ARG, "negative sequence count");
   const Dims& d = c->d;
-  const int pt = c->cfg.page_tokens;
   // The same steps on unchanged sequences (anything that touches a sequence clears `planned`):
   // the plan on the device is still the right one -- layers 2 .. L of a model step.
   if (c->planned && c->plan_reuse && causal == c->last_causal && (size_t)n_seqs == c->last_steps.size() &&
       (n_seqs == 0 || memcmp(steps, c->last_steps.data(), (size_t)n_seqs * sizeof(FstMlaSeqStep)) == 0)) {
     ++c->plans_reused;
+    *reused = true;
     return FST_MLA_OK;
   }
   c->planned = false;
@@ -848,9 +875,16 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
     }
   }
 
-  std::vector<float> lut((size_t)T * d.rope);
-  std::vector<long long> dst(T);
-  std::vector<int32_t> tok_table(T), tables, kvlen(T), kvlo(T), tok_part(T + 1);
+  std::vector<float>& lut = c->pl_lut;
+  std::vector<long long>& dst = c->pl_dst;
+  std::vector<int32_t>&tok_table = c->pl_tok_table, &tables = c->pl_tables, &kvlen = c->pl_kvlen, &kvlo = c->pl_kvlo;
+  lut.resize((size_t)T * d.rope);
+  dst.resize(T);
+  tok_table.resize(T);
+  kvlen.resize(T);
+  kvlo.resize(T);
+  tables.clear();
+  c->pl_tok_part.assign(T + 1, 0);
   int t = 0;
   for (int b = 0; b < n_seqs; ++b) {
     const FstMlaSeqStep& s = steps[b];
@@ -870,6 +904,38 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
     }
   }
   if ((int)tables.size() > c->tables_cap) return fail(FST_MLA_ERR_CAPACITY, "block tables overflow");
+  c->pl_steps.assign(steps, steps + n_seqs);
+  c->pl_causal = causal;
+  c->T = (int)T;
+
+  // the first part of the pinned blob (once the previous plan's copies have left it)
+  CU(cudaEventSynchronize(c->plan_ev));
+  CU(cudaEventSynchronize(c->plan_ev_b));
+  size_t off = 0;
+  auto put = [&](const void* src, size_t bytes) -> unsigned char* {
+    unsigned char* dev = c->d_plan + off;
+    if (bytes) memcpy(c->h_plan + off, src, bytes);
+    off = (off + bytes + 255) & ~(size_t)255;
+    return dev;
+  };
+  c->d_lut = reinterpret_cast<float*>(put(lut.data(), lut.size() * sizeof(float)));
+  c->d_dst = reinterpret_cast<long long*>(put(dst.data(), (size_t)T * sizeof(long long)));
+  c->pl_off_b = off;
+  c->front_uploaded = upload_now && off > 0;
+  if (c->front_uploaded) {
+    CU(cudaMemcpyAsync(c->d_plan, c->h_plan, off, cudaMemcpyHostToDevice, c->stream));
+    CU(cudaEventRecord(c->plan_ev, c->stream));
+  }
+  return FST_MLA_OK;
+}
+
+// The second part: schedule and block tables.  on_copy_stream: upload it beside the kernels that
+// already run on the context's stream (which then waits for it); else one copy of the whole blob
+// (or of the second part, if the first went ahead) on the context's stream.
+int plan_schedule_part(FstMlaCtx* c, bool on_copy_stream) {
+  const int T = c->T;
+  std::vector<int32_t>&tok_table = c->pl_tok_table, &tables = c->pl_tables, &kvlen = c->pl_kvlen, &kvlo = c->pl_kvlo,
+      &tok_part = c->pl_tok_part;
 
   // split-KV schedule: the concatenated tiles of all query tokens are cut into n_ctas contiguous
   // runs of about equal COST; a run that crosses a token boundary yields one segment (and one
@@ -950,37 +1016,53 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
   if ((int)segs.size() > c->segs_cap || (int)segs.size() > c->max_parts)
     return fail(FST_MLA_ERR_CAPACITY, "split schedule overflow");
 
-  // pack everything into the pinned blob (once the previous plan's copy has left it) and
-  // upload it with one copy; the device arrays are slices of the device blob
-  cudaStream_t st = c->stream;
-  CU(cudaEventSynchronize(c->plan_ev));
-  size_t off = 0;
+  // the second part of the pinned blob, behind the first; the device arrays are slices of the
+  // device blob
+  size_t off = c->pl_off_b;
   auto put = [&](const void* src, size_t bytes) -> unsigned char* {
     unsigned char* dev = c->d_plan + off;
     if (bytes) memcpy(c->h_plan + off, src, bytes);
     off = (off + bytes + 255) & ~(size_t)255;
     return dev;
   };
-  c->d_lut = reinterpret_cast<float*>(put(lut.data(), lut.size() * sizeof(float)));
-  c->d_dst = reinterpret_cast<long long*>(put(dst.data(), (size_t)T * sizeof(long long)));
   c->d_tok_table = reinterpret_cast<int32_t*>(put(tok_table.data(), (size_t)T * sizeof(int32_t)));
   c->d_tok_part = reinterpret_cast<int32_t*>(put(tok_part.data(), (size_t)(T + 1) * sizeof(int32_t)));
   c->d_cta_seg = reinterpret_cast<int32_t*>(put(cta_seg.data(), cta_seg.size() * sizeof(int32_t)));
   c->d_segs = reinterpret_cast<AttnSeg*>(put(segs.data(), segs.size() * sizeof(AttnSeg)));
   c->d_tables = reinterpret_cast<int32_t*>(put(tables.data(), tables.size() * sizeof(int32_t)));
   if (off > c->plan_cap) return fail(FST_MLA_ERR_CAPACITY, "plan blob overflow");
-  CU(cudaMemcpyAsync(c->d_plan, c->h_plan, off, cudaMemcpyHostToDevice, st));
-  CU(cudaEventRecord(c->plan_ev, st));
-  c->T = (int)T;
+  const size_t from = c->front_uploaded ? c->pl_off_b : 0;
+  if (on_copy_stream) {
+    // beside the front kernels; fwd_ev (recorded when the call began) keeps the copy behind
+    // everything that was on the stream before this call and may still read the old tables
+    CU(cudaStreamWaitEvent(c->copy_stream, c->fwd_ev, 0));
+    CU(cudaMemcpyAsync(c->d_plan + from, c->h_plan + from, off - from, cudaMemcpyHostToDevice, c->copy_stream));
+    CU(cudaEventRecord(c->plan_ev_b, c->copy_stream));
+    CU(cudaStreamWaitEvent(c->stream, c->plan_ev_b, 0));
+  } else {
+    CU(cudaMemcpyAsync(c->d_plan + from, c->h_plan + from, off - from, cudaMemcpyHostToDevice, c->stream));
+    CU(cudaEventRecord(c->plan_ev, c->stream));
+  }
   c->n_segs = (int)segs.size();
   c->n_parts = (int)segs.size();
   c->n_ctas = n_ctas;
   c->kv_rows = kv_rows;
-  c->last_steps.assign(steps, steps + n_seqs);
-  c->last_causal = causal;
+  c->last_steps = c->pl_steps;
+  c->last_causal = c->pl_causal;
   ++c->plans_built;
   c->planned = true;
   return FST_MLA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, int32_t causal) {
+  bool reused = false;
+  int rc = plan_tokens_part(c, steps, n_seqs, causal, false, &reused);
+  if (rc || reused) return rc;
+  return plan_schedule_part(c, false);
 }
 
 int fst_cuda_mla_set_plan_reuse(FstMlaCtx* c, int32_t on) {
@@ -1066,8 +1148,13 @@ int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* 
   const size_t bytes_in = (size_t)T_in * c->d.hidden * sizeof(uint16_t);
   const bool in_direct = page_locked(h_in, nullptr), out_direct = page_locked(h_out, &out_mapped);
   c->compress_done = false;
+  // With a layer that can run, the plan is built in two parts: its per-token part goes to the
+  // device at once, the front kernels start, and the split-KV schedule is built and uploaded on a
+  // second stream while they run.
+  const bool split = early && !c->profiling && lid >= 0 && lid < c->cfg.n_layers && c->layers[lid].set;
   if (early) {
     CU(cudaSetDevice(c->cfg.device));
+    if (split) CU(cudaEventRecord(c->fwd_ev, c->stream));  // what was on the stream before this call
     if (!in_direct) memcpy(c->h_pinned, h_in, bytes_in);
     CU(cudaMemcpyAsync(c->d_h, in_direct ? (const void*)h_in : (const void*)c->h_pinned, bytes_in, cudaMemcpyHostToDevice, c->stream));
     // ... and so does the first GEMM of the layer (q / kv compression), which needs the rows and
@@ -1078,19 +1165,32 @@ int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* 
       c->compress_done = true;
     }
   }
-  int rc = fst_cuda_mla_plan(c, steps.data(), n_seqs, causal);
+  bool reused = false;
+  int rc = plan_tokens_part(c, steps.data(), n_seqs, causal, split, &reused);
+  const bool two_parts = !rc && !reused && split && c->T > 0;
+  if (!rc && !reused && !two_parts) rc = plan_schedule_part(c, false);
   if (rc) {
     c->compress_done = false;
     return rc;
   }
-  if ((rc = check_run(c, lid))) return rc;
+  if (!two_parts && (rc = check_run(c, lid))) return rc;
   if (c->T == 0) return FST_MLA_OK;
   const size_t bytes = (size_t)c->T * c->d.hidden * sizeof(uint16_t);
   // A page-locked output buffer that the device can address is written by the last GEMM itself
   // (512 KB of posted writes spread over the kernel) instead of by a copy behind it.
   const bool zero_copy = out_direct && out_mapped && c->out_zero_copy && !c->profiling;
   c->out_src = zero_copy ? (const bf16*)out_mapped : c->d_out;
-  if ((rc = fst_cuda_mla_run_device(c, lid, c->d_h, zero_copy ? out_mapped : (void*)c->d_out))) return rc;
+  void* out_dev = zero_copy ? out_mapped : (void*)c->d_out;
+  if (two_parts) {
+    if ((rc = run_front(c, lid, c->d_h))) return rc;
+    if ((rc = plan_schedule_part(c, true))) return rc;
+    if ((rc = run_attention(c, lid, c->d_qeff))) return rc;
+    if ((rc = run_merge_local(c, lid, 0, nullptr))) return rc;
+    if ((rc = run_back(c, lid, (bf16*)out_dev))) return rc;
+    CU(cudaGetLastError());
+  } else if ((rc = fst_cuda_mla_run_device(c, lid, c->d_h, out_dev))) {
+    return rc;
+  }
   if (!zero_copy)
     CU(cudaMemcpyAsync(out_direct ? (void*)h_out : (void*)c->h_pinned, c->d_out, bytes, cudaMemcpyDeviceToHost, c->stream));
   // while the device works: the RoPE rows of the positions that a decode step asks for next
