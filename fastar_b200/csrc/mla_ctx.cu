@@ -942,9 +942,9 @@ int plan_schedule_part(FstMlaCtx* c, bool on_copy_stream) {
   // partial) per token it touches.  The unit is a cache page where pages hold 64 tokens, else
   // ATTN_TILE rows.  Cost, in half units: 2 per tile plus SEG_COST2 per segment -- a segment
   // pays for its Q_eff block (one ring slot), refilling the pipeline and writing its partial
-  // (measured: about four 64-token tiles of the streaming kernel).
+  // (measured inside the pipelined layer: about three 64-token tiles of the streaming kernel).
   const int unit = c->cfg.page_tokens == 64 ? 64 : ATTN_TILE;
-  long long SEG_COST2 = unit == 64 ? 8 : 5;
+  long long SEG_COST2 = unit == 64 ? 6 : 5;
   if (const char* e = getenv("FST_MLA_SEG_COST")) {  // tuning aid: the segment's cost in half tiles
     const int v = atoi(e);
     if (v > 0 && v < 64) SEG_COST2 = v;
