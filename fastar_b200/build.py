@@ -54,8 +54,8 @@ def build(force: bool = False, verbose: bool = False) -> None:
             _run(cmd)
     if force or _newer(LIB_CUDA, objs):
         _run([nvcc, "-shared", "-cudart", "static", "-o", LIB_CUDA] + objs)
-    host_srcs = [os.path.join(HOST, f) for f in ("fst_engine.cpp", "fst_engine_capi.cpp")]
-    host_hdrs = [os.path.join(HOST, "fst_engine.h"), os.path.join(ROOT, "include", "fst_cuda_mla.h")]
+    host_srcs = [os.path.join(HOST, f) for f in ("fst_engine.cpp", "fst_engine_capi.cpp", "fst_file.cpp")]
+    host_hdrs = [os.path.join(HOST, "fst_engine.h"), os.path.join(HOST, "fst_file.h"), os.path.join(ROOT, "include", "fst_cuda_mla.h")]
     if all(os.path.exists(s) for s in host_srcs) and (force or _newer(LIB_ENGINE, host_srcs + host_hdrs + [LIB_CUDA])):
         _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-I", os.path.join(ROOT, "include"),
               "-o", LIB_ENGINE] + host_srcs + ["-L", PKG, "-l:libfst_cuda_mla.so", "-Wl,-rpath,$ORIGIN"])

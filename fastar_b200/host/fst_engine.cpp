@@ -1,5 +1,6 @@
 // FSTEngine (MLA subset) over the CUDA C ABI.  See fst_engine.h.
 #include "fst_engine.h"
+#include "fst_file.h"
 
 #include <cmath>
 #include <cstring>
@@ -56,6 +57,86 @@ FSTEngine::FSTEngine(const ModelConfig& cfg) : config_(cfg) {
 }
 
 FSTEngine::~FSTEngine() { fst_cuda_mla_destroy(ctx_); }
+
+namespace {
+
+// expected element counts of the MLA tensors of one layer, by preset
+struct MlaSizes {
+  size_t wq_a, wq_b, wkv, wo_a, wo_b, q_norm, kv_norm, sinks, attn_norm;
+};
+
+MlaSizes sizes_of(const ModelConfig& c) {
+  const size_t hd = (size_t)c.hidden_dim, H = MLA_N_HEADS, low = 8192;
+  MlaSizes z;
+  z.wq_a = (size_t)MLA_Q_LORA * hd;
+  z.q_norm = MLA_Q_LORA;
+  z.kv_norm = MLA_KV_LORA;
+  z.sinks = H;
+  z.attn_norm = hd;
+  z.wo_b = hd * low;
+  if (c.preset == FST_MLA_PRESET_FASTAR_V4) {
+    z.wq_b = H * (size_t)MLA_HEAD_DIM * MLA_Q_LORA;
+    z.wkv = (size_t)MLA_KV_LORA * hd;
+    z.wo_a = low * (H * (size_t)MLA_HEAD_DIM / 8);
+  } else {
+    z.wq_b = H * 192 * (size_t)MLA_Q_LORA;
+    z.wkv = (size_t)(MLA_KV_LORA + MLA_ROPE_DIM) * hd;
+    z.wo_a = 0;  // the BASELINE form has no wo_a (W_UV comes with wkv_b, which the file format does not carry)
+  }
+  return z;
+}
+
+void take_bf16(const std::string& path, const std::vector<fstfile::Entry>& dir, uint32_t tid, int layer, int sub,
+               size_t want, const char* name, std::vector<bf16_t>* dst) {
+  const fstfile::Entry* e = fstfile::find(dir, tid, layer, sub);
+  if (!e) return;
+  std::vector<uint16_t> v = fstfile::load_bf16(path, *e);
+  if (want && v.size() != want)
+    throw std::runtime_error(path + ": layer " + std::to_string(layer) + " " + name + " has " + std::to_string(v.size()) +
+                             " values, the configuration wants " + std::to_string(want));
+  dst->assign(v.begin(), v.end());
+}
+
+void take_sinks(const std::string& path, const std::vector<fstfile::Entry>& dir, int layer, size_t want,
+                std::vector<float>* dst) {
+  const fstfile::Entry* e = fstfile::find(dir, fstfile::TID_ATTN_SINK, layer, 0);
+  if (!e) return;
+  std::vector<float> v = fstfile::load_f32(path, *e);
+  if (v.size() < want)
+    throw std::runtime_error(path + ": layer " + std::to_string(layer) + " attn_sinks has " + std::to_string(v.size()) + " values");
+  dst->assign(v.begin(), v.begin() + want);  // the engine copies the first n_heads (src/fst_engine.cpp:1630-1636)
+}
+
+}  // namespace
+
+void FSTEngine::load_shared_weights(const std::string& fst_path) {
+  const std::vector<fstfile::Entry> dir = fstfile::read_directory(fst_path);
+  const MlaSizes z = sizes_of(config_);
+  for (int l = 0; l < config_.n_layers; ++l) {
+    LayerWeightsC& w = shared_.at(l);
+    take_bf16(fst_path, dir, fstfile::TID_Q_PROJ, l, 0, z.wq_a, "wq_a", &w.wq_a);
+    take_bf16(fst_path, dir, fstfile::TID_Q_PROJ, l, 1, z.wq_b, "wq_b", &w.wq_b);
+    take_bf16(fst_path, dir, fstfile::TID_K_PROJ, l, 0, z.wkv, "wkv", &w.wkv);
+    take_bf16(fst_path, dir, fstfile::TID_O_PROJ, l, 0, z.wo_a, "wo_a", &w.wo_a);
+    take_bf16(fst_path, dir, fstfile::TID_O_PROJ, l, 1, z.wo_b, "wo_b", &w.wo_b);
+    take_bf16(fst_path, dir, fstfile::TID_Q_NORM, l, 0, z.q_norm, "q_norm", &w.q_norm);
+    take_bf16(fst_path, dir, fstfile::TID_KV_NORM, l, 0, z.kv_norm, "kv_norm", &w.kv_norm);
+    take_bf16(fst_path, dir, fstfile::TID_INPUT_NORM, l, 0, z.attn_norm, "attn_norm", &w.attn_norm);
+    take_sinks(fst_path, dir, l, z.sinks, &w.attn_sinks);
+  }
+}
+
+void FSTEngine::load_norm_override(const std::string& norm_path) {
+  const std::vector<fstfile::Entry> dir = fstfile::read_directory(norm_path);
+  const MlaSizes z = sizes_of(config_);
+  for (int l = 0; l < config_.n_layers; ++l) {
+    LayerWeightsC& w = shared_.at(l);
+    take_bf16(norm_path, dir, fstfile::TID_INPUT_NORM, l, 0, z.attn_norm, "attn_norm", &w.attn_norm);
+    take_bf16(norm_path, dir, fstfile::TID_Q_NORM, l, 0, z.q_norm, "q_norm", &w.q_norm);
+    take_bf16(norm_path, dir, fstfile::TID_KV_NORM, l, 0, z.kv_norm, "kv_norm", &w.kv_norm);
+    take_sinks(norm_path, dir, l, z.sinks, &w.attn_sinks);
+  }
+}
 
 void FSTEngine::preload_all_layers() {
   for (int l = 0; l < config_.n_layers; ++l) {

@@ -63,6 +63,14 @@ class FSTEngine {
   FSTEngine(const FSTEngine&) = delete;
   FSTEngine& operator=(const FSTEngine&) = delete;
 
+  // The MLA tensors of every layer from a `.fst` file into shared_[*] (the MLA share of
+  // load_shared_weights, src/fst_engine.cpp:1503-1642: wq_a, wq_b, wkv, wo_a, wo_b, q_norm, kv_norm,
+  // attn_sinks, attn_norm; BF16 or Q8_0), and the norm weights and sinks of a `.norm` sidecar over
+  // them (load_norm_override, 1873-1900).  Host only: call preload_all_layers() afterwards.
+  // Tensors the file does not hold stay as they are; a tensor of the wrong size is an error.
+  void load_shared_weights(const std::string& fst_path);
+  void load_norm_override(const std::string& norm_path);
+
   // Upload shared_[*] to the device (preload_all_layers, src/fst_engine.cpp:1152-1197).
   void preload_all_layers();
 

@@ -5,6 +5,7 @@
 #include <string>
 
 #include "fst_engine.h"
+#include "fst_file.h"
 
 namespace {
 thread_local std::string g_msg;
@@ -64,6 +65,32 @@ int fst_engine_set_weight(FSTEngine* e, int lid, const char* name, const uint16_
 }
 int fst_engine_set_sinks(FSTEngine* e, int lid, const float* data, size_t n) {
   return guard([&] { e->shared_.at(lid).attn_sinks.assign(data, data + n); });
+}
+int fst_engine_load_shared_weights(FSTEngine* e, const char* path) { return guard([&] { e->load_shared_weights(path); }); }
+int fst_engine_load_norm_override(FSTEngine* e, const char* path) { return guard([&] { e->load_norm_override(path); }); }
+// Host-only probe of the `.fst` reader (no engine, no device): the tensor (tid, layer, sub) as bf16
+// bits (out_bits) and as fp32 (out_f32), either may be null; *n_out = its element count, 0 if the
+// file has no such tensor.  cap = capacity of the buffers in elements.
+int fst_file_read_tensor(const char* path, uint32_t tid, int layer, int sub, uint16_t* out_bits, float* out_f32,
+                         int64_t cap, int64_t* n_out, int* qtype_out) {
+  return guard([&] {
+    const std::vector<fstfile::Entry> dir = fstfile::read_directory(path);
+    const fstfile::Entry* en = fstfile::find(dir, tid, layer, sub);
+    *n_out = 0;
+    if (!en) return;
+    if (qtype_out) *qtype_out = en->qtype;
+    const int64_t n = (int64_t)en->n_elements();
+    if (n > cap) throw std::runtime_error("buffer too small for the tensor");
+    if (out_bits) {
+      const std::vector<uint16_t> v = fstfile::load_bf16(path, *en);
+      std::memcpy(out_bits, v.data(), v.size() * 2);
+    }
+    if (out_f32) {
+      const std::vector<float> v = fstfile::load_f32(path, *en);
+      std::memcpy(out_f32, v.data(), v.size() * 4);
+    }
+    *n_out = n;
+  });
 }
 int fst_engine_preload(FSTEngine* e) { return guard([&] { e->preload_all_layers(); }); }
 int fst_engine_process_mla(FSTEngine* e, int lid, uint16_t* h, int M) { return guard([&] { e->process_mla(lid, h, M); }); }

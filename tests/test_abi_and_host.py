@@ -100,7 +100,8 @@ def test_engine_library_loads_and_exports_its_entry_points():
     lib = ctypes.CDLL(os.path.join(os.path.dirname(mla.LIB_PATH), "libfst_engine.so"))
     for n in ("fst_engine_create", "fst_engine_destroy", "fst_engine_set_weight", "fst_engine_preload",
               "fst_engine_process_mla", "fst_engine_process_mla_batch", "fst_engine_reset_session",
-              "fst_engine_rollback", "fst_engine_set_window", "fst_engine_randmat_test", "fst_engine_last_error"):
+              "fst_engine_rollback", "fst_engine_set_window", "fst_engine_randmat_test", "fst_engine_last_error",
+              "fst_engine_load_shared_weights", "fst_engine_load_norm_override", "fst_file_read_tensor"):
         assert hasattr(lib, n), n
     import torch
     if not torch.cuda.is_available():

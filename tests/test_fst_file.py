@@ -128,3 +128,42 @@ def test_malformed_files_are_errors(tmp_path):
         f.truncate(20000)   # the directory survives, most payloads do not
     with pytest.raises(F.FstFormatError, match="out of bounds"):
         F.read_directory(str(cut))
+
+
+def _engine_lib():
+    import ctypes as C
+    L = C.CDLL(os.path.join(os.path.dirname(mla.LIB_PATH), "libfst_engine.so"))
+    L.fst_file_read_tensor.argtypes = [C.c_char_p, C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_uint16),
+                                       C.POINTER(C.c_float), C.c_int64, C.POINTER(C.c_int64), C.POINTER(C.c_int)]
+    L.fst_engine_last_error.restype = C.c_char_p
+    return L
+
+
+def test_cpp_reader_agrees_with_the_python_reader(tmp_path):
+    """The host mirror's reader (fastar_b200/host/fst_file.cpp, what FSTEngine::load_shared_weights and
+    load_norm_override use) returns the same bits as fst_file.py for every tensor of both fixtures."""
+    import ctypes as C
+    L = _engine_lib()
+    for path in (MAIN, SIDE):
+        for e in F.read_directory(path):
+            want = F.load_tensor(path, e)
+            n = C.c_int64(0)
+            qt = C.c_int(0)
+            bits = np.zeros(e.n_elements, np.uint16)
+            f32 = np.zeros(e.n_elements, np.float32)
+            rc = L.fst_file_read_tensor(path.encode(), e.tid, e.layer, e.sub, bits.ctypes.data_as(C.POINTER(C.c_uint16)),
+                                        f32.ctypes.data_as(C.POINTER(C.c_float)), e.n_elements, C.byref(n), C.byref(qt))
+            assert rc == 0, L.fst_engine_last_error()
+            assert (n.value, qt.value) == (e.n_elements, e.qtype)
+            if e.qtype == F.QTYPE_F32:
+                assert np.array_equal(f32, want.ravel()) and np.array_equal(bits, trunc_bits(want).ravel())
+            else:
+                assert np.array_equal(bits, want.ravel()), (e.tid, e.layer, e.sub)
+                assert np.array_equal(trunc_bits(f32), want.ravel())
+    # a tensor the file does not hold: zero elements, no error; a broken file: an error with its reason
+    n = C.c_int64(7)
+    assert L.fst_file_read_tensor(MAIN.encode(), 99, 0, 0, None, None, 0, C.byref(n), None) == 0 and n.value == 0
+    bad = tmp_path / "bad.fst"
+    bad.write_bytes(b"nope" + bytes(200))
+    assert L.fst_file_read_tensor(str(bad).encode(), 5, 0, 0, None, None, 0, C.byref(n), None) != 0
+    assert b"magic" in L.fst_engine_last_error()

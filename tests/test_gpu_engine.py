@@ -138,3 +138,67 @@ def test_randmat_probe_passes_the_reference_gate():
             assert cos[i] >= 0.99999 and abs(ratio[i] - 1) < 1e-3
     finally:
         L.fst_engine_destroy(e)
+
+
+def _write_fst(path, n_layers, tensors):
+    """A `.fst` file in the reference's layout (scripts/fst_converter.py:173-176, 685-716, 1464-1500):
+    128-byte header, 64-byte directory entries, page-aligned payloads.  tensors: (tid, layer, sub,
+    qtype, ndarray) with BF16 payloads given as uint16 bits and F32 as float32."""
+    import struct
+    page = lambda x: (x + 4095) & ~4095  # noqa: E731
+    dir_off = page(128)
+    off = page(dir_off + 64 * len(tensors))
+    entries = []
+    with open(path, "wb") as f:
+        for tid, layer, sub, qtype, a in tensors:
+            shape = (tuple(a.shape) + (1, 1, 1))[:3]
+            f.seek(off)
+            f.write(a.tobytes())
+            entries.append(struct.pack("<IHHHHIQQQQQQ", tid, layer, sub, qtype, a.ndim, 0, *shape, off, a.nbytes, 0))
+            off = page(off + a.nbytes)
+        f.seek(dir_off)
+        f.write(b"".join(entries))
+        f.seek(0)
+        f.write(struct.pack("<4sIIIIIIIIIIIQffQQQQQQQQ", b"FST\x00", 2, 4096, n_layers, 0, 8, 64, 1, 512, 0, 1, 0, 1000,
+                            1e-6, 10000.0, dir_off, len(tensors), off, 0, 0, 0, 0, 0))
+        f.truncate(off)
+
+
+def test_weights_loaded_from_a_fst_file(tmp_path):
+    """FSTEngine::load_shared_weights / load_norm_override (src/fst_engine.cpp:1503-1642, 1873-1900): an
+    engine that read its MLA tensors from a `.fst` file (norms and sinks from the sidecar) computes the
+    same bits as one that was handed the same arrays; a file whose tensors do not fit is an error."""
+    L = load()
+    L.fst_engine_load_shared_weights.argtypes = [C.c_void_p, C.c_char_p]
+    L.fst_engine_load_norm_override.argtypes = [C.c_void_p, C.c_char_p]
+    bits, _ = weights_for(mla.PRESET_FASTAR_V4)
+    tid = {"wq_a": (5, 0), "wq_b": (5, 1), "wkv_a": (6, 0), "wo_a": (8, 0), "wo_b": (8, 1), "q_norm": (14, 0),
+           "kv_norm": (15, 0)}
+    main = [(t, 0, s, 2, np.ascontiguousarray(bits[n], np.uint16)) for n, (t, s) in tid.items()]
+    # the main file carries norms that the sidecar must replace, and no sinks
+    main[-2] = (14, 0, 0, 2, np.full_like(bits["q_norm"], 0x3C00))
+    main[-1] = (15, 0, 0, 2, np.full_like(bits["kv_norm"], 0x3C00))
+    side = [(14, 0, 0, 2, np.ascontiguousarray(bits["q_norm"], np.uint16)),
+            (15, 0, 0, 2, np.ascontiguousarray(bits["kv_norm"], np.uint16)),
+            (22, 0, 0, 3, np.ascontiguousarray(bits["attn_sinks"], np.float32))]
+    p_main, p_side = str(tmp_path / "m.fst"), str(tmp_path / "m.fst.norm")
+    _write_fst(p_main, 1, main)
+    _write_fst(p_side, 1, side)
+    e_ref, _ = make_engine(L, mla.PRESET_FASTAR_V4)
+    e = L.fst_engine_create(mla.PRESET_FASTAR_V4, 1, 128, 1, 16, 0, mla.IMPL_AUTO, mla.IMPL_AUTO)
+    try:
+        assert L.fst_engine_load_shared_weights(e, p_main.encode()) == 0, L.fst_engine_last_error()
+        assert L.fst_engine_load_norm_override(e, p_side.encode()) == 0, L.fst_engine_last_error()
+        assert L.fst_engine_preload(e) == 0, L.fst_engine_last_error()
+        cfg = mla.make_config(mla.PRESET_FASTAR_V4)
+        h = synth.to_bf16_bits(synth.hidden_f32(cfg, 21, 5))
+        L.fst_engine_set_prefill(e, 1)
+        L.fst_engine_set_prefill(e_ref, 1)
+        assert np.array_equal(process(L, e, h), process(L, e_ref, h))
+        # a file of another model size is refused, with the tensor named
+        golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "tiny_mla.fst")
+        assert L.fst_engine_load_shared_weights(e, golden.encode()) != 0
+        assert b"configuration wants" in L.fst_engine_last_error()
+    finally:
+        L.fst_engine_destroy(e)
+        L.fst_engine_destroy(e_ref)
