@@ -1,7 +1,7 @@
 // Split-KV latent attention as a STREAM of 64-token tiles; Q_eff lives in tensor memory.
 //
-// Same job as attn_tc.cu (QK, softmax, SV of process_mla, reference src/fst_engine.cpp:
-// 3573-3683, over the paged bf16 cache), 64 heads, 512- or 576-wide rows.  Both products are in
+// QK, softmax and SV of process_mla (reference src/fst_engine.cpp:3573-3683) over the paged bf16
+// cache, 64 heads, 512- or 576-wide rows.  Both products are in
 // their natural orientation with the 64 heads as MMA M:
 //   S[64 heads, 64 tok]   = Q[64, d_qk] * K^T   A = Q_eff from TENSOR MEMORY; B = one 8 KB chunk
 //                                               [64 tok x 64 dims] of the page, K-major
@@ -31,8 +31,6 @@
 // same way at lane offset 16); 32-lane loads are used where the other 16 lanes are only read.
 #include "kernels.cuh"
 #include "tc_common.cuh"
-
-FST_TL_DEFINE(attn)
 
 namespace fst {
 
@@ -71,20 +69,6 @@ struct StreamParams {
   float scale_log2;
 };
 
-#ifdef FST_ATTN_TRACE
-#ifndef FST_TRACE_CTA
-#define FST_TRACE_CTA 0
-#endif
-// Tuning builds: [tile][event] SM-clock stamps of CTA FST_TRACE_CTA, and per-CTA {entry ns, start ns, exit ns, segments, entry clk, exit clk}.
-__device__ long long g_st_trace[64 * 16];
-__device__ long long g_st_cta[256 * 8];
-__device__ __forceinline__ long long st_gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t) : : "memory"); return t; }
-#define STRACE(tile, ev) do { if (blockIdx.x == FST_TRACE_CTA && (tile) < 64) g_st_trace[(tile) * 16 + (ev)] = clock64(); } while (0)
-#define ST_CTA(ev, val) do { if (threadIdx.x == 0 && blockIdx.x < 256) g_st_cta[blockIdx.x * 8 + (ev)] = (val); } while (0)
-#else
-#define STRACE(tile, ev) do { } while (0)
-#define ST_CTA(ev, val) do { } while (0)
-#endif
 
 struct StreamMisc {
   uint64_t full_t[4][3]; // chunks 3i .. 3i+2 of tile g have landed: barrier [g & 3][i]
@@ -207,7 +191,6 @@ __device__ __forceinline__ bool qk_chunks(StreamMisc* mi, int g, uint32_t d, uin
   for (int c = C0; c < C1; ++c) {
     if (c == C0 || c % 3 == 0) {
       if (!tc::mbar_wait(&mi->full_t[g & 3][c / 3], (g >> 2) & 1, abort_flag, d_status, ST_MMA_TIMEOUT)) return false;
-      if (c == 0) STRACE(g, 0);
       tc::tc_fence_after();
     }
     const uint64_t db = k_major | (uint64_t)(frame16 + c * (CHUNK / 16));
@@ -228,22 +211,8 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
   unsigned char* s_p = smem + off_p(NCH);
   StreamMisc* mi = reinterpret_cast<StreamMisc*>(smem + off_misc(NCH));
   volatile int* abort_flag = &mi->abort_flag;
-
-  FST_TL_BEGIN();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seg0 = p.cta_seg[blockIdx.x], seg1 = p.cta_seg[blockIdx.x + 1];
-#ifdef FST_ATTN_TRACE
-  if (threadIdx.x == 64 && blockIdx.x < 256) {
-    g_st_cta[blockIdx.x * 8 + 0] = st_gtime();
-    g_st_cta[blockIdx.x * 8 + 4] = clock64();
-  }
-  ST_CTA(3, (long long)(seg1 - seg0));
-  {
-    unsigned smid;
-    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
-    ST_CTA(7, (long long)smid);
-  }
-#endif
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 4; ++i) {
@@ -264,9 +233,6 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
   const uint32_t tmem = mi->tmem_slot;
   pdl_launch();
   pdl_wait();  // Q_eff and the appended cache rows come from earlier kernels
-#ifdef FST_ATTN_TRACE
-  ST_CTA(1, st_gtime());
-#endif
 
   if (warp == 0 || warp == 10 || warp == 11) {
     // ---------------- TMA producers: lane 0 of warps 0, 10, 11 ----------------
@@ -303,12 +269,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
         }
         const int32_t* table = p.tables + p.tok_table[cur.sg.tok];
         const int row0 = table[(cur.sg.kv_begin >> 6) + cur.t] * TILE;
-        if (r == 0) STRACE(cur.n, 11);
         ok = fill(cur.g, &tmKV, row0);
-        if (r == 0) STRACE(cur.n, 12);
-#ifdef FST_ATTN_TRACE
-        if (r == 0) ST_CTA(6, (long long)(cur.n + 1));
-#endif
         cur.next(p.segs);
       }
     }
@@ -342,7 +303,6 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
         else ok = qk_chunks<5, NCH>(mi, g, d, tmem, frame16, abort_flag, p.d_status);
         if (!ok) break;
         tc::umma_commit(&mi->s_full[n & 1]);
-        if (part == 1) STRACE(n, 1);
         cur.next(p.segs);
       }
     }
@@ -360,7 +320,6 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
         const int g = cur.g;
         ok = tc::mbar_wait(&mi->p_full, cur.n & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
         if (!ok) break;
-        STRACE(cur.n, 3);
         tc::tc_fence_after();
         const uint64_t da = k_major | (uint64_t)p16;
         const uint32_t acc0 = cur.t > 0 ? 1u : 0u;
@@ -373,7 +332,6 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
           for (int k = 0; k < TILE / 16; ++k) tc::umma_bf16(d, da + k * 2, db + k * 128, id256, k > 0 ? 1u : acc0);
         }
         tc::umma_commit(&mi->o_done[g & 3]);
-        STRACE(cur.n, 4);
         cur.next(p.segs);
       }
     }
@@ -394,7 +352,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
     // came through the ring like a tile, ahead of the segment's first tile, so it does not queue
     // behind the tiles in flight as loads by these threads would.  Every QK MMA of the previous
     // segment must have retired (the caller saw s_full of its last tile).
-    auto write_q = [&](int gq, int n_trace) -> bool {
+    auto write_q = [&](int gq) -> bool {
       for (int i = 0; i < 3; ++i)
         if (!tc::mbar_wait(&mi->full_t[gq & 3][i], (gq >> 2) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT)) return false;
       const unsigned char* frame = s_ring + (gq % 3) * (NCH * CHUNK);
@@ -430,7 +388,6 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
       tmem_wait_st();
       tc::tc_fence_before();
       tc::mbar_arrive(&mi->q_ready);
-      if (threadIdx.x == 64) STRACE(n_trace, 15);
       return true;
     };
     TileCursor cur;
@@ -441,14 +398,13 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
       const int n_tiles = cur.n_tiles;
       const unsigned span = (unsigned)(sg.kv_end - sg.kv_begin);
       // Q_eff of the first segment; later segments are written at the end of their predecessor
-      if (cur.sidx == 0) ok = write_q(cur.gq, cur.n);
+      if (cur.sidx == 0) ok = write_q(cur.gq);
       float m_used = -INFINITY, l = 0.0f;
       int g = cur.g;
       for (int t = 0; t < n_tiles && ok; ++t, cur.next(p.segs)) {
         g = cur.g;
         const int n = cur.n;
         ok = tc::mbar_wait(&mi->s_full[n & 1], (n >> 1) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
-        if (threadIdx.x == 64) STRACE(n, 8);
         tc::tc_fence_after();
         // this thread's first token, relative to the first visible row; visible: [0, span)
         const int rel0 = (sg.kv_begin & ~(TILE - 1)) - sg.kv_begin + t * TILE + half * 32 + sub * 16;
@@ -469,7 +425,6 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
         if (sub == 0) mi->pmax[n & 1][half][row] = mx;
         ok = quad_bar_and(quad, ok);
         if (!ok) break;
-        if (threadIdx.x == 64) STRACE(n, 9);
         // the reference maximum moves only when the tile maximum exceeds it by more than 2^8
         const float tm = fmaxf(mi->pmax[n & 1][0][row], mi->pmax[n & 1][1][row]);
         float alpha = 1.0f;
@@ -511,19 +466,17 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
           }
           tmem_wait_st();
         }
-        if (threadIdx.x == 64) STRACE(n, 10);
         tc::fence_proxy_async();
         tc::tc_fence_before();
         tc::mbar_arrive(&mi->p_full);
       }
       if (!ok) break;
       // Q_eff of the next segment goes in first, so that its QK MMAs run during the epilogue
-      if (!cur.done()) ok = write_q(cur.gq, cur.n);
+      if (!cur.done()) ok = write_q(cur.gq);
       if (!ok) break;
       // ---- epilogue of the segment: un-normalised partial (max, sum, O) ----
       ok = tc::mbar_wait(&mi->o_done[g & 3], (g >> 2) & 1, abort_flag, p.d_status, ST_EPI_TIMEOUT);
       tc::tc_fence_after();
-      if (threadIdx.x == 64) STRACE(cur.n - 1, 13);
       l += __shfl_xor_sync(0xffffffffu, l, 16);
       if (sub == 0) mi->lsum[half][row] = l;
       ok = quad_bar_and(quad, ok);
@@ -586,7 +539,6 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
           }
         }
       }
-      if (threadIdx.x == 64) STRACE(cur.n - 1, 14);
       tc::tc_fence_before();
       ok = quad_bar_and(quad, ok);  // lsum, the staging rows and O are reused by the next segment
     }
@@ -594,13 +546,6 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
 
   tc::tc_fence_before();
   __syncthreads();
-#ifdef FST_ATTN_TRACE
-  // (stamped by a softmax thread: what thread 0 writes here can land before the barrier)
-  if (threadIdx.x == 64 && blockIdx.x < 256) {
-    g_st_cta[blockIdx.x * 8 + 2] = st_gtime();
-    g_st_cta[blockIdx.x * 8 + 5] = clock64();
-  }
-#endif
   if (*abort_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies and MMAs in flight settle
   }
@@ -609,18 +554,10 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
     tc::tmem_dealloc(tmem, TMEM_COLS);
   }
   __syncthreads();
-  FST_TL_END(attn, 4);
 }
 
 }  // namespace
 
-#ifdef FST_ATTN_TRACE
-extern "C" int fst_debug_read_stream_trace(long long* tiles, long long* ctas) {
-  cudaError_t e = cudaMemcpyFromSymbol(tiles, g_st_trace, sizeof(long long) * 64 * 16);
-  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(ctas, g_st_cta, sizeof(long long) * 256 * 8);
-  return (int)e;
-}
-#endif
 
 bool attn_stream_supported(const AttnArgs& a) {
   return a.H == HEADS && a.d_v == D_V && a.page_tokens == TILE && a.row == a.d_qk &&
@@ -649,13 +586,6 @@ cudaError_t launch_attn_stream(const AttnArgs& a, cudaStream_t st) {
   p.pool = a.pool;
   p.d_qk = a.d_qk;
   p.scale_log2 = a.scale * 1.4426950408889634f;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(k_attn_stream<9>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_total(9));
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_stream<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_total(8));
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
   if (a.d_qk == 576) return launch_pdl(k_attn_stream<9>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(9), st, 1, tmKV, tmQ, p);
   return launch_pdl(k_attn_stream<8>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(8), st, 1, tmKV, tmQ, p);
 }

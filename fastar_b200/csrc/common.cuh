@@ -43,35 +43,6 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-#ifdef FST_ATTN_TRACE
-// Tuning builds: every CTA logs {kind, entry ns, exit ns} (global timer), one log per source file.
-__device__ __forceinline__ long long tl_now() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t) : : "memory"); return t; }
-#define FST_TL_DEFINE(tu)                                                                         \
-  __device__ long long g_tl_##tu[3 * 32768];                                                      \
-  __device__ int g_tl_n_##tu;                                                                     \
-  extern "C" int fst_debug_tl_##tu(long long* out, int* n) {                                     \
-    int z = 0;                                                                                    \
-    cudaMemcpyFromSymbol(n, g_tl_n_##tu, sizeof(int));                                            \
-    cudaMemcpyFromSymbol(out, g_tl_##tu, sizeof(long long) * 3 * 32768);                          \
-    return (int)cudaMemcpyToSymbol(g_tl_n_##tu, &z, sizeof(int));                                 \
-  }
-#define FST_TL_BEGIN() const long long tl_t0 = tl_now()
-#define FST_TL_END(tu, kind)                                                                      \
-  do {                                                                                            \
-    if (threadIdx.x == 0) {                                                                       \
-      const int tl_i = atomicAdd(&g_tl_n_##tu, 1);                                                \
-      if (tl_i < 32768) {                                                                         \
-        g_tl_##tu[3 * tl_i] = (kind);                                                             \
-        g_tl_##tu[3 * tl_i + 1] = tl_t0;                                                          \
-        g_tl_##tu[3 * tl_i + 2] = tl_now();                                                       \
-      }                                                                                           \
-    }                                                                                             \
-  } while (0)
-#else
-#define FST_TL_DEFINE(tu)
-#define FST_TL_BEGIN() do { } while (0)
-#define FST_TL_END(tu, kind) do { } while (0)
-#endif
 
 // One segment of the split-KV schedule: query token `tok` attends to cache rows
 // [kv_begin, kv_end) of its sequence and writes partial slot `part`.
@@ -83,6 +54,7 @@ struct AttnSeg {
 };
 
 // Status word values written by kernels that give up a bounded wait.
-enum : int { ST_OK = 0, ST_TMA_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_SOFTMAX_TIMEOUT = 3, ST_EPI_TIMEOUT = 4 };
+enum : int { ST_OK = 0, ST_TMA_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_SOFTMAX_TIMEOUT = 3, ST_EPI_TIMEOUT = 4,
+              ST_SELFTEST_TIMEOUT = 5 };
 
 }  // namespace fst

@@ -18,8 +18,6 @@
 #include "kernels.cuh"
 #include "tc_common.cuh"
 
-FST_TL_DEFINE(gemm)
-
 namespace fst {
 
 namespace {
@@ -69,7 +67,6 @@ __device__ __forceinline__ float4 ld_peer_f32x4(uint32_t local_addr, uint32_t ra
 template <int NT, bool W_KN>
 __global__ void __launch_bounds__(GEMM_THREADS, 2)
 k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA, GemmTcParams p) {
-  FST_TL_BEGIN();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   constexpr int A_BYTES = NT * BK * 2;
   constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
@@ -286,7 +283,6 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem, TMEM_COLS);
   }
-  FST_TL_END(gemm, 100000 + p.N);
 }
 
 int pick_nt(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
@@ -294,13 +290,6 @@ int pick_nt(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 12
 template <int NT, bool W_KN>
 cudaError_t launch_one(const CUtensorMap& tmW, const CUtensorMap& tmA, const GemmTcParams& p, dim3 grid, size_t smem,
                        cudaStream_t st) {
-  static bool attr_set = false;
-  cudaError_t e;
-  if (!attr_set) {
-    e = cudaFuncSetAttribute(k_gemm_tc<NT, W_KN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
   return launch_pdl(k_gemm_tc<NT, W_KN>, grid, dim3(GEMM_THREADS, 1, 1), smem, st, p.splits, tmW, tmA, p);
 }
 

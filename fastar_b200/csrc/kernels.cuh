@@ -1,19 +1,54 @@
 // Launchers of the MLA kernels.  All pointers are device pointers; bf16 unless noted.
 #pragma once
+#include <map>
 #include <mutex>
-#include <set>
+#include <utility>
 #include "common.cuh"
 
 namespace fst {
 
+// Function attributes (the dynamic shared-memory limit, the carve-out preference) belong to the
+// DEVICE that is current when they are set, so a process that drives several GPUs has to set
+// them once per (kernel, device).  This is the bookkeeping: first_use() answers true exactly once
+// for every (kernel, device ordinal, value) triple -- a larger value asked for later answers true
+// again.  Pure host logic (no CUDA call), so it can be checked without a GPU.
+class PerDeviceOnce {
+ public:
+  bool first_use(const void* kernel, int device, long long value = 0) {
+    std::lock_guard<std::mutex> lk(mu_);
+    auto key = std::make_pair(kernel, device);
+    auto it = seen_.find(key);
+    if (it != seen_.end() && it->second >= value) return false;
+    seen_[key] = value;
+    return true;
+  }
+
+ private:
+  std::mutex mu_;
+  std::map<std::pair<const void*, int>, long long> seen_;
+};
+PerDeviceOnce& kernel_attr_registry();
+
+inline int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return dev;
+}
+
+// Raises the dynamic shared-memory limit of `kernel` to `bytes` on the current device (once per
+// device; again when a later launch needs more).
+inline cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes) {
+  if (bytes <= 48 * 1024) return cudaSuccess;
+  if (!kernel_attr_registry().first_use(kernel, current_device(), (long long)bytes)) return cudaSuccess;
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
 // Every kernel of the library asks for the largest shared-memory carve-out, whatever it uses:
 // an SM that has to change its L1 / shared split between two kernels drains first, and the
-// attention kernel (227 KB) would pay that after every GEMM.  Done once per kernel.
+// attention kernel (227 KB) would pay that after every GEMM.  Once per kernel and device.
 inline void prefer_max_shared(const void* kernel) {
-  static std::mutex mu;
-  static std::set<const void*> done;
-  std::lock_guard<std::mutex> lk(mu);
-  if (done.insert(kernel).second)
+  // (the tag keeps this entry apart from the kernel's dynamic shared-memory entry)
+  if (kernel_attr_registry().first_use(static_cast<const char*>(kernel) + 1, current_device()))
     cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
@@ -22,6 +57,8 @@ template <class... KArgs, class... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                               int cluster_y, Args&&... args) {
   prefer_max_shared(reinterpret_cast<const void*>(kernel));
+  cudaError_t e_attr = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
+  if (e_attr != cudaSuccess) return e_attr;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -144,6 +181,14 @@ struct MergeGatheredArgs {
   int n_parts, T, H, d_v, rope, inv_rope;
 };
 void launch_merge_gathered(const MergeGatheredArgs& a, cudaStream_t st);
+
+// Robustness self-test: one block waits on an mbarrier nothing ever arrives at, with a limit of
+// `polls` polls, gives up and records ST_SELFTEST_TIMEOUT in *d_status the way the tcgen05 kernels
+// record their own time-outs.  No TMA, no MMA, no tensor memory.
+void launch_wait_selftest(int* d_status, uint32_t polls, cudaStream_t st);
+
+// The calling thread's last-error string (what fst_cuda_mla_last_error returns).
+void set_last_error(const char* msg);
 
 void launch_zero_rows(bf16* pool, const long long* row_off, int n_rows, int row, cudaStream_t st);
 

@@ -2,8 +2,7 @@
 // log-sum-exp merge) and shape-agnostic GEMM / attention kernels used where the tcgen05
 // kernels do not apply (odd shapes, the [K,N] absorb operand) and for bisecting.
 #include "kernels.cuh"
-
-FST_TL_DEFINE(simt)
+#include "tc_common.cuh"
 
 namespace fst {
 
@@ -154,7 +153,6 @@ void launch_rmsnorm_rows(const bf16* x, const bf16* w, bf16* y, int T, int dim, 
 // table, the destination) is issued before anything is reduced, and the two sums of squares
 // share one exchange: the kernel is one memory round trip and one block reduction long.
 __global__ void __launch_bounds__(256) k_norm_append(NormAppendArgs a) {
-  FST_TL_BEGIN();
   pdl_launch();
   pdl_wait();
   extern __shared__ float s_row[];  // [row]
@@ -226,7 +224,6 @@ __global__ void __launch_bounds__(256) k_norm_append(NormAppendArgs a) {
     a.kv_new[(long long)t * a.row + j] = v;
     if (dst >= 0) a.pool[dst + j] = v;
   }
-  FST_TL_END(simt, 1);
 }
 
 void launch_norm_append(const NormAppendArgs& a, cudaStream_t st) {
@@ -239,7 +236,6 @@ void launch_norm_append(const NormAppendArgs& a, cudaStream_t st) {
 // (rope_qpe_all_heads, reference src/fst_engine.cpp:2025-2058; the absorb GEMM fills the rest).
 // V4: per-head weightless RMSNorm (3487-3495), then the tail rotation (3503).
 __global__ void __launch_bounds__(128) k_q_prep(QPrepArgs a) {
-  FST_TL_BEGIN();
   pdl_launch();
   pdl_wait();
   __shared__ float scratch[32];
@@ -274,13 +270,11 @@ __global__ void __launch_bounds__(128) k_q_prep(QPrepArgs a) {
       out[a.d_qk - a.rope + 2 * p + 1] = f2bf(x0 * s + x1 * c);
     }
   }
-  FST_TL_END(simt, 2);
 }
 
 // BASELINE only: one block per token rotates the rope pairs of all its heads (a pair per thread
 // and step) -- a handful of fat blocks instead of T * H blocks of 32 busy threads.
 __global__ void __launch_bounds__(256) k_q_rope_token(QPrepArgs a) {
-  FST_TL_BEGIN();
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x, half = a.rope / 2;
@@ -294,7 +288,6 @@ __global__ void __launch_bounds__(256) k_q_rope_token(QPrepArgs a) {
     const float x0 = __low2float(x), x1 = __high2float(x);
     *reinterpret_cast<__nv_bfloat162*>(out) = __floats2bfloat162_rn(x0 * c - x1 * s, x0 * s + x1 * c);
   }
-  FST_TL_END(simt, 2);
 }
 
 void launch_q_prep(const QPrepArgs& a, cudaStream_t st) {
@@ -429,11 +422,6 @@ __global__ void __launch_bounds__(256, 1) k_attn_simt(AttnArgs a) {
 void launch_attn_simt(const AttnArgs& a, cudaStream_t st) {
   if (a.n_segs <= 0) return;
   const size_t smem = (size_t)a.H * a.d_qk * 2 + (size_t)SIMT_TILE * (a.row * 2 + 16);
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaFuncSetAttribute(k_attn_simt, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    configured = smem;
-  }
   launch_pdl(k_attn_simt, dim3(a.n_segs), dim3(256), smem, st, 1, a);
 }
 
@@ -552,23 +540,10 @@ __device__ __forceinline__ void merge_row(int n_parts, GetPart get, const float*
   den_out = den;
 }
 
-#ifdef FST_ATTN_TRACE
-__device__ long long g_merge_stamp[4];
-extern "C" int fst_debug_read_merge_stamp(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_merge_stamp, sizeof(long long) * 4);
-}
-#endif
 
 __global__ void __launch_bounds__(MERGE_THREADS) k_merge(MergeArgs a) {
-  FST_TL_BEGIN();
-#ifdef FST_ATTN_TRACE
-  if (blockIdx.x == 0 && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g_merge_stamp[0]) : : "memory");
-#endif
   pdl_launch();
   pdl_wait();
-#ifdef FST_ATTN_TRACE
-  if (blockIdx.x == 0 && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g_merge_stamp[1]) : : "memory");
-#endif
   __shared__ __align__(16) float s_acc[8 * 512];
   __shared__ float s_red[32];
   const int r = blockIdx.x, t = r / a.H, h = r % a.H;
@@ -591,14 +566,12 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge(MergeArgs a) {
   const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
   for (int j = threadIdx.x; j < a.d_v; j += blockDim.x) s_acc[j] = rbf(s_acc[j] * inv);
   finish_row(s_acc, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope, a.inv_rope);
-  FST_TL_END(simt, 3);
 }
 
 // Rows with few parts: one WARP per query row (token, head), eight rows per block, nothing
 // shared.  A lane owns columns lane*4 + 128*j and walks the parts in order, so the arithmetic per
 // column is that of the 128-thread mode of merge_row.
 __global__ void __launch_bounds__(256) k_merge_rows(MergeArgs a) {
-  FST_TL_BEGIN();
   pdl_launch();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -676,7 +649,6 @@ __global__ void __launch_bounds__(256) k_merge_rows(MergeArgs a) {
       }
     }
   }
-  FST_TL_END(simt, 3);
 }
 
 void launch_merge(const MergeArgs& a, cudaStream_t st) {
@@ -709,6 +681,24 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge_gathered(MergeGatheredA
 void launch_merge_gathered(const MergeGatheredArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
   launch_pdl(k_merge_gathered, dim3(a.T * a.H), dim3(a.n_parts <= 4 ? 128 : MERGE_THREADS), 0, st, 1, a);
+}
+
+// ---- bounded-wait self-test ----------------------------------------------------------------------
+__global__ void k_wait_selftest(int* d_status, uint32_t polls) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&bar, 1);
+    abort_flag = 0;
+    tc::fence_barrier_init();
+  }
+  __syncthreads();
+  // phase 0 never completes: nobody arrives.  Every thread's wait runs out (or sees the flag).
+  tc::mbar_wait(&bar, 0, &abort_flag, d_status, ST_SELFTEST_TIMEOUT, polls);
+}
+
+void launch_wait_selftest(int* d_status, uint32_t polls, cudaStream_t st) {
+  k_wait_selftest<<<1, 32, 0, st>>>(d_status, polls);
 }
 
 // Zero whole cache rows (speculative rollback, reference src/fst_engine.cpp:6132-6147).

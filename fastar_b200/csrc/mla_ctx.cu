@@ -18,6 +18,18 @@ namespace {
 
 thread_local std::string g_err;
 
+}  // namespace
+
+namespace fst {
+PerDeviceOnce& kernel_attr_registry() {
+  static PerDeviceOnce r;
+  return r;
+}
+void set_last_error(const char* msg) { g_err = msg ? msg : ""; }
+}  // namespace fst
+
+namespace {
+
 int fail(int code, const char* fmt, ...) {
   char buf[512];
   va_list ap;
@@ -85,8 +97,11 @@ struct FstMlaCtx {
   bool out_zero_copy = true;
   int* h_status = nullptr;  // page-locked copy of the status word, fetched on the stream before a sync
 
+  // RoPE kind of every layer: 0 plain (theta = cfg.rope_theta), 1 YaRN (reference
+  // build_rope_lut picks per layer, src/fst_engine.cpp:1979-1982)
+  std::vector<int8_t> layer_yarn;
   // plan (device)
-  float* d_lut = nullptr;
+  float* d_lut_k[2] = {nullptr, nullptr};  // [T, rope] (cos, sin) per RoPE kind that some layer uses
   long long* d_dst = nullptr;
   int32_t *d_tables = nullptr, *d_tok_table = nullptr, *d_cta_seg = nullptr, *d_tok_part = nullptr;
   AttnSeg* d_segs = nullptr;
@@ -98,10 +113,10 @@ struct FstMlaCtx {
   cudaEvent_t plan_ev = nullptr;
   // RoPE table rows by position, direct-mapped: one step of a model asks for the same positions
   // in every layer, and a decode step for the positions right after the previous step's
-  std::vector<float> lut_rows;
-  std::vector<int32_t> lut_tag;
+  std::vector<float> lut_rows[2];  // per RoPE kind
+  std::vector<int32_t> lut_tag[2];
   // plan (host): the per-token arrays live here between the two phases of a plan
-  std::vector<float> pl_lut;
+  std::vector<float> pl_lut[2];
   std::vector<long long> pl_dst;
   std::vector<int32_t> pl_tok_table, pl_tables, pl_kvlen, pl_kvlo, pl_tok_part;
   std::vector<FstMlaSeqStep> pl_steps;
@@ -120,6 +135,7 @@ struct FstMlaCtx {
   long long kv_rows = 0;
 
   int64_t launches = 0;
+  int64_t launches_tensor = 0, launches_simt = 0;  // GEMM / attention launches by kernel family
   bool profiling = false;
   bool compress_done = false;  // fst_cuda_mla_forward has launched the compress GEMM of this call already
   std::vector<EventSet> ev_pool;
@@ -192,20 +208,27 @@ constexpr int LUT_CACHE_ROWS = 4096;  // power of two
 
 // the RoPE row of one position, computed on its first use and kept until another position maps to
 // the same slot
-const float* lut_row_cached(FstMlaCtx* c, int pos) {
+const float* lut_row_cached(FstMlaCtx* c, int kind, int pos) {
   const int rope = c->d.rope;
-  if (c->lut_tag.empty()) {
-    c->lut_tag.assign(LUT_CACHE_ROWS, -1);
-    c->lut_rows.resize((size_t)LUT_CACHE_ROWS * rope);
+  if (c->lut_tag[kind].empty()) {
+    c->lut_tag[kind].assign(LUT_CACHE_ROWS, -1);
+    c->lut_rows[kind].resize((size_t)LUT_CACHE_ROWS * rope);
   }
   const int slot = pos & (LUT_CACHE_ROWS - 1);
-  float* row = &c->lut_rows[(size_t)slot * rope];
-  if (c->lut_tag[slot] != pos) {
-    rope_lut_row(row, pos, rope, c->cfg.rope_theta, c->cfg.rope_yarn != 0);
-    c->lut_tag[slot] = pos;
+  float* row = &c->lut_rows[kind][(size_t)slot * rope];
+  if (c->lut_tag[kind][slot] != pos) {
+    rope_lut_row(row, pos, rope, c->cfg.rope_theta, kind != 0);
+    c->lut_tag[kind][slot] = pos;
   }
   return row;
 }
+
+// which RoPE kinds the layers of this context use
+void rope_kinds(const FstMlaCtx* c, bool need[2]) {
+  need[0] = need[1] = false;
+  for (int8_t k : c->layer_yarn) need[k ? 1 : 0] = true;
+}
+const float* lut_of(const FstMlaCtx* c, int lid) { return c->d_lut_k[c->layer_yarn[lid] ? 1 : 0]; }
 
 bool seq_ok(const FstMlaCtx* c, int32_t s) { return s >= 0 && s < c->cfg.max_seqs && c->live[s]; }
 
@@ -291,8 +314,10 @@ int run_gemm(FstMlaCtx* c, const GemmArgs& g) {
   if (use_tc_gemm(c, g)) {
     cudaError_t e = launch_gemm_tc(g, c->d_status, c->stream);
     if (e != cudaSuccess) return fail(FST_MLA_ERR_CUDA, "tcgen05 GEMM launch: %s", cudaGetErrorString(e));
+    c->launches_tensor += 1;
   } else {
     launch_gemm_simt(g, c->stream);
+    c->launches_simt += 1;
   }
   c->launches += 1;
   return FST_MLA_OK;
@@ -342,8 +367,10 @@ int run_attention(FstMlaCtx* c, int lid, const bf16* q_eff) {
   if (c->cfg.attn_impl != FST_MLA_IMPL_SIMT && tc_ok) {
     cudaError_t e = launch_attn_stream(a, c->stream);
     if (e != cudaSuccess) return fail(FST_MLA_ERR_CUDA, "tcgen05 attention launch: %s", cudaGetErrorString(e));
+    c->launches_tensor += 1;
   } else {
     launch_attn_simt(a, c->stream);
+    c->launches_simt += 1;
   }
   c->launches += 1;
   return FST_MLA_OK;
@@ -366,7 +393,7 @@ int run_front(FstMlaCtx* c, int lid, const bf16* h_in) {
   c->compress_done = false;
   prof_mark(c, FST_MLA_K_NORM_APPEND);
   NormAppendArgs na;
-  na.cmp = c->d_cmp; na.q_norm = w.q_norm; na.kv_norm = w.kv_norm; na.lut = c->d_lut;
+  na.cmp = c->d_cmp; na.q_norm = w.q_norm; na.kv_norm = w.kv_norm; na.lut = lut_of(c, lid);
   na.dst_row = c->d_dst; na.qc = c->d_qc; na.kv_new = c->d_kvnew; na.pool = c->pools[lid];
   na.T = T; na.q_lora = d.q_lora; na.kv_lora = d.kv_lora; na.row = d.row; na.rope = d.rope;
   na.eps = c->cfg.rms_eps;
@@ -376,7 +403,7 @@ int run_front(FstMlaCtx* c, int lid, const bf16* h_in) {
   if ((rc = run_gemm(c, plain_gemm(c->d_qc, w.wq_b, c->d_qfull, T, d.H * d.q_head, d.q_lora)))) return rc;
   prof_mark(c, FST_MLA_K_Q_ABSORB);
   QPrepArgs qp;
-  qp.q_full = c->d_qfull; qp.lut = c->d_lut; qp.q_eff = c->d_qeff;
+  qp.q_full = c->d_qfull; qp.lut = lut_of(c, lid); qp.q_eff = c->d_qeff;
   qp.T = T; qp.H = d.H; qp.q_head = d.q_head; qp.nope = d.nope; qp.rope = d.rope; qp.d_qk = d.d_qk;
   qp.v4 = d.v4; qp.eps = c->cfg.rms_eps;
   if (d.v4) {
@@ -394,7 +421,7 @@ int run_front(FstMlaCtx* c, int lid, const bf16* h_in) {
     if (use_tc_gemm(c, g) && even) {
       // the q_pe RoPE rides in the same kernel: it reads the same input and fills the other
       // columns of q_eff, and a kernel boundary costs more than the rotation itself
-      g.rope_src = c->d_qfull; g.rope_lut = c->d_lut; g.rope_dst = c->d_qeff;
+      g.rope_src = c->d_qfull; g.rope_lut = lut_of(c, lid); g.rope_dst = c->d_qeff;
       g.rope_T = T; g.rope_H = d.H; g.rope_q_head = d.q_head; g.rope_nope = d.nope; g.rope_dims = d.rope;
       g.rope_d_qk = d.d_qk;
     } else {
@@ -438,7 +465,7 @@ int run_merge_local(FstMlaCtx* c, int lid, int mode, float* rank_partial) {
   MergeArgs m;
   m.part_m = c->d_part_m; m.part_l = c->d_part_l; m.part_o = c->d_part_o; m.tok_part = c->d_tok_part;
   m.sinks = (d.v4 && mode == 0) ? c->layers[lid].sinks : nullptr;
-  m.lut = c->d_lut; m.o_lat = c->d_olat; m.rank_partial = rank_partial;
+  m.lut = lut_of(c, lid); m.o_lat = c->d_olat; m.rank_partial = rank_partial;
   m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope; m.inv_rope = d.v4 ? 1 : 0; m.mode = mode;
   m.threads = c->n_parts <= 6 * c->T ? 128 : 256;
   launch_merge(m, c->stream);
@@ -503,6 +530,7 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
   x->d = d;
   x->n_sm = prop.multiProcessorCount;
   x->layers.resize(c.n_layers);
+  x->layer_yarn.assign(c.n_layers, c.rope_yarn ? 1 : 0);
   x->pools.assign(c.n_layers, nullptr);
   for (int i = c.n_pages - 1; i >= 0; --i) x->free_pages.push_back(i);
   for (int i = c.max_seqs - 1; i >= 0; --i) x->free_seqs.push_back(i);
@@ -535,7 +563,7 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
   if (!rc) rc = dev_alloc(&x->d_part_o, (size_t)x->max_parts * d.H * d.d_v);
   x->segs_cap = x->max_parts;
   x->tables_cap = c.n_pages + c.max_seqs;
-  x->plan_cap = T * d.rope * sizeof(float) + T * sizeof(long long) + (2 * T + 1) * sizeof(int32_t) +
+  x->plan_cap = 2 * T * d.rope * sizeof(float) + T * sizeof(long long) + (2 * T + 1) * sizeof(int32_t) +
                 ((size_t)x->n_sm + 1) * sizeof(int32_t) + (size_t)x->segs_cap * sizeof(AttnSeg) +
                 (size_t)x->tables_cap * sizeof(int32_t) + 8 * 256;
   if (!rc) rc = dev_alloc(&x->d_plan, x->plan_cap);
@@ -552,7 +580,6 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
   if (!rc && cudaHostAlloc((void**)&x->h_status, sizeof(int), cudaHostAllocDefault) != cudaSuccess)
     rc = fail(FST_MLA_ERR_CUDA, "cudaHostAlloc failed");
   if (!rc) *x->h_status = 0;
-  if (const char* e = getenv("FST_MLA_ZERO_COPY_OUT")) x->out_zero_copy = atoi(e) != 0;  // tuning aid
   if (!rc && cudaHostAlloc((void**)&x->h_pinned, T * d.hidden * sizeof(uint16_t), cudaHostAllocDefault) != cudaSuccess)
     rc = fail(FST_MLA_ERR_CUDA, "cudaHostAlloc failed");
   if (rc) {
@@ -663,6 +690,28 @@ int fst_cuda_mla_set_layer_weights(FstMlaCtx* c, int lid, const FstMlaWeights* w
       CU(cudaMemset(L.sinks, 0, d.H * sizeof(float)));  // empty sinks: logit 0 (reference 3623)
   }
   L.set = true;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_set_rope_theta(FstMlaCtx* c, float theta) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (!(theta > 0.0f) || !std::isfinite(theta)) return fail(FST_MLA_ERR_ARG, "rope_theta must be positive");
+  if (theta != c->cfg.rope_theta) {
+    c->cfg.rope_theta = theta;
+    for (auto& t : c->lut_tag) t.clear();  // the cached table rows were built with the old base
+    c->planned = false;
+  }
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_set_layer_rope(FstMlaCtx* c, int lid, int32_t yarn) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (lid < 0 || lid >= c->cfg.n_layers) return fail(FST_MLA_ERR_ARG, "layer %d out of range", lid);
+  if (yarn != 0 && yarn != 1) return fail(FST_MLA_ERR_ARG, "RoPE kind %d (0: plain, 1: YaRN)", yarn);
+  if (c->layer_yarn[lid] != yarn) {
+    c->layer_yarn[lid] = (int8_t)yarn;
+    c->planned = false;  // the next plan uploads the tables of every kind in use
+  }
   return FST_MLA_OK;
 }
 
@@ -875,10 +924,11 @@ int plan_tokens_part(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, i
     }
   }
 
-  std::vector<float>& lut = c->pl_lut;
+  bool need[2];
+  rope_kinds(c, need);
   std::vector<long long>& dst = c->pl_dst;
   std::vector<int32_t>&tok_table = c->pl_tok_table, &tables = c->pl_tables, &kvlen = c->pl_kvlen, &kvlo = c->pl_kvlo;
-  lut.resize((size_t)T * d.rope);
+  for (int k = 0; k < 2; ++k) c->pl_lut[k].resize(need[k] ? (size_t)T * d.rope : 0);
   dst.resize(T);
   tok_table.resize(T);
   kvlen.resize(T);
@@ -892,7 +942,8 @@ int plan_tokens_part(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, i
     tables.insert(tables.end(), c->tables[s.seq].begin(), c->tables[s.seq].end());
     const int rp0 = s.rope_pos0 >= 0 ? s.rope_pos0 : s.pos0;
     for (int i = 0; i < s.q_len; ++i, ++t) {
-      memcpy(&lut[(size_t)t * d.rope], lut_row_cached(c, rp0 + i), (size_t)d.rope * sizeof(float));
+      for (int k = 0; k < 2; ++k)
+        if (need[k]) memcpy(&c->pl_lut[k][(size_t)t * d.rope], lut_row_cached(c, k, rp0 + i), (size_t)d.rope * sizeof(float));
       dst[t] = s.append ? row_offset(c, s.seq, s.pos0 + i) : -1;
       tok_table[t] = toff;
       int len = s.append ? s.pos0 + s.q_len : s.pos0;
@@ -918,7 +969,8 @@ int plan_tokens_part(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, i
     off = (off + bytes + 255) & ~(size_t)255;
     return dev;
   };
-  c->d_lut = reinterpret_cast<float*>(put(lut.data(), lut.size() * sizeof(float)));
+  for (int k = 0; k < 2; ++k)
+    c->d_lut_k[k] = need[k] ? reinterpret_cast<float*>(put(c->pl_lut[k].data(), c->pl_lut[k].size() * sizeof(float))) : nullptr;
   c->d_dst = reinterpret_cast<long long*>(put(dst.data(), (size_t)T * sizeof(long long)));
   c->pl_off_b = off;
   c->front_uploaded = upload_now && off > 0;
@@ -944,11 +996,7 @@ int plan_schedule_part(FstMlaCtx* c, bool on_copy_stream) {
   // pays for its Q_eff block (one ring slot), refilling the pipeline and writing its partial
   // (measured inside the pipelined layer: about three 64-token tiles of the streaming kernel).
   const int unit = c->cfg.page_tokens == 64 ? 64 : ATTN_TILE;
-  long long SEG_COST2 = unit == 64 ? 6 : 5;
-  if (const char* e = getenv("FST_MLA_SEG_COST")) {  // tuning aid: the segment's cost in half tiles
-    const int v = atoi(e);
-    if (v > 0 && v < 64) SEG_COST2 = v;
-  }
+  const long long SEG_COST2 = unit == 64 ? 6 : 5;
   long long total_tiles = 0, kv_rows = 0, n_nonempty = 0;
   // tiles are counted from the tile that holds the first visible row
   auto tile0_of = [&](int i) { return kvlo[i] / unit; };
@@ -958,11 +1006,7 @@ int plan_schedule_part(FstMlaCtx* c, bool on_copy_stream) {
     kv_rows += kvlen[i] - kvlo[i];
     n_nonempty += kvlen[i] > 0;
   }
-  int max_ctas = c->n_sm;
-  if (const char* e = getenv("FST_MLA_MAX_CTAS")) {  // tuning aid: fewer attention CTAs than SMs
-    const int v = atoi(e);
-    if (v > 0 && v < max_ctas) max_ctas = v;
-  }
+  const int max_ctas = c->n_sm;
   const int n_ctas = (int)std::min<long long>(max_ctas, std::max<long long>(total_tiles, 1));
   std::vector<AttnSeg> segs;
   std::vector<int32_t> cta_seg(n_ctas + 1, 0);
@@ -1196,7 +1240,9 @@ int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* 
   // while the device works: the RoPE rows of the positions that a decode step asks for next
   for (int b = 0; b < n_seqs; ++b)
     if (q_lens[b] > 0 && q_lens[b] <= 4)
-      for (int i = 0; i < q_lens[b]; ++i) lut_row_cached(c, pos0[b] + q_lens[b] + i);
+      for (int i = 0; i < q_lens[b]; ++i)
+        for (int k = 0; k < 2; ++k)
+          if (!c->lut_tag[k].empty()) lut_row_cached(c, k, pos0[b] + q_lens[b] + i);
   if ((rc = fst_cuda_mla_sync(c))) return rc;
   if (!out_direct) memcpy(h_out, c->h_pinned, bytes);
   return FST_MLA_OK;
@@ -1249,7 +1295,7 @@ int fst_cuda_mla_run_merge_device(FstMlaCtx* c, int lid, const void* d_partials,
   if ((rc = prof_begin(c))) return rc;
   prof_mark(c, FST_MLA_K_MERGE);
   MergeGatheredArgs m;
-  m.parts = (const float*)d_partials; m.sinks = d.v4 ? c->layers[lid].sinks : nullptr; m.lut = c->d_lut;
+  m.parts = (const float*)d_partials; m.sinks = d.v4 ? c->layers[lid].sinks : nullptr; m.lut = lut_of(c, lid);
   m.o_lat = c->d_olat; m.n_parts = n_parts; m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope;
   m.inv_rope = d.v4 ? 1 : 0;
   launch_merge_gathered(m, c->stream);
@@ -1315,6 +1361,36 @@ int fst_cuda_mla_gemm(FstMlaCtx* c, uint16_t* C, const uint16_t* A, const uint16
 int fst_cuda_mla_launch_count(FstMlaCtx* c, int64_t* n_out) {
   if (!c || !n_out) return fail(FST_MLA_ERR_ARG, "null argument");
   *n_out = c->launches;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_family_counts(FstMlaCtx* c, int64_t* tensor_out, int64_t* simt_out) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (tensor_out) *tensor_out = c->launches_tensor;
+  if (simt_out) *simt_out = c->launches_simt;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_selftest_wait_expiry(FstMlaCtx* c, int32_t polls) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (polls < 1 || polls > (1 << 16)) return fail(FST_MLA_ERR_ARG, "poll limit %d outside [1, 65536]", polls);
+  CU(cudaSetDevice(c->cfg.device));
+  launch_wait_selftest(c->d_status, (uint32_t)polls, c->stream);
+  c->launches += 1;
+  CU(cudaGetLastError());
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_debug_attr_first_use(uint64_t kernel_key, int32_t device, int64_t value) {
+  return kernel_attr_registry().first_use(reinterpret_cast<const void*>(static_cast<uintptr_t>(kernel_key)), device,
+                                          value) ? 1 : 0;
+}
+
+int fst_cuda_mla_debug_set_status(FstMlaCtx* c, int32_t code) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  CU(cudaSetDevice(c->cfg.device));
+  CU(cudaMemcpyAsync(c->d_status, &code, sizeof(int), cudaMemcpyHostToDevice, c->stream));
+  CU(cudaStreamSynchronize(c->stream));
   return FST_MLA_OK;
 }
 

@@ -9,6 +9,7 @@
 // the library image instead, so it needs no context and allocates nothing, at the price of a
 // stated maximum problem size.
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 
 #include "../../include/fst_cuda_mla.h"
@@ -71,8 +72,12 @@ __global__ void k_na_setup(unsigned char* scratch, int n_rows, int n_splits) {
   }
 }
 
+// Failures are reported like those of every other entry point: the message goes to the calling
+// thread's last-error string (fst_cuda_mla_last_error).
 int na_fail(int code, const char* msg) {
-  fprintf(stderr, "fst_cuda_mla_attention_noalloc: %s\n", msg);
+  char buf[256];
+  snprintf(buf, sizeof(buf), "fst_cuda_mla_attention_noalloc: %s", msg);
+  set_last_error(buf);
   return code;
 }
 
@@ -82,8 +87,10 @@ extern "C" int fst_cuda_mla_attention_noalloc(const void* d_q_eff, const void* d
                                               int32_t n_heads, int32_t d_qk, int32_t d_v, float softmax_scale,
                                               void* d_o_lat, void* cuda_stream) {
   if (!d_q_eff || !d_cache || !d_o_lat) return na_fail(FST_MLA_ERR_ARG, "null device pointer");
-  if (n_rows <= 0 || n_heads <= 0 || d_qk <= 0 || d_v <= 0 || softmax_scale <= 0.0f)
-    return na_fail(FST_MLA_ERR_ARG, "non-positive size or scale");
+  if (n_rows <= 0 || n_heads <= 0 || d_qk <= 0 || d_v <= 0)
+    return na_fail(FST_MLA_ERR_ARG, "non-positive size");
+  if (!(softmax_scale > 0.0f) || !std::isfinite(softmax_scale))  // also rejects NaN
+    return na_fail(FST_MLA_ERR_ARG, "softmax_scale must be a positive finite number");
   if (n_rows > NA_MAX_ROWS || n_heads > NA_MAX_HEADS || d_v > NA_MAX_DV || d_qk > NA_MAX_DQK)
     return na_fail(FST_MLA_ERR_CAPACITY,
                    "beyond the fixed scratch: at most 65536 cached rows, 64 heads, d_qk 576, d_v 512");
@@ -93,6 +100,10 @@ extern "C" int fst_cuda_mla_attention_noalloc(const void* d_q_eff, const void* d
     return na_fail(FST_MLA_ERR_ARG, "q_eff and cache must be 16-byte aligned");
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return na_fail(FST_MLA_ERR_NO_DEVICE, "no current CUDA device");
+  // An error left pending by an earlier call of the caller's is the caller's to read: it is
+  // reported here but not cleared, and nothing is launched on top of it.
+  if (cudaPeekAtLastError() != cudaSuccess)
+    return na_fail(FST_MLA_ERR_CUDA, "a CUDA error from an earlier call is pending on this thread; nothing was launched");
   if (dev < 0 || dev >= 64) return na_fail(FST_MLA_ERR_ARG, "device ordinal out of range");
   if (!g_na_ptr[dev]) {
     // first call on this device: resolve the device address of the scratch array

@@ -59,11 +59,11 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 
 constexpr uint32_t WAIT_LIMIT = 1u << 22;  // polls before a wait is given up
 
-// Bounded wait.  Gives up when `*abort_flag` is raised by another role or after WAIT_LIMIT
+// Bounded wait.  Gives up when `*abort_flag` is raised by another role or after `limit`
 // polls; in the second case it raises the flag itself and records `code` in *d_status.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* d_status, int code) {
-  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+                                          int* d_status, int code, uint32_t limit = WAIT_LIMIT) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > 1024) {  // the common case completes within a few polls: back off only after that
       if (*abort_flag) return false;

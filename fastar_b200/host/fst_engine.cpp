@@ -37,10 +37,9 @@ FSTEngine::FSTEngine(const ModelConfig& cfg) : config_(cfg) {
   c.v_head = 128;
   c.o_groups = 8;
   c.o_lora = 1024;
-  c.rope_theta = 10000.0f;
+  c.rope_theta = cfg.rope_freq_base > 0.0f ? cfg.rope_freq_base : 10000.0f;
   c.rms_eps = 1e-6f;
-  // one context serves layers of one RoPE kind; a model mixing plain and YaRN layers uses two
-  c.rope_yarn = !cfg.compress_ratios.empty() && cfg.compress_ratios[0] != 0;
+  c.rope_yarn = 0;  // the kind is a property of each layer: preload_all_layers sets it
   c.n_layers = cfg.n_layers;
   c.page_tokens = cfg.page_tokens;
   const int pages_per_seq = (cfg.max_seq + cfg.page_tokens - 1) / cfg.page_tokens;
@@ -86,9 +85,13 @@ MlaSizes sizes_of(const ModelConfig& c) {
   return z;
 }
 
+// A matrix is looked up by its shape among the entries of its tensor id first, as the engine finds
+// it (src/fst_engine.cpp:1553-1558, 1610-1615) -- one converter path stores wq_a / wq_b and wo_a / wo_b
+// under one (tensor id, sub id) -- and by its sub id when no entry has the expected shape.
 void take_bf16(const std::string& path, const std::vector<fstfile::Entry>& dir, uint32_t tid, int layer, int sub,
-               size_t want, const char* name, std::vector<bf16_t>* dst) {
-  const fstfile::Entry* e = fstfile::find(dir, tid, layer, sub);
+               size_t want, const char* name, std::vector<bf16_t>* dst, uint64_t rows = 0, uint64_t cols = 0) {
+  const fstfile::Entry* e = rows ? fstfile::find_shape(dir, tid, layer, rows, cols ? cols : 1) : nullptr;
+  if (!e) e = fstfile::find(dir, tid, layer, sub);
   if (!e) return;
   std::vector<uint16_t> v = fstfile::load_bf16(path, *e);
   if (want && v.size() != want)
@@ -109,16 +112,42 @@ void take_sinks(const std::string& path, const std::vector<fstfile::Entry>& dir,
 
 }  // namespace
 
+bool FSTEngine::layer_is_compressed(int lid) const {
+  if (config_.preset != FST_MLA_PRESET_FASTAR_V4) return false;
+  return lid < (int)config_.compress_ratios.size() ? config_.compress_ratios[lid] != 0 : lid >= 2;
+}
+
 void FSTEngine::load_shared_weights(const std::string& fst_path) {
-  const std::vector<fstfile::Entry> dir = fstfile::read_directory(fst_path);
+  fstfile::Header hd;
+  const std::vector<fstfile::Entry> dir = fstfile::read_directory(fst_path, &hd);
   const MlaSizes z = sizes_of(config_);
+  // rope_freq_base_ comes from the header (src/fst_engine.cpp:1505)
+  config_.rope_freq_base = hd.rope_freq_base;
+  check(fst_cuda_mla_set_rope_theta(ctx_, config_.rope_freq_base), "set_rope_theta");
+  // compress_ratios: TID 40, F32 [n_layers], float -> int; without it the default pattern 0, 0, 4,
+  // 128, 4, ... with the last two layers uncompressed from layer 41 on (1559-1590)
+  config_.compress_ratios.assign(config_.n_layers, 0);
+  const fstfile::Entry* cr = nullptr;
+  for (const fstfile::Entry& e : dir)
+    if (e.tid == fstfile::TID_COMPRESS_RATIOS) {
+      cr = &e;
+      break;
+    }
+  if (cr) {
+    const std::vector<float> r = fstfile::load_f32(fst_path, *cr);
+    for (int l = 0; l < config_.n_layers && l < (int)r.size(); ++l) config_.compress_ratios[l] = (int)r[l];
+  } else {
+    for (int l = 0; l < config_.n_layers; ++l) config_.compress_ratios[l] = (l < 2 || l >= 41) ? 0 : (l % 2 == 0 ? 4 : 128);
+  }
+  const uint64_t hdim = (uint64_t)config_.hidden_dim, low = 8192;
+  const bool v4 = config_.preset == FST_MLA_PRESET_FASTAR_V4;
   for (int l = 0; l < config_.n_layers; ++l) {
     LayerWeightsC& w = shared_.at(l);
-    take_bf16(fst_path, dir, fstfile::TID_Q_PROJ, l, 0, z.wq_a, "wq_a", &w.wq_a);
-    take_bf16(fst_path, dir, fstfile::TID_Q_PROJ, l, 1, z.wq_b, "wq_b", &w.wq_b);
+    take_bf16(fst_path, dir, fstfile::TID_Q_PROJ, l, 0, z.wq_a, "wq_a", &w.wq_a, MLA_Q_LORA, hdim);
+    take_bf16(fst_path, dir, fstfile::TID_Q_PROJ, l, 1, z.wq_b, "wq_b", &w.wq_b, z.wq_b / MLA_Q_LORA, MLA_Q_LORA);
     take_bf16(fst_path, dir, fstfile::TID_K_PROJ, l, 0, z.wkv, "wkv", &w.wkv);
-    take_bf16(fst_path, dir, fstfile::TID_O_PROJ, l, 0, z.wo_a, "wo_a", &w.wo_a);
-    take_bf16(fst_path, dir, fstfile::TID_O_PROJ, l, 1, z.wo_b, "wo_b", &w.wo_b);
+    if (v4) take_bf16(fst_path, dir, fstfile::TID_O_PROJ, l, 0, z.wo_a, "wo_a", &w.wo_a, low, z.wo_a / low);
+    take_bf16(fst_path, dir, fstfile::TID_O_PROJ, l, 1, z.wo_b, "wo_b", &w.wo_b, hdim, low);
     take_bf16(fst_path, dir, fstfile::TID_Q_NORM, l, 0, z.q_norm, "q_norm", &w.q_norm);
     take_bf16(fst_path, dir, fstfile::TID_KV_NORM, l, 0, z.kv_norm, "kv_norm", &w.kv_norm);
     take_bf16(fst_path, dir, fstfile::TID_INPUT_NORM, l, 0, z.attn_norm, "attn_norm", &w.attn_norm);
@@ -155,6 +184,7 @@ void FSTEngine::preload_all_layers() {
     fw.attn_sinks = w.attn_sinks.empty() ? nullptr : w.attn_sinks.data();
     fw.attn_norm = p(w.attn_norm);
     check(fst_cuda_mla_set_layer_weights(ctx_, l, &fw), "set_layer_weights");
+    check(fst_cuda_mla_set_layer_rope(ctx_, l, layer_is_compressed(l) ? 1 : 0), "set_layer_rope");
   }
 }
 

@@ -26,6 +26,7 @@ struct ModelConfig {
   int max_seq = 128;        // capacity of one sequence (the reference's flat cache length)
   int rope_dim = MLA_ROPE_DIM;
   std::vector<int> compress_ratios;  // per layer; non-zero selects the YaRN RoPE table (1979-1982)
+  float rope_freq_base = 10000.0f;   // base of the plain tables (rope_freq_base_, 1505: the file header's, else 10000)
   // what this build adds
   int preset = FST_MLA_PRESET_FASTAR_V4;  // FST_MLA_PRESET_BASELINE for the 576-wide form
   int page_tokens = 64;
@@ -105,6 +106,11 @@ class FSTEngine {
   // Random-matrix probe of the GEMM tile engine (randmat_test, 586-685): xorshift-seeded
   // uniform [-1, 1] bf16 A[16, K], B[N, K] against a double-precision CPU product.
   std::vector<RandmatResult> randmat_test();
+
+  // RoPE kind of a layer as build_rope_lut chooses it (src/fst_engine.cpp:1979-1982): YaRN when the
+  // layer's compress ratio is non-zero; a layer the ratios do not cover counts as compressed from
+  // layer 2 on.  The 576-wide BASELINE form has no compressed layers.
+  bool layer_is_compressed(int lid) const;
 
   FstMlaCtx* ctx() { return ctx_; }
 

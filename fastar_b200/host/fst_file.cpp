@@ -165,6 +165,14 @@ const Entry* find(const std::vector<Entry>& dir, uint32_t tid, int layer, int su
   return nullptr;
 }
 
+const Entry* find_shape(const std::vector<Entry>& dir, uint32_t tid, int layer, uint64_t s0, uint64_t s1) {
+  for (const Entry& e : dir)
+    if (e.tid == tid && (e.layer == layer || e.layer == GLOBAL_LAYER) && e.ndim >= 1 && e.shape[0] == s0 &&
+        (e.ndim >= 2 ? e.shape[1] : 1) == s1)
+      return &e;
+  return nullptr;
+}
+
 std::vector<uint16_t> load_bf16(const std::string& path, const Entry& e) {
   std::vector<float> f;
   std::vector<uint16_t> b;

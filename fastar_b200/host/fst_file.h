@@ -16,6 +16,7 @@ namespace fstfile {
 
 constexpr uint32_t TID_INPUT_NORM = 3, TID_Q_PROJ = 5, TID_K_PROJ = 6, TID_O_PROJ = 8;
 constexpr uint32_t TID_Q_NORM = 14, TID_KV_NORM = 15, TID_ATTN_SINK = 22;
+constexpr uint32_t TID_COMPRESS_RATIOS = 40;  // F32 [n_layers], stored once (src/fst_engine.cpp:1559-1590)
 constexpr int QTYPE_Q8_0 = 1, QTYPE_BF16 = 2, QTYPE_F32 = 3;
 constexpr int GLOBAL_LAYER = 0xFFFF;
 
@@ -40,6 +41,11 @@ Header read_header(const std::string& path);
 std::vector<Entry> read_directory(const std::string& path, Header* header_out = nullptr);
 // First entry with this tensor id and sub id for the layer (or stored as global); nullptr if none.
 const Entry* find(const std::vector<Entry>& dir, uint32_t tid, int layer, int sub = 0);
+// First entry with this tensor id for the layer (or global) whose shape is [s0, s1]: the engine itself
+// finds its matrices by shape (src/fst_engine.cpp:1553-1558, 1610-1615), and one of the converter's
+// paths stores wq_a and wq_b (and wo_a and wo_b) under the same tensor id AND sub id 0
+// (scripts/fst_converter.py:636-644), so the sub id alone cannot tell them apart.
+const Entry* find_shape(const std::vector<Entry>& dir, uint32_t tid, int layer, uint64_t s0, uint64_t s1);
 // BF16 and Q8_0 tensors as bf16 bits; an F32 tensor is truncated to bf16.
 std::vector<uint16_t> load_bf16(const std::string& path, const Entry& e);
 // F32 tensors as they are; BF16 and Q8_0 widened to fp32.

@@ -112,6 +112,12 @@ def load_library() -> C.CDLL:
     L.fst_cuda_mla_set_plan_reuse.argtypes = [vp, i32]
     L.fst_cuda_mla_set_window.argtypes = [vp, i32]
     L.fst_cuda_mla_plan_counts.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
+    L.fst_cuda_mla_set_layer_rope.argtypes = [vp, C.c_int, i32]
+    L.fst_cuda_mla_set_rope_theta.argtypes = [vp, C.c_float]
+    L.fst_cuda_mla_family_counts.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
+    L.fst_cuda_mla_selftest_wait_expiry.argtypes = [vp, i32]
+    L.fst_cuda_mla_debug_set_status.argtypes = [vp, i32]
+    L.fst_cuda_mla_debug_attr_first_use.argtypes = [C.c_uint64, i32, i64]
     L.fst_cuda_mla_attention_noalloc.argtypes = [vp, vp, i32, i32, i32, i32, C.c_float, vp, vp]
     _lib = L
     return L
@@ -203,6 +209,13 @@ class MlaContext:
                 setattr(w, name, _u16(a))
             keep[name] = a
         self._check(self.lib.fst_cuda_mla_set_layer_weights(self._h, lid, C.byref(w)))
+
+    def set_layer_rope(self, lid: int, yarn: bool) -> None:
+        """RoPE kind of one layer: plain, or the YaRN tables of the compressed V4 layers."""
+        self._check(self.lib.fst_cuda_mla_set_layer_rope(self._h, lid, 1 if yarn else 0))
+
+    def set_rope_theta(self, theta: float) -> None:
+        self._check(self.lib.fst_cuda_mla_set_rope_theta(self._h, theta))
 
     # -- paged cache --
     def seq_alloc(self) -> int:
@@ -362,6 +375,18 @@ class MlaContext:
         n = C.c_int64()
         self._check(self.lib.fst_cuda_mla_launch_count(self._h, C.byref(n)))
         return n.value
+
+    def family_counts(self) -> dict:
+        """GEMM and attention launches so far by kernel family."""
+        a, b = C.c_int64(0), C.c_int64(0)
+        self._check(self.lib.fst_cuda_mla_family_counts(self._h, C.byref(a), C.byref(b)))
+        return {"tensor": a.value, "simt": b.value}
+
+    def selftest_wait_expiry(self, polls: int = 2000) -> None:
+        self._check(self.lib.fst_cuda_mla_selftest_wait_expiry(self._h, polls))
+
+    def debug_set_status(self, code: int) -> None:
+        self._check(self.lib.fst_cuda_mla_debug_set_status(self._h, code))
 
     def set_profiling(self, on: bool) -> None:
         self._check(self.lib.fst_cuda_mla_set_profiling(self._h, int(on)))

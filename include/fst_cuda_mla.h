@@ -61,7 +61,9 @@ typedef struct FstMlaConfig {
   float softmax_scale; /* <= 0: preset default (1/sqrt(nope+rope) or 1/sqrt(kv_lora)) */
   float rope_theta;    /* 10000 */
   float rms_eps;       /* 1e-6 */
-  int32_t rope_yarn;   /* V4 compressed layers: YaRN tables (src/fst_engine.cpp:1995-2022) */
+  int32_t rope_yarn;   /* RoPE kind every layer starts with: 0 plain, 1 the YaRN tables of the V4
+                          compressed layers (src/fst_engine.cpp:1995-2022); per layer:
+                          fst_cuda_mla_set_layer_rope */
   int32_t n_layers;
   int32_t page_tokens; /* 64 */
   int32_t n_pages;     /* pages per layer in the pool */
@@ -144,6 +146,16 @@ int fst_cuda_mla_sync(FstMlaCtx* ctx);
 
 /* ---- weights -------------------------------------------------------------------------- */
 int fst_cuda_mla_set_layer_weights(FstMlaCtx* ctx, int lid, const FstMlaWeights* w);
+
+/* RoPE kind of one layer.  build_rope_lut (src/fst_engine.cpp:1970-2023) chooses per layer: plain
+ * RoPE with the model's base for layers whose compress ratio is 0, YaRN (base 160000, scale 1/16)
+ * for the others (1979-1982).  yarn: 0 plain, 1 YaRN.  q, k and the V4 inverse output rotation of
+ * that layer all use the chosen table; a context whose layers differ keeps both tables per plan. */
+int fst_cuda_mla_set_layer_rope(FstMlaCtx* ctx, int lid, int32_t yarn);
+/* Base of the plain RoPE tables (FstMlaConfig.rope_theta) when it is only known after the
+ * context exists: the engine takes it from the checkpoint header (rope_freq_base_,
+ * src/fst_engine.cpp:1505). */
+int fst_cuda_mla_set_rope_theta(FstMlaCtx* ctx, float theta);
 
 /* ---- paged latent cache --------------------------------------------------------------- */
 /* The reference cache is one flat [max_seq, 512] bf16 buffer per layer indexed by seq_pos_
@@ -232,6 +244,28 @@ int fst_cuda_mla_kernel_times(FstMlaCtx* ctx, float* ms_out, int32_t* n_out);
 /* Schedule of the current plan: partial count, CTAs of the attention kernel, cached rows read. */
 int fst_cuda_mla_plan_info(FstMlaCtx* ctx, int32_t* n_partials, int32_t* n_ctas, int64_t* kv_rows);
 
+/* GEMM and attention launches so far by kernel family: tcgen05 kernels, CUDA-core kernels.
+ * FST_MLA_IMPL_AUTO takes the CUDA-core kernels for shapes the tcgen05 kernels do not cover
+ * (head count other than 64, pages other than 64 tokens, unaligned rows); a benchmark prints
+ * these so that the slow family can never be measured unnoticed. */
+int fst_cuda_mla_family_counts(FstMlaCtx* ctx, int64_t* tensor_out, int64_t* simt_out);
+
+/* ---- robustness checks ------------------------------------------------------------------ */
+/* Every wait inside the kernels is bounded: a kernel that gives one up records a status word,
+ * lets its copies land, frees its tensor memory and returns; the next fst_cuda_mla_sync then
+ * returns FST_MLA_ERR_DEVICE_CHECK and clears the word, and the context stays usable.  This call
+ * exercises that path without touching the product kernels: one tiny kernel (no TMA, no MMA, no
+ * tensor memory) waits on a barrier that nothing arrives at, with a limit of `polls` polls
+ * (1 .. 65536), gives up and records its status.  Enqueued on the context's stream. */
+int fst_cuda_mla_selftest_wait_expiry(FstMlaCtx* ctx, int32_t polls);
+/* Test hook: writes `code` into the device status word, as a kernel that failed a check would. */
+int fst_cuda_mla_debug_set_status(FstMlaCtx* ctx, int32_t code);
+/* Test hook, host only (no CUDA call): the library sets function attributes (the dynamic
+ * shared-memory limit, the carve-out preference) once per (kernel, device), because they belong
+ * to the device that is current when they are set.  Returns 1 the first time the triple
+ * (kernel_key, device, value) is seen -- and again when a later value is larger -- else 0. */
+int fst_cuda_mla_debug_attr_first_use(uint64_t kernel_key, int32_t device, int64_t value);
+
 /* ---- decode attention without any allocation -------------------------------------------- */
 /* No counterpart in the reference.  For callers that cannot allocate device memory at the
  * moment they need attention: a serving process whose device memory was handed out in full at
@@ -240,14 +274,17 @@ int fst_cuda_mla_plan_info(FstMlaCtx* ctx, int32_t* n_partials, int32_t* n_ctas,
  * cudaMalloc / cudaFree nor any allocating library routine.
  *
  * One query token: d_q_eff device bf16 [n_heads, d_qk]; d_cache device bf16 [n_rows, d_qk],
- * contiguous rows, keys = row[:d_qk], values = row[:d_v]; d_o_lat device bf16 [n_heads, d_v]
+ * contiguous rows whose stride is exactly d_qk elements (no padding between rows),
+ * keys = row[:d_qk], values = row[:d_v]; d_o_lat device bf16 [n_heads, d_v]
  * = softmax(scale * q K^T) V, no sink.  Both inputs 16-byte aligned.  Work is enqueued on
  * cuda_stream (NULL: default stream) of the current device; the call does not synchronise.
  *
  * The split-KV partials live in a fixed array inside the library image (about 4 MiB, held by
  * every GPU that loads the library until the process exits), hence the limits: n_rows <= 65536,
  * n_heads <= 64, d_qk <= 576 (multiple of 8), d_v <= 512 (multiple of 64, <= d_qk).  Anything
- * larger returns FST_MLA_ERR_CAPACITY (a line on stderr says why); use the context API then.
+ * larger returns FST_MLA_ERR_CAPACITY (fst_cuda_mla_last_error says why); use the context API
+ * then.  A CUDA error that an earlier call left pending on the calling thread is reported as
+ * FST_MLA_ERR_CUDA without being cleared, and nothing is launched.
  * All calls share that one array: it keeps the previous call's contents, every call rewrites
  * whatever it later reads (nothing has to start at zero), and two calls that overlap on the
  * GPU -- different streams, or different host threads -- race on it.  Serialise them.

@@ -11,6 +11,7 @@
 #include "mla_oracle.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -71,6 +72,23 @@ void parallel_for(int64_t n, int n_threads, const std::function<void(int64_t, in
     if (a >= b) break;
     th.emplace_back([=, &fn] { fn(a, b); });
   }
+  for (auto& t : th) t.join();
+}
+
+/* Work items [0, n) handed out one at a time from a shared counter: for items of uneven cost
+ * (sequences of different lengths). */
+void parallel_dynamic(int64_t n, int n_threads, const std::function<void(int64_t)>& fn) {
+  n_threads = (int)std::min<int64_t>(resolve_threads(n_threads), std::max<int64_t>(n, 1));
+  if (n_threads <= 1) {
+    for (int64_t i = 0; i < n; ++i) fn(i);
+    return;
+  }
+  std::atomic<int64_t> next{0};
+  std::vector<std::thread> th;
+  for (int t = 0; t < n_threads; ++t)
+    th.emplace_back([&] {
+      for (int64_t i = next.fetch_add(1); i < n; i = next.fetch_add(1)) fn(i);
+    });
   for (auto& t : th) t.join();
 }
 
@@ -227,6 +245,41 @@ void fst_oracle_gemm(const float* A, const float* B, float* C, int M, int N, int
   }
 }
 
+}  /* extern "C" */
+
+namespace {
+
+/* One (query token, head) row of QK -> softmax -> SV over rows [0, S) of `cache`. */
+void attention_row(const FstOracleCfg* c, const Dims& d, const float* q, const float* cache, int S,
+                   bool has_sink, float sink, std::vector<float>& sc, std::vector<double>& acc, float* o) {
+  const float scale = c->softmax_scale;
+  const int rb = c->round_bf16;
+  if ((int)sc.size() < S) sc.resize(S);
+  float mx = has_sink ? sink : -INFINITY;
+  for (int s = 0; s < S; ++s) {
+    sc[s] = dot(q, cache + (size_t)s * d.row, d.d_qk) * scale;
+    mx = std::max(mx, sc[s]);
+  }
+  if (S <= 0 && !has_sink) {
+    for (int j = 0; j < d.d_v; ++j) o[j] = 0.0f;
+    return;
+  }
+  float sum = has_sink ? std::exp(sink - mx) : 0.0f;
+  for (int s = 0; s < S; ++s) sum += std::exp(sc[s] - mx);
+  const float inv = 1.0f / (sum + 1e-12f);
+  std::fill(acc.begin(), acc.end(), 0.0);
+  for (int s = 0; s < S; ++s) {
+    const float p = rnd(std::exp(sc[s] - mx) * inv, rb);
+    const float* v = cache + (size_t)s * d.row;
+    for (int j = 0; j < d.d_v; ++j) acc[j] += (double)p * v[j];
+  }
+  for (int j = 0; j < d.d_v; ++j) o[j] = rnd((float)acc[j], rb);
+}
+
+}  // namespace
+
+extern "C" {
+
 /* QK -> softmax -> SV of src/fst_engine.cpp:3573-3683 for one sequence.
  * Softmax (3614-3666): v = score * scale; max starts at the sink logit; sum starts at
  * exp(sink - max); p = exp(v - max) / (sum + 1e-12), rounded to bf16 (3651-3652); masked
@@ -236,38 +289,16 @@ void fst_oracle_attention(const FstOracleCfg* c, const float* q_eff, const float
                           int kv_len, int n_q, int pos0, int causal, const float* sinks,
                           float* out) {
   const Dims d = dims_of(c);
-  const float scale = c->softmax_scale;
-  const int rb = c->round_bf16;
   parallel_for((int64_t)n_q * d.H, c->n_threads, [&](int64_t r0, int64_t r1) {
     std::vector<float> sc(std::max(kv_len, 1));
     std::vector<double> acc(d.d_v);
     for (int64_t r = r0; r < r1; ++r) {
       const int i = (int)(r / d.H), hh = (int)(r % d.H);
-      const float* q = q_eff + (size_t)r * d.d_qk;
       int S = kv_len;
       if (causal) S = std::min(S, pos0 + i + 1);
       const bool has_sink = c->use_sink && sinks;
-      const float sink = has_sink ? sinks[hh] : 0.0f;
-      float mx = has_sink ? sink : -INFINITY;
-      for (int s = 0; s < S; ++s) {
-        sc[s] = dot(q, cache + (size_t)s * d.row, d.d_qk) * scale;
-        mx = std::max(mx, sc[s]);
-      }
-      float* o = out + (size_t)r * d.d_v;
-      if (S <= 0 && !has_sink) {
-        for (int j = 0; j < d.d_v; ++j) o[j] = 0.0f;
-        continue;
-      }
-      float sum = has_sink ? std::exp(sink - mx) : 0.0f;
-      for (int s = 0; s < S; ++s) sum += std::exp(sc[s] - mx);
-      const float inv = 1.0f / (sum + 1e-12f);
-      std::fill(acc.begin(), acc.end(), 0.0);
-      for (int s = 0; s < S; ++s) {
-        const float p = rnd(std::exp(sc[s] - mx) * inv, rb);
-        const float* v = cache + (size_t)s * d.row;
-        for (int j = 0; j < d.d_v; ++j) acc[j] += (double)p * v[j];
-      }
-      for (int j = 0; j < d.d_v; ++j) o[j] = rnd((float)acc[j], rb);
+      attention_row(c, d, q_eff + (size_t)r * d.d_qk, cache, S, has_sink, has_sink ? sinks[hh] : 0.0f, sc, acc,
+                    out + (size_t)r * d.d_v);
     }
   });
 }
@@ -333,66 +364,81 @@ void fst_oracle_merge_partials(const FstOracleCfg* c, const float* m, const floa
   }
 }
 
-/* process_mla, src/fst_engine.cpp:3320-3890, stage by stage. */
-int fst_oracle_mla_forward(const FstOracleCfg* c, const FstOracleWeights* w, const float* h, int M,
-                           int pos0, int causal, float* cache, int cap, float* out,
-                           FstOracleTrace* trace) {
+/* process_mla, src/fst_engine.cpp:3320-3890, stage by stage, for B sequences in one call.  The
+ * reference runs one sequence per call; here the rows of all sequences share every projection
+ * (one product over T = sum q_lens rows, the weights read once), and the per-sequence stages
+ * (RoPE position, cache push, attention) follow each row's own sequence.  h[T, hidden] holds the
+ * sequences' rows back to back; trace buffers are sized for T rows. */
+int fst_oracle_mla_forward_batch(const FstOracleCfg* c, const FstOracleWeights* w, const float* h, int B,
+                                 const int32_t* q_lens, const int32_t* pos0, int causal, float* const* caches,
+                                 const int32_t* caps, float* out, FstOracleTrace* trace) {
   const Dims d = dims_of(c);
   const int rb = c->round_bf16, nt = c->n_threads;
-  if (pos0 < 0 || M < 0 || pos0 + M > cap) return -1; /* assert at 3327 */
-  if (M == 0) return 0;
+  if (B < 0) return -1;
+  std::vector<int> seq_of, pos_of, tok0(B + 1, 0);
+  for (int b = 0; b < B; ++b) {
+    if (pos0[b] < 0 || q_lens[b] < 0 || pos0[b] + q_lens[b] > caps[b]) return -1; /* assert at 3327 */
+    for (int i = 0; i < q_lens[b]; ++i) {
+      seq_of.push_back(b);
+      pos_of.push_back(pos0[b] + i);
+    }
+    tok0[b + 1] = (int)seq_of.size();
+  }
+  const int T = (int)seq_of.size();
+  if (T == 0) return 0;
   const bool v4 = c->preset == FST_ORACLE_PRESET_FASTAR_V4;
 
   /* attn_norm of process_layer (2687-2688), when its weight is given: an = rmsnorm(h) * w. */
   std::vector<float> an;
   if (w->attn_norm) {
-    an.resize((size_t)M * d.hidden);
-    fst_oracle_rmsnorm(h, w->attn_norm, an.data(), M, d.hidden, c->rms_eps, rb);
+    an.resize((size_t)T * d.hidden);
+    fst_oracle_rmsnorm(h, w->attn_norm, an.data(), T, d.hidden, c->rms_eps, rb);
     h = an.data();
   }
 
   /* q compress (3362-3364) + q_norm (3385-3389). */
-  std::vector<float> qc((size_t)M * d.q_lora);
-  fst_oracle_gemm(h, w->wq_a, qc.data(), M, d.q_lora, d.hidden, 0, rb, nt);
-  if (w->q_norm) fst_oracle_rmsnorm(qc.data(), w->q_norm, qc.data(), M, d.q_lora, c->rms_eps, rb);
+  std::vector<float> qc((size_t)T * d.q_lora);
+  fst_oracle_gemm(h, w->wq_a, qc.data(), T, d.q_lora, d.hidden, 0, rb, nt);
+  if (w->q_norm) fst_oracle_rmsnorm(qc.data(), w->q_norm, qc.data(), T, d.q_lora, c->rms_eps, rb);
 
   /* kv compress (3366-3368) + kv_norm on the kv_lora latent (3390-3394). BASELINE: the
    * projection has kv_lora + rope outputs and the trailing k_pe is not normed. */
-  std::vector<float> kv((size_t)M * d.row);
-  fst_oracle_gemm(h, w->wkv_a, kv.data(), M, d.row, d.hidden, 0, rb, nt);
-  for (int m = 0; m < M; ++m) {
+  std::vector<float> kv((size_t)T * d.row);
+  fst_oracle_gemm(h, w->wkv_a, kv.data(), T, d.row, d.hidden, 0, rb, nt);
+  for (int m = 0; m < T; ++m) {
     float* r = kv.data() + (size_t)m * d.row;
     if (w->kv_norm) fst_oracle_rmsnorm(r, w->kv_norm, r, 1, d.kv_lora, c->rms_eps, rb);
     /* RoPE on the key's rope dims (3504-3517): V4 row tail, BASELINE the separate k_pe. */
-    fst_oracle_rope_apply(r + d.row - d.rope, pos0 + m, d.rope, c->rope_theta, c->rope_yarn, 0, rb);
+    fst_oracle_rope_apply(r + d.row - d.rope, pos_of[m], d.rope, c->rope_theta, c->rope_yarn, 0, rb);
   }
   if (trace && trace->qc) std::memcpy(trace->qc, qc.data(), qc.size() * sizeof(float));
   if (trace && trace->kv) std::memcpy(trace->kv, kv.data(), kv.size() * sizeof(float));
 
   /* q expand (3409-3473). */
   const int qn = d.H * d.q_head;
-  std::vector<float> q_full((size_t)M * qn);
-  fst_oracle_gemm(qc.data(), w->wq_b, q_full.data(), M, qn, d.q_lora, 0, rb, nt);
+  std::vector<float> q_full((size_t)T * qn);
+  fst_oracle_gemm(qc.data(), w->wq_b, q_full.data(), T, qn, d.q_lora, 0, rb, nt);
 
-  std::vector<float> q_eff((size_t)M * d.H * d.d_qk);
+  std::vector<float> q_eff((size_t)T * d.H * d.d_qk);
   if (v4) {
     /* per-head weightless RMSNorm (3487-3495), then RoPE on every head's tail (3503). */
-    for (int r = 0; r < M * d.H; ++r) {
-      float* qh = q_full.data() + (size_t)r * d.q_head;
-      fst_oracle_rmsnorm(qh, nullptr, qh, 1, d.q_head, c->rms_eps, rb);
-      fst_oracle_rope_apply(qh + d.nope, pos0 + r / d.H, d.rope, c->rope_theta, c->rope_yarn, 0, rb);
-      std::memcpy(q_eff.data() + (size_t)r * d.d_qk, qh, d.q_head * sizeof(float));
-    }
+    parallel_for((int64_t)T * d.H, nt, [&](int64_t r0, int64_t r1) {
+      for (int64_t r = r0; r < r1; ++r) {
+        float* qh = q_full.data() + (size_t)r * d.q_head;
+        fst_oracle_rmsnorm(qh, nullptr, qh, 1, d.q_head, c->rms_eps, rb);
+        fst_oracle_rope_apply(qh + d.nope, pos_of[r / d.H], d.rope, c->rope_theta, c->rope_yarn, 0, rb);
+        std::memcpy(q_eff.data() + (size_t)r * d.d_qk, qh, d.q_head * sizeof(float));
+      }
+    });
   } else {
     /* BASELINE: rotate q_pe, absorb q_nope through W_UK (rows [h*(nope+v), +nope) of
      * wkv_b, each [kv_lora]): q_lat[c] = sum_n q_nope[n] * W_UK[h][n, c]. */
-    parallel_for((int64_t)M * d.H, nt, [&](int64_t r0, int64_t r1) {
+    parallel_for((int64_t)T * d.H, nt, [&](int64_t r0, int64_t r1) {
       std::vector<double> acc(d.kv_lora);
       for (int64_t r = r0; r < r1; ++r) {
         const int hh = (int)(r % d.H);
         float* qh = q_full.data() + (size_t)r * d.q_head;
-        fst_oracle_rope_apply(qh + d.nope, pos0 + (int)(r / d.H), d.rope, c->rope_theta,
-                              c->rope_yarn, 0, rb);
+        fst_oracle_rope_apply(qh + d.nope, pos_of[r / d.H], d.rope, c->rope_theta, c->rope_yarn, 0, rb);
         const float* wuk = w->wkv_b + (size_t)hh * (d.nope + d.v_head) * d.kv_lora;
         std::fill(acc.begin(), acc.end(), 0.0);
         for (int n = 0; n < d.nope; ++n) {
@@ -408,31 +454,46 @@ int fst_oracle_mla_forward(const FstOracleCfg* c, const FstOracleWeights* w, con
   }
   if (trace && trace->q_eff) std::memcpy(trace->q_eff, q_eff.data(), q_eff.size() * sizeof(float));
 
-  /* cache push (3534-3544): rows pos0 .. pos0+M-1. */
-  std::memcpy(cache + (size_t)pos0 * d.row, kv.data(), kv.size() * sizeof(float));
+  /* cache push (3534-3544): rows pos0 .. pos0+M-1 of every sequence. */
+  for (int b = 0; b < B; ++b)
+    if (q_lens[b] > 0)
+      std::memcpy(caches[b] + (size_t)pos0[b] * d.row, kv.data() + (size_t)tok0[b] * d.row,
+                  (size_t)q_lens[b] * d.row * sizeof(float));
 
-  /* QK, softmax, SV (3573-3683) over S = pos0 + M rows. */
-  std::vector<float> o_lat((size_t)M * d.H * d.d_v);
-  fst_oracle_attention(c, q_eff.data(), cache, pos0 + M, M, pos0, causal, w->attn_sinks,
-                       o_lat.data());
+  /* QK, softmax, SV (3573-3683): a row (token, head) attends to S = pos0 + M rows of its own
+   * sequence, minus the rows the causal mask drops (3626). */
+  std::vector<float> o_lat((size_t)T * d.H * d.d_v);
+  {
+    const bool has_sink = c->use_sink && w->attn_sinks;
+    parallel_dynamic((int64_t)T * d.H, nt, [&](int64_t r) {
+      thread_local std::vector<float> sc;
+      thread_local std::vector<double> acc;
+      if ((int)acc.size() != d.d_v) acc.assign(d.d_v, 0.0);
+      const int t = (int)(r / d.H), hh = (int)(r % d.H), b = seq_of[t];
+      int S = pos0[b] + q_lens[b];
+      if (causal) S = std::min(S, pos_of[t] + 1);
+      attention_row(c, d, q_eff.data() + (size_t)r * d.d_qk, caches[b], S, has_sink,
+                    has_sink ? w->attn_sinks[hh] : 0.0f, sc, acc, o_lat.data() + (size_t)r * d.d_v);
+    });
+  }
 
   /* V4: inverse RoPE on every head's output tail (3716). */
   if (v4)
-    for (int r = 0; r < M * d.H; ++r)
-      fst_oracle_rope_apply(o_lat.data() + (size_t)r * d.d_v + d.nope, pos0 + r / d.H, d.rope,
+    for (int r = 0; r < T * d.H; ++r)
+      fst_oracle_rope_apply(o_lat.data() + (size_t)r * d.d_v + d.nope, pos_of[r / d.H], d.rope,
                             c->rope_theta, c->rope_yarn, 1, rb);
   if (trace && trace->o_lat) std::memcpy(trace->o_lat, o_lat.data(), o_lat.size() * sizeof(float));
 
   /* O-proj a. V4 (3736-3839): low[:, g*o_lora:(g+1)*o_lora] = heads[:, g*gk:(g+1)*gk] *
    * wo_a[g*o_lora:(g+1)*o_lora, :]^T with gk = H*512/o_groups.  BASELINE: the per-head
    * W_UV (rows [h*(nope+v)+nope, +v) of wkv_b): low[h*v + j] = sum_c W_UV[h][j,c] o_lat[h][c]. */
-  std::vector<float> low((size_t)M * d.low);
+  std::vector<float> low((size_t)T * d.low);
   if (v4) {
     const int gk = d.H * d.d_v / c->o_groups;
     parallel_for((int64_t)c->o_groups * c->o_lora, nt, [&](int64_t n0, int64_t n1) {
       for (int64_t n = n0; n < n1; ++n) {
         const int g = (int)(n / c->o_lora);
-        for (int m = 0; m < M; ++m)
+        for (int m = 0; m < T; ++m)
           low[(size_t)m * d.low + n] = rnd(
               dot(o_lat.data() + (size_t)m * d.H * d.d_v + (size_t)g * gk, w->wo_a + (size_t)n * gk, gk), rb);
       }
@@ -442,7 +503,7 @@ int fst_oracle_mla_forward(const FstOracleCfg* c, const FstOracleWeights* w, con
       for (int64_t n = n0; n < n1; ++n) {
         const int hh = (int)(n / d.v_head), j = (int)(n % d.v_head);
         const float* wuv = w->wkv_b + ((size_t)hh * (d.nope + d.v_head) + d.nope + j) * d.kv_lora;
-        for (int m = 0; m < M; ++m)
+        for (int m = 0; m < T; ++m)
           low[(size_t)m * d.low + n] =
               rnd(dot(o_lat.data() + ((size_t)m * d.H + hh) * d.d_v, wuv, d.d_v), rb);
       }
@@ -451,8 +512,17 @@ int fst_oracle_mla_forward(const FstOracleCfg* c, const FstOracleWeights* w, con
   if (trace && trace->low) std::memcpy(trace->low, low.data(), low.size() * sizeof(float));
 
   /* O-proj b (3853-3868): attn_out = low * wo_b^T, written back over h by the caller (3889). */
-  fst_oracle_gemm(low.data(), w->wo_b, out, M, d.hidden, d.low, 0, rb, nt);
+  fst_oracle_gemm(low.data(), w->wo_b, out, T, d.hidden, d.low, 0, rb, nt);
   return 0;
+}
+
+/* The reference's own call shape: one sequence, M new rows at pos0 .. pos0+M-1. */
+int fst_oracle_mla_forward(const FstOracleCfg* c, const FstOracleWeights* w, const float* h, int M,
+                           int pos0, int causal, float* cache, int cap, float* out,
+                           FstOracleTrace* trace) {
+  const int32_t q = M, p = pos0, cp = cap;
+  float* caches[1] = {cache};
+  return fst_oracle_mla_forward_batch(c, w, h, 1, &q, &p, causal, caches, &cp, out, trace);
 }
 
 /* ---- paged-cache bookkeeping twin ------------------------------------------------------

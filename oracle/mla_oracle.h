@@ -144,6 +144,14 @@ int fst_oracle_mla_forward(const FstOracleCfg* c, const FstOracleWeights* w, con
                            int pos0, int causal, float* cache, int cap, float* out,
                            FstOracleTrace* trace);
 
+/* The same layer for B sequences in one call (batched decode): h[T, hidden] holds the rows of
+ * the sequences back to back (T = sum q_lens), caches[b] is sequence b's [caps[b], row] buffer.
+ * Every row gets exactly the arithmetic of fst_oracle_mla_forward; the projections run over all
+ * T rows at once so the weights are read once per call.  Trace buffers hold T rows. */
+int fst_oracle_mla_forward_batch(const FstOracleCfg* c, const FstOracleWeights* w, const float* h, int B,
+                                 const int32_t* q_lens, const int32_t* pos0, int causal, float* const* caches,
+                                 const int32_t* caps, float* out, FstOracleTrace* trace);
+
 /* Host twin of the paged-cache bookkeeping: a LIFO free list of n_pages pages.
  * Used to check page mapping bit-exactly.  Opaque handle. */
 typedef struct FstOraclePager FstOraclePager;

@@ -98,6 +98,10 @@ def lib() -> C.CDLL:
         L.fst_oracle_mla_forward.argtypes = [cp, C.POINTER(_Weights), fp, C.c_int, C.c_int, C.c_int,
                                              fp, C.c_int, fp, C.POINTER(_Trace)]
         L.fst_oracle_mla_forward.restype = C.c_int
+        i32p = C.POINTER(C.c_int32)
+        L.fst_oracle_mla_forward_batch.argtypes = [cp, C.POINTER(_Weights), fp, C.c_int, i32p, i32p, C.c_int,
+                                                   C.POINTER(fp), i32p, fp, C.POINTER(_Trace)]
+        L.fst_oracle_mla_forward_batch.restype = C.c_int
         for n in ("row_width", "d_qk", "d_v", "low_dim", "threads"):
             getattr(L, "fst_oracle_" + n).argtypes = [cp]
         L.fst_oracle_pager_create.restype = C.c_void_p
@@ -273,6 +277,42 @@ def mla_forward(cfg, weights: dict, h, pos0, cache, causal=False, want_trace=Tru
                                       _p(cache), cache.shape[0], _p(out), C.byref(t))
     if rc != 0:
         raise ValueError("oracle: pos0 + M exceeds the cache capacity")
+    return ForwardResult(out, tr)
+
+
+def mla_forward_batch(cfg, weights: dict, h, q_lens, pos0, caches, causal=False, want_trace=False) -> ForwardResult:
+    """The layer for B sequences in one call: h [sum q_lens, hidden] holds the sequences' rows back to
+    back, caches[b] is sequence b's float32 [cap_b, row] array (updated in place).  Row for row the
+    arithmetic of mla_forward; the projections run over all rows at once."""
+    d = dims(cfg)
+    h = _f(h)
+    q = np.ascontiguousarray(q_lens, np.int32)
+    p0 = np.ascontiguousarray(pos0, np.int32)
+    B, T = len(q), int(q.sum())
+    assert h.shape == (T, cfg.hidden) and len(caches) == B and len(p0) == B
+    for c in caches:
+        assert c.dtype == np.float32 and c.flags.c_contiguous and c.shape[1] == d["row"]
+    caps = np.array([c.shape[0] for c in caches], np.int32)
+    fp = C.POINTER(C.c_float)
+    cptr = (fp * max(B, 1))(*[_p(c) for c in caches])
+    keep = {k: _f(v) for k, v in weights.items() if v is not None}
+    w = _Weights(**{k: _p(v) for k, v in keep.items()})
+    out = np.empty((T, cfg.hidden), np.float32)
+    H = cfg.n_heads
+    tr = {}
+    t = _Trace()
+    if want_trace:
+        tr = {"qc": np.empty((T, cfg.q_lora), np.float32), "kv": np.empty((T, d["row"]), np.float32),
+              "q_eff": np.empty((T * H, d["d_qk"]), np.float32),
+              "o_lat": np.empty((T * H, d["d_v"]), np.float32),
+              "low": np.empty((T, d["low"]), np.float32)}
+        t = _Trace(**{k: _p(v) for k, v in tr.items()})
+    i32p = C.POINTER(C.c_int32)
+    rc = lib().fst_oracle_mla_forward_batch(C.byref(cfg), C.byref(w), _p(h), B, q.ctypes.data_as(i32p),
+                                            p0.ctypes.data_as(i32p), int(causal), cptr, caps.ctypes.data_as(i32p),
+                                            _p(out), C.byref(t))
+    if rc != 0:
+        raise ValueError("oracle: a sequence's pos0 + q_len exceeds its cache capacity")
     return ForwardResult(out, tr)
 
 

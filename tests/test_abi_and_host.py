@@ -109,3 +109,31 @@ def test_engine_library_loads_and_exports_its_entry_points():
         lib.fst_engine_last_error.restype = ctypes.c_char_p
         assert not lib.fst_engine_create(1, 1, 128, 1, 16, 0, 0, 0)
         assert b"no CPU fallback" in lib.fst_engine_last_error()
+
+
+def test_kernel_attributes_are_tracked_per_device():
+    """Function attributes belong to the device that is current when they are set, so the library
+    sets them once per (kernel, device): a second device must be told again, a larger request on
+    the same device too, a repeat must not."""
+    lib = mla.load_library()
+    f = lib.fst_cuda_mla_debug_attr_first_use
+    k1, k2 = 0x7E570001, 0x7E570002  # stand-ins for two kernel addresses
+    assert f(k1, 0, 100_000) == 1
+    assert f(k1, 0, 100_000) == 0      # same kernel, same device: nothing to do
+    assert f(k1, 1, 100_000) == 1      # the second device has not been told yet
+    assert f(k1, 1, 100_000) == 0
+    assert f(k2, 0, 50_000) == 1       # another kernel
+    assert f(k1, 0, 80_000) == 0       # a smaller request is covered
+    assert f(k1, 0, 200_000) == 1      # a larger one is not
+    assert f(k1, 1, 150_000) == 1
+
+
+def test_strong_sharding_covers_the_batch_once():
+    from fastar_b200 import workloads
+    lens = synth.context_lengths(0, 64, 1024, 8192, (0,))
+    for world in (2, 4, 8):
+        shards = parallel.shard_sequences(lens, world)
+        assert sorted(i for s in shards for i in s) == list(range(64))
+    b, q, lo, hi, causal, _ = workloads.shape("verify")
+    assert (b, q, lo, hi, causal) == (32, 16, 16384, 16384, True)
+    assert workloads.shape("batched", batch=8)[0] == 8

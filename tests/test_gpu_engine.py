@@ -202,3 +202,61 @@ def test_weights_loaded_from_a_fst_file(tmp_path):
     finally:
         L.fst_engine_destroy(e)
         L.fst_engine_destroy(e_ref)
+
+
+def test_rope_kind_follows_each_layers_compress_ratio(tmp_path):
+    """build_rope_lut chooses per layer (src/fst_engine.cpp:1979-1982): plain RoPE with the file's
+    rope_freq_base for layers whose compress ratio is 0, YaRN for the others.  A three-layer engine
+    reads ratios {0, 0, 4} (TID 40) and a non-default base from a file written in the converter's
+    other form (wq_a / wq_b and wo_a / wo_b under one tensor id AND sub id 0, found by shape as the
+    engine finds them, 1610-1615); every layer is prefilled in 15-row chunks -- rows 60..74 straddle
+    a page boundary -- and compared with the oracle that uses that layer's RoPE kind."""
+    import struct
+    L = load()
+    L.fst_engine_load_shared_weights.argtypes = [C.c_void_p, C.c_char_p]
+    bits, rounded = weights_for(mla.PRESET_FASTAR_V4)
+    theta = 50000.0
+    tensors = []
+    for l in range(3):
+        tensors += [(5, l, 0, 2, bits["wq_a"]), (5, l, 0, 2, bits["wq_b"]), (6, l, 0, 2, bits["wkv_a"]),
+                    (8, l, 0, 2, bits["wo_a"]), (8, l, 0, 2, bits["wo_b"]), (14, l, 0, 2, bits["q_norm"]),
+                    (15, l, 0, 2, bits["kv_norm"]), (22, l, 0, 3, np.ascontiguousarray(bits["attn_sinks"], np.float32))]
+    tensors.append((40, 0xFFFF, 0, 3, np.array([0.0, 0.0, 4.0], np.float32)))
+    path = str(tmp_path / "three.fst")
+    _write_fst(path, 3, [(t, l, s, q, np.ascontiguousarray(a)) for t, l, s, q, a in tensors])
+    with open(path, "r+b") as f:  # the header's rope_freq_base
+        f.seek(struct.calcsize("<4sIIIIIIIIIIIQf"))
+        f.write(struct.pack("<f", theta))
+    e = L.fst_engine_create(mla.PRESET_FASTAR_V4, 3, 128, 1, 16, 0, mla.IMPL_AUTO, mla.IMPL_AUTO)
+    assert e, L.fst_engine_last_error()
+    try:
+        assert L.fst_engine_load_shared_weights(e, path.encode()) == 0, L.fst_engine_last_error()
+        assert L.fst_engine_preload(e) == 0, L.fst_engine_last_error()
+        cfg = mla.make_config(mla.PRESET_FASTAR_V4)
+        caches = [np.zeros((128, 512), np.float32) for _ in range(3)]
+        ocfgs = []
+        for l in range(3):
+            oc = oracle_cfg(cfg)
+            oc.rope_yarn = 1 if l == 2 else 0
+            oc.rope_theta = theta
+            ocfgs.append(oc)
+        L.fst_engine_set_prefill(e, 1)
+        outs = {}
+        for chunk in range(5):
+            pos = L.fst_engine_seq_pos(e)
+            assert pos == 15 * chunk
+            h = synth.to_bf16_bits(synth.hidden_f32(cfg, 31, 15, (chunk,)))
+            for l in range(3):
+                buf = np.ascontiguousarray(h, np.uint16).copy()
+                rc = L.fst_engine_process_mla(e, l, buf.ctypes.data_as(C.POINTER(C.c_uint16)), 15)
+                assert rc == 0, L.fst_engine_last_error()
+                want = O.mla_forward(ocfgs[l], rounded, synth.from_bf16_bits(h), pos, caches[l], causal=True,
+                                     want_trace=False).out
+                check_close(buf, want, f"chunk {chunk} layer {l}", ulps=2)
+                outs[chunk, l] = buf
+            L.fst_engine_advance(e, 15)
+        # same weights, same rows: the layers differ only by their RoPE kind, and layer 2 must differ
+        assert np.array_equal(outs[4, 0], outs[4, 1])
+        assert not np.array_equal(outs[4, 0], outs[4, 2])
+    finally:
+        L.fst_engine_destroy(e)

@@ -27,20 +27,24 @@ def weights_for(preset, attn_norm=False):
     return _W[key]
 
 
-def run_layer(preset, impl, lens, q_len, causal, seed=0, steps=1, ulps=0, attn_norm=False):
+def run_layer(preset, impl, lens, q_len, causal, seed=0, steps=1, ulps=0, attn_norm=False, rope_yarn=False,
+              yarn_by_layer_call=False):
     """`steps` consecutive layer calls (each appends q_len tokens per sequence); every call is
     compared with the oracle, and so is the cache content afterwards."""
     attn_impl, gemm_impl = impl[1], impl[2]
     B = len(lens)
     n_pages = sum((L + q_len * steps + 63) // 64 for L in lens) + 4
     cfg = mla.make_config(preset, n_pages=n_pages, max_tokens=B * q_len, max_seqs=B, attn_impl=attn_impl,
-                          gemm_impl=gemm_impl)
+                          gemm_impl=gemm_impl, rope_yarn=rope_yarn and not yarn_by_layer_call)
     bits, rounded = weights_for(preset, attn_norm)
     ocfg = oracle_cfg(cfg)
+    ocfg.rope_yarn = int(rope_yarn)
     d = mla.dims_of(cfg)
     H = cfg.n_heads
     with mla.MlaContext(cfg) as ctx:
         ctx.set_layer_weights(0, bits)
+        if yarn_by_layer_call:
+            ctx.set_layer_rope(0, rope_yarn)
         seqs, caches = [], []
         for b, L in enumerate(lens):
             s = ctx.seq_alloc()
@@ -120,6 +124,40 @@ def test_attn_norm_in_front_of_the_layer(impl, preset):
     # before attn_norm and applies it itself; inputs with a row scale far from 1 so that a missing
     # norm cannot pass
     run_layer(preset, impl, [300, 65], 2, True, seed=5, steps=2, ulps=2, attn_norm=True)
+
+
+@pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
+@pytest.mark.parametrize("preset", [mla.PRESET_BASELINE, mla.PRESET_FASTAR_V4], ids=["baseline", "v4"])
+@pytest.mark.parametrize("by_call", [False, True], ids=["config", "per-layer"])
+def test_yarn_rope_tables(impl, preset, by_call):
+    # the YaRN tables of the compressed layers (build_rope_lut, src/fst_engine.cpp:1995-2022) on the
+    # key, the query and (V4) the inverse output rotation: new rows at positions 60..67 and
+    # 4090..4097, both across a page boundary; stages kv and q_eff are compared inside run_layer.
+    # Far positions matter: below a few hundred the YaRN and plain angles of the slow pairs agree
+    # to bf16 precision.
+    run_layer(preset, impl, [60, 4090], 8, True, seed=6, ulps=2, rope_yarn=True, yarn_by_layer_call=by_call)
+
+
+def test_yarn_and_plain_tables_differ_on_the_device():
+    """A context with one plain and one YaRN layer keeps both tables per plan; the same weights and
+    rows give different q_eff / kv in the rope dims only."""
+    cfg = mla.make_config(mla.PRESET_FASTAR_V4, n_pages=80, max_tokens=2, max_seqs=1, n_layers=2)
+    bits, _ = weights_for(mla.PRESET_FASTAR_V4)
+    with mla.MlaContext(cfg) as ctx:
+        ctx.set_layer_weights(0, bits)
+        ctx.set_layer_weights(1, bits)
+        ctx.set_layer_rope(1, True)
+        s = ctx.seq_alloc()
+        rows = synth.to_bf16_bits(synth.cache_rows_f32(cfg, 7, 0, 4000))
+        ctx.cache_write(0, s, 0, rows)
+        ctx.cache_write(1, s, 0, rows)
+        h = synth.to_bf16_bits(synth.hidden_f32(cfg, 7, 2))
+        kv = []
+        for lid in range(2):
+            ctx.forward(lid, h, [s], [4000], [2])
+            kv.append(ctx.get_stage(mla.STAGE_KV).copy())
+        assert np.array_equal(kv[0][:, :448], kv[1][:, :448])      # the nope part does not rotate
+        assert not np.array_equal(kv[0][:, 448:], kv[1][:, 448:])  # the rope tail does, differently
 
 
 def test_plan_is_kept_across_the_layers_of_a_step():

@@ -13,6 +13,7 @@ import pytest
 import torch
 
 from fastar_b200 import mla, synth
+from oracle import oracle as O
 from tests.helpers import check_close
 
 pytestmark = pytest.mark.gpu
@@ -50,6 +51,39 @@ def test_matches_the_regular_entry_point_twice_in_a_row():
         want = synth.from_bf16_bits(regular_path(rows, q))
         # same bar as the other attention tests: cosine >= 0.9999, max-abs <= 2e-2
         check_close(got, want, f"call {call} (L={L})")
+
+
+@pytest.mark.parametrize("heads,d_qk,d_v,n_rows", [(64, 576, 512, 1), (64, 576, 512, 129), (5, 72, 64, 300),
+                                                   (16, 512, 512, 1000), (3, 136, 128, 33)])
+def test_small_and_odd_shapes_against_the_cpu_oracle(heads, d_qk, d_v, n_rows):
+    """Fewer than 64 heads, narrow rows, one row, a ragged second split: each against the oracle's
+    attention on the same bits (rows are d_qk wide with no padding; values are row[:d_v])."""
+    rng = np.random.default_rng(heads * 1000 + n_rows)
+    rows = synth.to_bf16_bits(rng.standard_normal((n_rows, d_qk)).astype(np.float32))
+    q = synth.to_bf16_bits(rng.standard_normal((heads, d_qk)).astype(np.float32))
+    scale = 1.0 / math.sqrt(d_qk)
+    d_rows = torch.from_numpy(rows.view(np.int16)).cuda()
+    d_q = torch.from_numpy(q.view(np.int16)).cuda()
+    d_out = torch.zeros((heads, d_v), dtype=torch.int16, device="cuda")
+    rc = mla.attention_noalloc(d_q.data_ptr(), d_rows.data_ptr(), n_rows, heads, d_qk, d_v, scale, d_out.data_ptr(),
+                               torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, mla.load_library().fst_cuda_mla_last_error()
+    torch.cuda.synchronize()
+    # the oracle with this geometry: V4 form (row == d_qk, values = row[:kv_lora]) without a sink
+    ocfg = O.make_cfg(O.PRESET_FASTAR_V4, n_heads=heads, kv_lora=d_qk, use_sink=False, softmax_scale=scale)
+    want = O.attention(ocfg, synth.from_bf16_bits(q), synth.from_bf16_bits(rows), n_rows, 1)[:, :d_v]
+    check_close(d_out.cpu().numpy().view(np.uint16), want, f"H={heads} d_qk={d_qk} d_v={d_v} rows={n_rows}", ulps=2)
+
+
+def test_refusals_reach_the_last_error_string():
+    d = torch.zeros(64 * 576, dtype=torch.int16, device="cuda")
+    p = d.data_ptr()
+    lib = mla.load_library()
+    assert mla.attention_noalloc(p, p, 70000, 64, 576, 512, 0.07, p) == mla.ERR_CAPACITY
+    assert b"65536 cached rows" in lib.fst_cuda_mla_last_error()
+    assert mla.attention_noalloc(p, p, 64, 64, 576, 512, float("nan"), p) == mla.ERR_ARG
+    assert b"softmax_scale" in lib.fst_cuda_mla_last_error()
+    assert mla.attention_noalloc(p, p, 64, 64, 576, 512, float("inf"), p) == mla.ERR_ARG
 
 
 def test_sizes_beyond_the_fixed_array_are_refused():
