@@ -47,6 +47,7 @@ def parse():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--cpu-seqs", type=int, default=8, help="sequences in the bounded CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--merge-kernel", action="store_true", help="merge the split-KV partials in a kernel of its own")
     return ap.parse_args()
 
 
@@ -239,6 +240,8 @@ def main():
                           attn_impl=a.attn_impl, gemm_impl=a.gemm_impl)
     ctx = mla.MlaContext(cfg)
     ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+    if a.merge_kernel:
+        ctx.set_fused_merge(False)
     ctx.set_layer_weights(0, synth.weights_to_bits(synth.layer_weights_f32(cfg, a.seed, 0)))
     # scramble the free list so that the block tables are a random page permutation
     rng = synth.rng_for(a.seed, "perm", rank)

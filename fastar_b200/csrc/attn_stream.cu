@@ -47,12 +47,29 @@ constexpr uint32_t COL_Q = 0, COL_S = 288, COL_O = 0;
 constexpr uint32_t LANE16 = 16u << 16;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
-// Shared memory: a ring of three tile frames (NCH chunk slots each), P (also the staging area of
-// the epilogue), barriers and small arrays.
+// Shared memory: a ring of three tile frames (NCH chunk slots each); with eight chunks per tile
+// three P buffers behind it (with nine, P lives in the frame's ninth chunk, see below); the
+// staging area of the epilogue; barriers and small arrays.  227 KB either way.
+//
+// Where P lives.  The probabilities of a tile (64 heads x 64 tokens bf16, 8 KB) are the A operand
+// of its SV MMAs.  Every tile has a P buffer of its own, with the life of its ring frame: for
+// 576-wide rows it is the frame's ninth chunk -- the 64 rope dims, which only the QK MMAs read
+// and which are dead once the tile's scores are complete; for 512-wide rows (eight chunks per
+// tile, 24 KB of shared memory to spare) three buffers behind the ring.  So the softmax of the
+// next tile stores its result without waiting for the SV MMAs of this one (with one shared P
+// buffer it had to); it waits for them only in the rare case that it rescales O.  Worth 1.3 us
+// of 85 on the batched-decode workload: the kernel is not bound by that dependency.
 constexpr int MISC_BYTES = 2048;
-__host__ __device__ constexpr int off_p(int nch) { return 3 * nch * CHUNK; }
-__host__ __device__ constexpr int off_misc(int nch) { return off_p(nch) + P_BYTES; }
+constexpr int STAGE_BYTES = 8192;
+__host__ __device__ constexpr int off_pbuf(int nch) { return 3 * nch * CHUNK; }
+__host__ __device__ constexpr int off_stage(int nch) { return 3 * nch * CHUNK + (nch == 9 ? 0 : 3 * P_BYTES); }
+__host__ __device__ constexpr int off_misc(int nch) { return off_stage(nch) + STAGE_BYTES; }
 __host__ __device__ constexpr int smem_total(int nch) { return off_misc(nch) + MISC_BYTES + 1024; }
+// byte offset (from the ring base) of the P buffer of the tile in ring slot g
+template <int NCH>
+__device__ __forceinline__ int p_slot_off(int g) {
+  return NCH == 9 ? ((g % 3) * NCH + 8) * CHUNK : off_pbuf(NCH) + (g % 3) * P_BYTES;
+}
 
 struct StreamParams {
   const bf16* q_eff;
@@ -67,6 +84,15 @@ struct StreamParams {
   int* d_status;
   int d_qk;
   float scale_log2;
+  // direct != 0: a token whose whole context is one segment (one partial) is finished here --
+  // normalised, rounded, (V4) inverse-rotated and written to o_lat -- and leaves no partial; the
+  // merge kernel then skips it (see finish_token below)
+  int direct;
+  const int32_t* tok_part;  // [T + 1] partial slots of every token
+  bf16* o_lat;              // [T * 64, 512]
+  const float* sinks;       // [64] or null
+  const float* lut;         // [T, rope] (cos, sin): inverse RoPE of the output tail when inv_rope
+  int rope, inv_rope;
 };
 
 
@@ -76,7 +102,7 @@ struct StreamMisc {
   uint64_t q_ready;      // Q_eff of a segment written to tensor memory by the softmax threads
   uint64_t s_full[2];    // both score partials of tile g are complete: barrier g & 1 (two commits)
   uint64_t s_free[3];    // the softmax threads have read the partial in this score buffer
-  uint64_t p_full;       // the probabilities of a tile are written
+  uint64_t p_full[3];    // the probabilities of tile n are written: barrier n % 3
   uint32_t tmem_slot;
   int abort_flag;
   float pmax[2][2][HEADS];  // [tile parity][token half][head]: row maxima of the two warps of a quadrant
@@ -180,6 +206,54 @@ struct TileCursor {
   }
 };
 
+// A token whose whole context was one segment needs no merge: its output row goes from tensor
+// memory straight to o_lat, with the arithmetic the merge kernels apply to a single part --
+// out = e^{m - M} O / (e^{m - M} l [+ e^{sink - M}] + 1e-12) with M = max(m, sink), rounded to bf16,
+// then (V4) the inverse RoPE of the output tail (reference src/fst_engine.cpp:3623, 3636, 3646,
+// 3716).  Run by the eight softmax warps; a thread owns 32 columns of one head (the 16-lane
+// tensor-memory access shape).
+__device__ __forceinline__ void finish_token(const StreamParams& p, int tok, int row, int half, int sub,
+                                             uint32_t lane_addr, float m_ln, float l_row) {
+  const bool sk = p.sinks != nullptr;
+  const float M = sk ? fmaxf(p.sinks[row], m_ln) : m_ln;
+  const float w = m_ln == -INFINITY ? 0.0f : expf(m_ln - M);
+  float den = sk ? expf(p.sinks[row] - M) : 0.0f;
+  if (m_ln != -INFINITY) den += w * l_row;
+  const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
+  const float* lut = p.lut + (long long)tok * p.rope;
+  bf16* o_row = p.o_lat + ((long long)tok * HEADS + row) * D_V;
+#pragma unroll 1
+  for (int cc = 0; cc < 4; ++cc) {
+    const int col0 = half * 256 + cc * 64 + sub * 32;
+    float o[32];
+    tmem_ld16x64(lane_addr + LANE16 + COL_O + half * 256 + cc * 64, o);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[j] = rbf(fmaf(w, o[j], 0.0f) * inv);
+    if (p.inv_rope && col0 + 32 > D_V - p.rope) {
+      // inverse RoPE of the rounded output tail: pairs (2i, 2i+1) sit in one thread
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const int pr = col0 + j - (D_V - p.rope);
+        if (pr >= 0) {
+          const float c = lut[pr], sn = -lut[pr + 1], x0 = o[j], x1 = o[j + 1];
+          o[j] = x0 * c - x1 * sn;
+          o[j + 1] = x0 * sn + x1 * c;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      uint32_t pk[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(o[8 * u + 2 * e], o[8 * u + 2 * e + 1]);
+        pk[e] = *reinterpret_cast<uint32_t*>(&b2);
+      }
+      *reinterpret_cast<uint4*>(o_row + col0 + 8 * u) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+  }
+}
+
 // The QK MMAs of chunks [C0, C1) of tile g: S_partial = Q[:, chunks] * K[:, chunks]^T.  Chunks land
 // in groups of three, each group with a barrier.
 template <int C0, int C1>
@@ -202,13 +276,16 @@ __device__ __forceinline__ bool qk_chunks(StreamMisc* mi, int g, uint32_t d, uin
 }
 
 // 14 warps are allocated as 16 (granularity four): 128 registers per thread
-template <int NCH>
+// DIRECT: tokens with a single partial are finished here (finish_token); the variant without it is
+// the one batched decode runs, where every token is split (the mere presence of that code in the
+// kernel costs 2-3 us of 85 there, measured).
+template <int NCH, bool DIRECT>
 __global__ void __launch_bounds__(ST_THREADS, 1)
 k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ CUtensorMap tmQ, StreamParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* s_ring = smem;
-  unsigned char* s_p = smem + off_p(NCH);
+  unsigned char* s_stage = smem + off_stage(NCH);
   StreamMisc* mi = reinterpret_cast<StreamMisc*>(smem + off_misc(NCH));
   volatile int* abort_flag = &mi->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -222,7 +299,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
     tc::mbar_init(&mi->q_ready, 256);
     for (int i = 0; i < 2; ++i) tc::mbar_init(&mi->s_full[i], 2);
     for (int i = 0; i < 3; ++i) tc::mbar_init(&mi->s_free[i], 256);
-    tc::mbar_init(&mi->p_full, 256);
+    for (int i = 0; i < 3; ++i) tc::mbar_init(&mi->p_full[i], 256);
     mi->abort_flag = 0;
     tc::fence_barrier_init();
   }
@@ -311,17 +388,17 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
     if (lane == 0) {
       const uint64_t k_major = tc::umma_desc_sw128(0, 16, 1024);
       const uint64_t v_desc = tc::umma_desc_sw128(0, CHUNK, 1024);  // MN-major: 64-column groups one slot apart
-      const uint32_t ring16 = (tc::smem_u32(s_ring) & 0x3FFFFu) >> 4, p16 = (tc::smem_u32(s_p) & 0x3FFFFu) >> 4;
+      const uint32_t ring16 = (tc::smem_u32(s_ring) & 0x3FFFFu) >> 4;
       constexpr uint32_t id256 = tc::umma_idesc_bf16(HEADS, 256, 0, 1);
       TileCursor cur;
       cur.init(p.segs, seg0, seg1);
       bool ok = true;
       while (!cur.done() && ok) {
         const int g = cur.g;
-        ok = tc::mbar_wait(&mi->p_full, cur.n & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
+        ok = tc::mbar_wait(&mi->p_full[cur.n % 3], (cur.n / 3) & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
         if (!ok) break;
         tc::tc_fence_after();
-        const uint64_t da = k_major | (uint64_t)p16;
+        const uint64_t da = k_major | (uint64_t)(ring16 + (p_slot_off<NCH>(g) >> 4));
         const uint32_t acc0 = cur.t > 0 ? 1u : 0u;
 #pragma unroll
         for (int nh = 0; nh < 2; ++nh) {
@@ -347,7 +424,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
     // epilogue staging: half of the P rows of this quadrant (what the two warps of the quadrant
     // write during the softmax, so the quadrant barrier orders the two uses)
-    unsigned char* stage = s_p + quad * 2048 + half * 1024;
+    unsigned char* stage = s_stage + quad * 2048 + half * 1024;
     // The Q_eff block in ring slot gq -> tensor memory (bf16 pairs, two dims per column).  The block
     // came through the ring like a tile, ahead of the segment's first tile, so it does not queue
     // behind the tiles in flight as loads by these threads would.  Every QK MMA of the previous
@@ -444,16 +521,23 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
         l = l * alpha + sum;
         // P (and O, if it is rescaled below) belong to the SV MMAs of the previous tile until they
         // retire (before a segment's first tile the epilogue has waited for them already)
-        if (t > 0) ok = tc::mbar_wait(&mi->o_done[(g - 1) & 3], ((g - 1) >> 2) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
         {
-          // P[row, tokens 32*half + 16*sub .. +15]: two 16-byte units of the row, 128-byte swizzle
-          unsigned char* prow = s_p + row * 128;
+          // P[row, tokens 32*half + 16*sub .. +15]: two 16-byte units of the row, 128-byte swizzle.
+          // The tile's own P buffer is free: with nine chunks it is the frame's rope chunk, which
+          // the QK MMAs of this tile (retired: s_full) were the last to read; with eight it was last
+          // read by the SV MMAs of the tile three slots back, which retired before this frame was
+          // filled.
+          unsigned char* prow = s_ring + p_slot_off<NCH>(g) + row * 128;
           const int u0 = half * 4 + sub * 2;
           *reinterpret_cast<uint4*>(prow + (((u0) ^ (row & 7)) * 16)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
           *reinterpret_cast<uint4*>(prow + (((u0 + 1) ^ (row & 7)) * 16)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
         }
         // O rows are scaled by their own alpha through the 16-lane access shape at lane offset 16
+        // (O belongs to the SV MMAs of the previous tile until they retire: only this path waits)
         if (t > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+          ok = tc::mbar_wait(&mi->o_done[(g - 1) & 3], ((g - 1) >> 2) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
+          ok = __all_sync(0xffffffffu, ok);  // (the tensor-memory accesses below are warp-collective)
+          if (!ok) break;
           tc::tc_fence_after();
 #pragma unroll 1
           for (int cc = 0; cc < 4; ++cc) {
@@ -468,7 +552,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
         }
         tc::fence_proxy_async();
         tc::tc_fence_before();
-        tc::mbar_arrive(&mi->p_full);
+        tc::mbar_arrive(&mi->p_full[n % 3]);
       }
       if (!ok) break;
       // Q_eff of the next segment goes in first, so that its QK MMAs run during the epilogue
@@ -481,60 +565,65 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
       if (sub == 0) mi->lsum[half][row] = l;
       ok = quad_bar_and(quad, ok);
       if (!ok) break;
-      if (half == 0 && sub == 0) {
-        p.part_l[(long long)sg.part * HEADS + row] = mi->lsum[0][row] + mi->lsum[1][row];
-        p.part_m[(long long)sg.part * HEADS + row] = m_used * 0.6931471805599453f;  // back to ln units
-      }
-      {
-        // A 32-lane load hands lanes 16-31 the O rows of this quadrant (row lane-16), 32 columns
-        // at a time; this warp owns columns 256*half .. +255.  The rows go through shared memory
-        // so that every store instruction writes four full 128-byte lines.
-        float* po = p.part_o + ((long long)sg.part * HEADS + quad * 16) * D_V + half * 256;
-        if (cur.done()) {
-          // The CTA's last segment: every tile has retired, so the ring is idle and each warp
-          // stages its whole 16 x 256 block there (16 KB) -- all tensor-memory loads first, one
-          // warp barrier, then the stores back to back instead of 16 small round trips.
-          unsigned char* big = s_ring + (warp - 2) * 16384;
+      if (DIRECT && p.tok_part[sg.tok + 1] - p.tok_part[sg.tok] == 1) {
+        finish_token(p, sg.tok, row, half, sub, lane_addr, m_used * 0.6931471805599453f,
+                     mi->lsum[0][row] + mi->lsum[1][row]);
+      } else {
+        if (half == 0 && sub == 0) {
+          p.part_l[(long long)sg.part * HEADS + row] = mi->lsum[0][row] + mi->lsum[1][row];
+          p.part_m[(long long)sg.part * HEADS + row] = m_used * 0.6931471805599453f;  // back to ln units
+        }
+        {
+          // A 32-lane load hands lanes 16-31 the O rows of this quadrant (row lane-16), 32 columns
+          // at a time; this warp owns columns 256*half .. +255.  The rows go through shared memory
+          // so that every store instruction writes four full 128-byte lines.
+          float* po = p.part_o + ((long long)sg.part * HEADS + quad * 16) * D_V + half * 256;
+          if (cur.done()) {
+            // The CTA's last segment: every tile has retired, so the ring is idle and each warp
+            // stages its whole 16 x 256 block there (16 KB) -- all tensor-memory loads first, one
+            // warp barrier, then the stores back to back instead of 16 small round trips.
+            unsigned char* big = s_ring + (warp - 2) * 16384;
 #pragma unroll 1
-          for (int cc = 0; cc < 8; ++cc) {
-            float o[32];
-            tc::tmem_ld32(lane_addr + COL_O + half * 256 + cc * 32, o);
-            if (sub == 1) {
-              const int rr = lane - 16;
-#pragma unroll
-              for (int u = 0; u < 8; ++u)
-                *reinterpret_cast<float4*>(big + cc * 2048 + rr * 128 + ((u ^ (rr & 7)) * 16)) =
-                    make_float4(o[u * 4], o[u * 4 + 1], o[u * 4 + 2], o[u * 4 + 3]);
-            }
-          }
-          __syncwarp();
-#pragma unroll 4
-          for (int i = 0; i < 32; ++i) {
-            const int cc = i >> 2, rr = (i & 3) * 4 + (lane >> 3), u = lane & 7;
-            const float4 v = *reinterpret_cast<const float4*>(big + cc * 2048 + rr * 128 + ((u ^ (rr & 7)) * 16));
-            *reinterpret_cast<float4*>(po + (long long)rr * D_V + cc * 32 + u * 4) = v;
-          }
-        } else {
-#pragma unroll 1
-          for (int cc = 0; cc < 8; ++cc) {
-            float o[32];
-            tc::tmem_ld32(lane_addr + COL_O + half * 256 + cc * 32, o);
-#pragma unroll
-            for (int h8 = 0; h8 < 2; ++h8) {  // eight rows at a time through the 1 KB staging area
-              if (sub == 1 && ((lane >> 3) & 1) == h8) {
-                const int rr = lane & 7;
+            for (int cc = 0; cc < 8; ++cc) {
+              float o[32];
+              tc::tmem_ld32(lane_addr + COL_O + half * 256 + cc * 32, o);
+              if (sub == 1) {
+                const int rr = lane - 16;
 #pragma unroll
                 for (int u = 0; u < 8; ++u)
-                  *reinterpret_cast<float4*>(stage + rr * 128 + ((u ^ rr) * 16)) = make_float4(o[u * 4], o[u * 4 + 1], o[u * 4 + 2], o[u * 4 + 3]);
+                  *reinterpret_cast<float4*>(big + cc * 2048 + rr * 128 + ((u ^ (rr & 7)) * 16)) =
+                      make_float4(o[u * 4], o[u * 4 + 1], o[u * 4 + 2], o[u * 4 + 3]);
               }
-              __syncwarp();
+            }
+            __syncwarp();
+#pragma unroll 4
+            for (int i = 0; i < 32; ++i) {
+              const int cc = i >> 2, rr = (i & 3) * 4 + (lane >> 3), u = lane & 7;
+              const float4 v = *reinterpret_cast<const float4*>(big + cc * 2048 + rr * 128 + ((u ^ (rr & 7)) * 16));
+              *reinterpret_cast<float4*>(po + (long long)rr * D_V + cc * 32 + u * 4) = v;
+            }
+          } else {
+#pragma unroll 1
+            for (int cc = 0; cc < 8; ++cc) {
+              float o[32];
+              tc::tmem_ld32(lane_addr + COL_O + half * 256 + cc * 32, o);
 #pragma unroll
-              for (int i = 0; i < 2; ++i) {
-                const int rr = i * 4 + (lane >> 3), u = lane & 7;
-                const float4 v = *reinterpret_cast<const float4*>(stage + rr * 128 + ((u ^ rr) * 16));
-                *reinterpret_cast<float4*>(po + (long long)(h8 * 8 + rr) * D_V + cc * 32 + u * 4) = v;
+              for (int h8 = 0; h8 < 2; ++h8) {  // eight rows at a time through the 1 KB staging area
+                if (sub == 1 && ((lane >> 3) & 1) == h8) {
+                  const int rr = lane & 7;
+#pragma unroll
+                  for (int u = 0; u < 8; ++u)
+                    *reinterpret_cast<float4*>(stage + rr * 128 + ((u ^ rr) * 16)) = make_float4(o[u * 4], o[u * 4 + 1], o[u * 4 + 2], o[u * 4 + 3]);
+                }
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                  const int rr = i * 4 + (lane >> 3), u = lane & 7;
+                  const float4 v = *reinterpret_cast<const float4*>(stage + rr * 128 + ((u ^ rr) * 16));
+                  *reinterpret_cast<float4*>(po + (long long)(h8 * 8 + rr) * D_V + cc * 32 + u * 4) = v;
+                }
+                __syncwarp();
               }
-              __syncwarp();
             }
           }
         }
@@ -567,7 +656,7 @@ bool attn_stream_supported(const AttnArgs& a) {
 
 cudaError_t launch_attn_stream(const AttnArgs& a, cudaStream_t st) {
   static_assert(sizeof(StreamMisc) <= MISC_BYTES, "misc region too small");
-  static_assert(smem_total(9) <= 227 * 1024, "shared memory budget");
+  static_assert(smem_total(9) <= 227 * 1024 && smem_total(8) <= 227 * 1024, "shared memory budget");
   static_assert(COL_S + 3 * TILE <= TMEM_COLS, "tensor memory budget");
   if (a.n_segs <= 0) return cudaSuccess;
   CUtensorMap tmKV;
@@ -586,8 +675,15 @@ cudaError_t launch_attn_stream(const AttnArgs& a, cudaStream_t st) {
   p.pool = a.pool;
   p.d_qk = a.d_qk;
   p.scale_log2 = a.scale * 1.4426950408889634f;
-  if (a.d_qk == 576) return launch_pdl(k_attn_stream<9>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(9), st, 1, tmKV, tmQ, p);
-  return launch_pdl(k_attn_stream<8>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(8), st, 1, tmKV, tmQ, p);
+  p.direct = a.direct_single ? 1 : 0;
+  p.tok_part = a.tok_part; p.o_lat = a.o_lat; p.sinks = a.sinks; p.lut = a.lut;
+  p.rope = a.rope; p.inv_rope = a.inv_rope;
+  if (a.d_qk == 576) {
+    if (p.direct) return launch_pdl(k_attn_stream<9, true>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(9), st, 1, tmKV, tmQ, p);
+    return launch_pdl(k_attn_stream<9, false>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(9), st, 1, tmKV, tmQ, p);
+  }
+  if (p.direct) return launch_pdl(k_attn_stream<8, true>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(8), st, 1, tmKV, tmQ, p);
+  return launch_pdl(k_attn_stream<8, false>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(8), st, 1, tmKV, tmQ, p);
 }
 
 }  // namespace fst

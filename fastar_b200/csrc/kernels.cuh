@@ -151,6 +151,15 @@ struct AttnArgs {
   long long q_rows;         // rows of q_eff (new tokens * H)
   long long pool_rows;      // n_pages * page_tokens
   float scale;
+  // tcgen05 kernel only: a token whose whole context is ONE segment of the schedule (one partial)
+  // is normalised and written to o_lat by the attention kernel itself and leaves no partial; the
+  // merge kernel that follows is told to skip such tokens (MergeArgs::skip_single).
+  bool direct_single = false;
+  const int32_t* tok_part = nullptr;  // [T + 1]
+  bf16* o_lat = nullptr;              // [T * H, d_v]
+  const float* sinks = nullptr;       // [H] or null
+  const float* lut = nullptr;         // [T, rope]
+  int rope = 0, inv_rope = 0;
 };
 void launch_attn_simt(const AttnArgs& a, cudaStream_t st);
 // tcgen05 kernel: a stream of 64-token tiles, Q_eff in tensor memory, ring of three tile frames.
@@ -169,6 +178,7 @@ struct MergeArgs {
   float* rank_partial;      // [T * H, 2 + d_v] fp32        (mode 1, no sink)
   int T, H, d_v, rope, inv_rope, mode;
   int threads;              // 128: rows have few parts (a thread per 4 columns); otherwise 256 (8 warps share the parts)
+  int skip_single = 0;      // rows of tokens with exactly one partial are already in o_lat (AttnArgs::direct_single)
 };
 void launch_merge(const MergeArgs& a, cudaStream_t st);
 

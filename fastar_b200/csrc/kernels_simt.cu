@@ -548,6 +548,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge(MergeArgs a) {
   __shared__ float s_red[32];
   const int r = blockIdx.x, t = r / a.H, h = r % a.H;
   const int p0 = a.tok_part[t], n_parts = a.tok_part[t + 1] - p0;
+  if (a.skip_single && n_parts == 1) return;  // finished by the attention kernel
   auto get = [&](int p) {
     const long long i = (long long)(p0 + p) * a.H + h;
     return PartRef{a.part_m[i], a.part_l[i], a.part_o + i * a.d_v};
@@ -579,6 +580,7 @@ __global__ void __launch_bounds__(256) k_merge_rows(MergeArgs a) {
   if (r < a.T * a.H) {
     const int t = r / a.H, h = r % a.H;
     const int p0 = a.tok_part[t], n_parts = a.tok_part[t + 1] - p0;
+    if (a.skip_single && n_parts == 1) return;  // finished by the attention kernel
     const bool sk = a.sinks != nullptr;
     float M = sk ? a.sinks[h] : -INFINITY;
     for (int p = 0; p < n_parts; ++p) M = fmaxf(M, a.part_m[(long long)(p0 + p) * a.H + h]);

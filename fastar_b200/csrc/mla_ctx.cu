@@ -91,6 +91,9 @@ struct FstMlaCtx {
   bf16 *d_qeff = nullptr, *d_olat = nullptr, *d_low = nullptr, *d_out = nullptr;
   float *d_part_m = nullptr, *d_part_l = nullptr, *d_part_o = nullptr;
   int max_parts = 0;
+  bool fused_merge = true;       // the attention kernel finishes single-partial tokens itself
+  int max_tok_parts = 0, min_tok_parts = 0;  // most / fewest partials of one token in the current plan
+  int n_single_part = 0;                     // tokens of the current plan with exactly one partial
   uint16_t* h_pinned = nullptr;  // [max_tokens, hidden] staging for the host-buffer entry point
   int* d_status = nullptr;
   const bf16* out_src = nullptr;  // where the last layer call left its output rows
@@ -333,7 +336,7 @@ GemmArgs plain_gemm(const bf16* A, const bf16* B, bf16* C, int M, int N, int K) 
   return g;
 }
 
-AttnArgs attn_args(FstMlaCtx* c, int lid, const bf16* q_eff) {
+AttnArgs attn_args(FstMlaCtx* c, int lid, const bf16* q_eff, bool may_fuse = false) {
   AttnArgs a;
   a.q_eff = q_eff;
   a.pool = c->pools[lid];
@@ -355,13 +358,27 @@ AttnArgs attn_args(FstMlaCtx* c, int lid, const bf16* q_eff) {
   a.pool_rows = (long long)c->cfg.n_pages * c->cfg.page_tokens;
   a.q_rows = (long long)c->T * c->d.H;
   a.scale = c->cfg.softmax_scale;
+  if (may_fuse && c->fused_merge && c->n_single_part > 0) {
+    a.direct_single = true;
+    a.tok_part = c->d_tok_part;
+    a.o_lat = c->d_olat;
+    a.sinks = c->d.v4 ? c->layers[lid].sinks : nullptr;
+    a.lut = lut_of(c, lid);
+    a.rope = c->d.rope;
+    a.inv_rope = c->d.v4 ? 1 : 0;
+  }
   return a;
 }
 
-int run_attention(FstMlaCtx* c, int lid, const bf16* q_eff) {
+// *direct (if given; mode-0 callers): the attention kernel has written the o_lat rows of every
+// token that has exactly one partial; the merge that follows skips them.
+int run_attention(FstMlaCtx* c, int lid, const bf16* q_eff, bool* direct = nullptr) {
+  if (direct) *direct = false;
   if (c->n_segs == 0) return FST_MLA_OK;
-  AttnArgs a = attn_args(c, lid, q_eff);
+  AttnArgs a = attn_args(c, lid, q_eff, direct != nullptr);
   const bool tc_ok = attn_stream_supported(a);
+  if (!(c->cfg.attn_impl != FST_MLA_IMPL_SIMT && tc_ok)) a.direct_single = false;
+  if (direct) *direct = a.direct_single;
   if (c->cfg.attn_impl == FST_MLA_IMPL_TENSOR && !tc_ok)
     return fail(FST_MLA_ERR_ARG, "this shape has no tcgen05 attention path");
   if (c->cfg.attn_impl != FST_MLA_IMPL_SIMT && tc_ok) {
@@ -460,9 +477,14 @@ int run_back(FstMlaCtx* c, int lid, bf16* h_out) {
   return FST_MLA_OK;
 }
 
-int run_merge_local(FstMlaCtx* c, int lid, int mode, float* rank_partial) {
+// skip_single: the attention kernel finished the single-partial tokens; when every token with a
+// context is one, nothing is left to merge (tokens without any context still get their zero /
+// sink-only rows from the merge kernel).
+int run_merge_local(FstMlaCtx* c, int lid, int mode, float* rank_partial, bool skip_single = false) {
   const Dims& d = c->d;
+  if (skip_single && c->min_tok_parts == 1 && c->max_tok_parts == 1) return FST_MLA_OK;
   MergeArgs m;
+  m.skip_single = skip_single ? 1 : 0;
   m.part_m = c->d_part_m; m.part_l = c->d_part_l; m.part_o = c->d_part_o; m.tok_part = c->d_tok_part;
   m.sinks = (d.v4 && mode == 0) ? c->layers[lid].sinks : nullptr;
   m.lut = lut_of(c, lid); m.o_lat = c->d_olat; m.rank_partial = rank_partial;
@@ -1087,6 +1109,14 @@ int plan_schedule_part(FstMlaCtx* c, bool on_copy_stream) {
     CU(cudaMemcpyAsync(c->d_plan + from, c->h_plan + from, off - from, cudaMemcpyHostToDevice, c->stream));
     CU(cudaEventRecord(c->plan_ev, c->stream));
   }
+  c->max_tok_parts = 0;
+  c->n_single_part = 0;
+  c->min_tok_parts = T > 0 ? (1 << 30) : 0;
+  for (int i = 0; i < T; ++i) {
+    c->max_tok_parts = std::max(c->max_tok_parts, tok_part[i + 1] - tok_part[i]);
+    c->min_tok_parts = std::min(c->min_tok_parts, tok_part[i + 1] - tok_part[i]);
+    c->n_single_part += tok_part[i + 1] - tok_part[i] == 1;
+  }
   c->n_segs = (int)segs.size();
   c->n_parts = (int)segs.size();
   c->n_ctas = n_ctas;
@@ -1112,6 +1142,12 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
 int fst_cuda_mla_set_plan_reuse(FstMlaCtx* c, int32_t on) {
   if (!c) return fail(FST_MLA_ERR_ARG, "null context");
   c->plan_reuse = on != 0;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_set_fused_merge(FstMlaCtx* c, int32_t on) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  c->fused_merge = on != 0;
   return FST_MLA_OK;
 }
 
@@ -1155,9 +1191,10 @@ int fst_cuda_mla_run_device(FstMlaCtx* c, int lid, const void* d_h_in, void* d_h
   if ((rc = prof_begin(c))) return rc;
   if ((rc = run_front(c, lid, (const bf16*)d_h_in))) return rc;
   prof_mark(c, FST_MLA_K_ATTN);
-  if ((rc = run_attention(c, lid, c->d_qeff))) return rc;
+  bool direct = false;
+  if ((rc = run_attention(c, lid, c->d_qeff, &direct))) return rc;
   prof_mark(c, FST_MLA_K_MERGE);
-  if ((rc = run_merge_local(c, lid, 0, nullptr))) return rc;
+  if ((rc = run_merge_local(c, lid, 0, nullptr, direct))) return rc;
   if ((rc = run_back(c, lid, (bf16*)d_h_out))) return rc;
   c->cur = nullptr;
   CU(cudaGetLastError());
@@ -1228,8 +1265,9 @@ int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* 
   if (two_parts) {
     if ((rc = run_front(c, lid, c->d_h))) return rc;
     if ((rc = plan_schedule_part(c, true))) return rc;
-    if ((rc = run_attention(c, lid, c->d_qeff))) return rc;
-    if ((rc = run_merge_local(c, lid, 0, nullptr))) return rc;
+    bool direct = false;
+    if ((rc = run_attention(c, lid, c->d_qeff, &direct))) return rc;
+    if ((rc = run_merge_local(c, lid, 0, nullptr, direct))) return rc;
     if ((rc = run_back(c, lid, (bf16*)out_dev))) return rc;
     CU(cudaGetLastError());
   } else if ((rc = fst_cuda_mla_run_device(c, lid, c->d_h, out_dev))) {
@@ -1258,9 +1296,10 @@ int fst_cuda_mla_attention_only(FstMlaCtx* c, int lid, const uint16_t* q_eff, ui
   CU(cudaMemcpyAsync(c->d_qeff, q_eff, (size_t)c->T * d.H * d.d_qk * 2, cudaMemcpyHostToDevice, c->stream));
   if ((rc = prof_begin(c))) return rc;
   prof_mark(c, FST_MLA_K_ATTN);
-  if ((rc = run_attention(c, lid, c->d_qeff))) return rc;
+  bool direct = false;
+  if ((rc = run_attention(c, lid, c->d_qeff, &direct))) return rc;
   prof_mark(c, FST_MLA_K_MERGE);
-  if ((rc = run_merge_local(c, lid, 0, nullptr))) return rc;
+  if ((rc = run_merge_local(c, lid, 0, nullptr, direct))) return rc;
   prof_mark(c, FST_MLA_K_OPROJ_A);
   c->cur = nullptr;
   CU(cudaMemcpyAsync(o_lat, c->d_olat, (size_t)c->T * d.H * d.d_v * 2, cudaMemcpyDeviceToHost, c->stream));

@@ -193,6 +193,12 @@ int fst_cuda_mla_plan(FstMlaCtx* ctx, const FstMlaSeqStep* steps, int32_t n_seqs
  * between) returns at once and keeps the tables that are on the device: that is what layers
  * 2 .. L of a step see, also through fst_cuda_mla_forward.  on = 0 rebuilds every time. */
 int fst_cuda_mla_set_plan_reuse(FstMlaCtx* ctx, int32_t on);
+/* A query token whose whole context the split-KV schedule gives to ONE thread block needs no
+ * merge: the attention kernel normalises, rounds and writes its output rows itself, no partial
+ * goes to memory, and the merge kernel skips the token (and is not launched when every token is
+ * such a token: verify blocks and prefill chunks mostly are).  on = 0: every token goes through
+ * its partial and the merge kernel.  Both give the same bits.  Default: on. */
+int fst_cuda_mla_set_fused_merge(FstMlaCtx* ctx, int32_t on);
 /* Sliding window that fst_cuda_mla_forward applies to every sequence of its calls (0: none). */
 int fst_cuda_mla_set_window(FstMlaCtx* ctx, int32_t window);
 /* Plans built and plan requests answered by the valid plan, since the context was created. */

@@ -264,3 +264,40 @@ def test_forward_with_a_window_set_on_the_context():
         assert not np.array_equal(out_w[0], out_full[0])      # 301 rows against the last 100
         # 65 rows: the window covers them all (the split into partials differs, so not bit for bit)
         check_close(out_w[1:2], synth.from_bf16_bits(out_full[1:2]), "window covers the context")
+
+
+@pytest.mark.parametrize("preset", [mla.PRESET_BASELINE, mla.PRESET_FASTAR_V4], ids=["baseline", "v4"])
+@pytest.mark.parametrize("n_seqs", [45, 150], ids=["mostly-split", "mostly-whole"])
+def test_tokens_finished_by_the_attention_kernel_equal_the_merge_kernel(preset, n_seqs):
+    """A token whose whole context is one segment of the split-KV schedule is normalised and written
+    by the attention kernel itself; with the switch off it goes through its partial and the merge
+    kernel like the split ones.  Same bits either way (o_lat and the layer output), run after run,
+    with the sink and the inverse RoPE of the V4 form, empty contexts included."""
+    rng = np.random.default_rng(5)
+    hi = 2600 if n_seqs < 100 else 400
+    lens = [int(x) for x in rng.integers(40, hi, size=n_seqs - 5)] + [0, 1, 63, 64, 65]
+    B, q = len(lens), 2
+    cfg = mla.make_config(preset, n_pages=sum((L + q + 63) // 64 for L in lens) + 4, max_tokens=B * q, max_seqs=B)
+    bits, _ = weights_for(preset)
+    with mla.MlaContext(cfg) as ctx:
+        ctx.set_layer_weights(0, bits)
+        seqs = []
+        for b, L in enumerate(lens):
+            s = ctx.seq_alloc()
+            if L:
+                ctx.cache_write(0, s, 0, synth.to_bf16_bits(synth.cache_rows_f32(cfg, 9, b, L)))
+            seqs.append(s)
+        h = synth.to_bf16_bits(synth.hidden_f32(cfg, 9, B * q))
+        res = {}
+        for key, direct in (("direct", True), ("kernel", False), ("direct again", True)):
+            ctx.set_fused_merge(direct)
+            out = ctx.forward(0, h, seqs, lens, [q] * B, causal=True)
+            res[key] = (out.copy(), ctx.get_stage(mla.STAGE_OLAT).copy())
+            info = ctx.plan_info()
+            for s, L in zip(seqs, lens):
+                ctx.seq_truncate(s, L)
+        # both kinds of token are present: some split over thread blocks, some whole
+        assert info["n_partials"] > B * q - 5  # split tokens are present (whole ones too: the short contexts)
+        a, b, c = res["direct"], res["kernel"], res["direct again"]
+        assert np.array_equal(a[1], b[1]) and np.array_equal(a[0], b[0])
+        assert np.array_equal(a[1], c[1]) and np.array_equal(a[0], c[0])
