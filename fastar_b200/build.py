@@ -53,7 +53,7 @@ def build(force: bool = False, verbose: bool = False) -> None:
             cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             _run(cmd)
     if force or _newer(LIB_CUDA, objs):
-        _run([nvcc, "-shared", "-cudart", "static", "-o", LIB_CUDA] + objs)
+        _run([nvcc, "-shared", "-cudart", "static", "-o", LIB_CUDA] + objs + ["-ldl"])
     host_srcs = [os.path.join(HOST, f) for f in ("fst_engine.cpp", "fst_engine_capi.cpp", "fst_file.cpp")]
     host_hdrs = [os.path.join(HOST, "fst_engine.h"), os.path.join(HOST, "fst_file.h"), os.path.join(ROOT, "include", "fst_cuda_mla.h")]
     if all(os.path.exists(s) for s in host_srcs) and (force or _newer(LIB_ENGINE, host_srcs + host_hdrs + [LIB_CUDA])):

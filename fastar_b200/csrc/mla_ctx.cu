@@ -1,5 +1,7 @@
 // Context, paged-cache bookkeeping, split-KV planning and the C ABI of the MLA path.
 // Host-side logic only; the kernels live in kernels_simt.cu, gemm_tc.cu and attn_stream.cu.
+#include <dlfcn.h>
+
 #include <algorithm>
 #include <cmath>
 #include <cstdarg>
@@ -137,6 +139,13 @@ struct FstMlaCtx {
   int T = 0, n_segs = 0, n_parts = 0, n_ctas = 0;
   long long kv_rows = 0;
 
+  // split-KV across GPUs: the exchange of the per-GPU partials
+  void* nccl_comm = nullptr;         // ncclComm_t
+  FstMlaGatherFn gather_fn = nullptr;  // host-supplied transport instead
+  void* gather_user = nullptr;
+  int comm_rank = 0, comm_world = 0;
+  float *d_xpart = nullptr, *d_xgath = nullptr;  // [T*H, 2 + d_v] and [world][T*H, 2 + d_v]
+
   int64_t launches = 0;
   int64_t launches_tensor = 0, launches_simt = 0;  // GEMM / attention launches by kernel family
   bool profiling = false;
@@ -149,6 +158,8 @@ struct FstMlaCtx {
 };
 
 namespace {
+
+void comm_release(FstMlaCtx* c);  // (defined with the exchange code below)
 
 Dims dims_of(const FstMlaConfig& c) {
   Dims d;
@@ -618,6 +629,7 @@ void fst_cuda_mla_destroy(FstMlaCtx* c) {
   if (!c) return;
   cudaSetDevice(c->cfg.device);
   cudaDeviceSynchronize();
+  comm_release(c);
   for (auto& l : c->layers) {
     cudaFree(l.w_cmp); cudaFree(l.wq_b); cudaFree(l.wkv_b); cudaFree(l.wo_a); cudaFree(l.wo_b);
     cudaFree(l.q_norm); cudaFree(l.kv_norm); cudaFree(l.sinks); cudaFree(l.attn_norm);
@@ -1332,7 +1344,7 @@ int fst_cuda_mla_run_merge_device(FstMlaCtx* c, int lid, const void* d_partials,
   CU(cudaSetDevice(c->cfg.device));
   const Dims& d = c->d;
   if ((rc = prof_begin(c))) return rc;
-  prof_mark(c, FST_MLA_K_MERGE);
+  prof_mark(c, FST_MLA_K_MERGE_GATHERED);
   MergeGatheredArgs m;
   m.parts = (const float*)d_partials; m.sinks = d.v4 ? c->layers[lid].sinks : nullptr; m.lut = lut_of(c, lid);
   m.o_lat = c->d_olat; m.n_parts = n_parts; m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope;
@@ -1394,6 +1406,171 @@ int fst_cuda_mla_gemm(FstMlaCtx* c, uint16_t* C, const uint16_t* A, const uint16
   cudaFree(dA); cudaFree(dB); cudaFree(dC);
   if (e != cudaSuccess) return fail(FST_MLA_ERR_CUDA, "GEMM copy failed: %s", cudaGetErrorString(e));
   return rc;
+}
+
+/* ---- split-KV across GPUs: the exchange ------------------------------------------------- */
+}  // extern "C"
+
+namespace {
+
+// NCCL through its C entry points, resolved at run time: the library already in the process (a
+// host that uses NCCL itself has loaded it), else libnccl.so.2.
+struct NcclApi {
+  typedef struct { char internal[128]; } UniqueId;
+  int (*GetUniqueId)(UniqueId*) = nullptr;
+  int (*CommInitRank)(void**, int, UniqueId, int) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+  int (*CommDestroy)(void*) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+  bool ok = false;
+};
+
+NcclApi& nccl() {
+  static NcclApi api;
+  static bool tried = false;
+  if (tried) return api;
+  tried = true;
+  void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+  if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) return api;
+  api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
+  api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
+  api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(h, "ncclAllGather"));
+  api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+  api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+  api.ok = api.GetUniqueId && api.CommInitRank && api.AllGather && api.CommDestroy && api.GetErrorString;
+  return api;
+}
+
+int comm_buffers(FstMlaCtx* c, int world) {
+  const size_t rows = (size_t)c->cfg.max_tokens * c->d.H, w = 2 + (size_t)c->d.d_v;
+  cudaFree(c->d_xpart);
+  cudaFree(c->d_xgath);
+  c->d_xpart = c->d_xgath = nullptr;
+  int rc = dev_alloc(&c->d_xpart, rows * w);
+  if (!rc) rc = dev_alloc(&c->d_xgath, rows * w * (size_t)world);
+  return rc;
+}
+
+void comm_release(FstMlaCtx* c) {
+  if (c->nccl_comm && nccl().ok) nccl().CommDestroy(c->nccl_comm);
+  c->nccl_comm = nullptr;
+  c->gather_fn = nullptr;
+  c->gather_user = nullptr;
+  cudaFree(c->d_xpart);
+  cudaFree(c->d_xgath);
+  c->d_xpart = c->d_xgath = nullptr;
+  c->comm_world = 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fst_cuda_mla_comm_unique_id(uint8_t id_out[128]) {
+  if (!id_out) return fail(FST_MLA_ERR_ARG, "null argument");
+  NcclApi& n = nccl();
+  if (!n.ok) return fail(FST_MLA_ERR_COMM, "NCCL is not available (libnccl.so.2 could not be opened)");
+  NcclApi::UniqueId id;
+  const int r = n.GetUniqueId(&id);
+  if (r != 0) return fail(FST_MLA_ERR_COMM, "ncclGetUniqueId: %s", n.GetErrorString(r));
+  memcpy(id_out, id.internal, 128);
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_comm_init(FstMlaCtx* c, const uint8_t id[128], int32_t rank, int32_t world) {
+  if (!c || !id) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (world < 1 || rank < 0 || rank >= world) return fail(FST_MLA_ERR_ARG, "rank %d of %d", rank, world);
+  NcclApi& n = nccl();
+  if (!n.ok) return fail(FST_MLA_ERR_COMM, "NCCL is not available (libnccl.so.2 could not be opened)");
+  CU(cudaSetDevice(c->cfg.device));
+  comm_release(c);
+  NcclApi::UniqueId uid;
+  memcpy(uid.internal, id, 128);
+  void* comm = nullptr;
+  const int r = n.CommInitRank(&comm, world, uid, rank);
+  if (r != 0) return fail(FST_MLA_ERR_COMM, "ncclCommInitRank: %s", n.GetErrorString(r));
+  c->nccl_comm = comm;
+  c->comm_rank = rank;
+  c->comm_world = world;
+  return comm_buffers(c, world);
+}
+
+int fst_cuda_mla_comm_set_gather(FstMlaCtx* c, FstMlaGatherFn fn, void* user, int32_t rank, int32_t world) {
+  if (!c || !fn) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (world < 1 || rank < 0 || rank >= world) return fail(FST_MLA_ERR_ARG, "rank %d of %d", rank, world);
+  CU(cudaSetDevice(c->cfg.device));
+  comm_release(c);
+  c->gather_fn = fn;
+  c->gather_user = user;
+  c->comm_rank = rank;
+  c->comm_world = world;
+  return comm_buffers(c, world);
+}
+
+int fst_cuda_mla_comm_destroy(FstMlaCtx* c) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  cudaSetDevice(c->cfg.device);
+  cudaStreamSynchronize(c->stream);
+  comm_release(c);
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_run_split_device(FstMlaCtx* c, int lid, const void* d_h_in, void* d_h_out) {
+  int rc = check_run(c, lid);
+  if (rc) return rc;
+  if (!d_h_in || !d_h_out) return fail(FST_MLA_ERR_ARG, "null device pointer");
+  if (c->comm_world < 1) return fail(FST_MLA_ERR_STATE, "no communicator: call fst_cuda_mla_comm_init first");
+  if (c->T == 0) return FST_MLA_OK;
+  CU(cudaSetDevice(c->cfg.device));
+  const Dims& d = c->d;
+  const size_t bytes = (size_t)c->T * d.H * (2 + d.d_v) * sizeof(float);
+  if ((rc = prof_begin(c))) return rc;
+  if ((rc = run_front(c, lid, (const bf16*)d_h_in))) return rc;
+  prof_mark(c, FST_MLA_K_ATTN);
+  if ((rc = run_attention(c, lid, c->d_qeff))) return rc;
+  prof_mark(c, FST_MLA_K_MERGE);
+  if ((rc = run_merge_local(c, lid, 1, c->d_xpart))) return rc;
+  prof_mark(c, FST_MLA_K_EXCHANGE);
+  if (c->gather_fn) {
+    if (c->gather_fn(c->gather_user, c->d_xpart, c->d_xgath, bytes, c->stream) != 0)
+      return fail(FST_MLA_ERR_COMM, "the host's gather function failed");
+  } else {
+    NcclApi& n = nccl();
+    const int r = n.AllGather(c->d_xpart, c->d_xgath, bytes / sizeof(float), /* ncclFloat */ 7, c->nccl_comm, c->stream);
+    if (r != 0) return fail(FST_MLA_ERR_COMM, "ncclAllGather: %s", n.GetErrorString(r));
+  }
+  prof_mark(c, FST_MLA_K_MERGE_GATHERED);
+  MergeGatheredArgs m;
+  m.parts = c->d_xgath; m.sinks = d.v4 ? c->layers[lid].sinks : nullptr; m.lut = lut_of(c, lid);
+  m.o_lat = c->d_olat; m.n_parts = c->comm_world; m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope;
+  m.inv_rope = d.v4 ? 1 : 0;
+  launch_merge_gathered(m, c->stream);
+  c->launches += 1;
+  if ((rc = run_back(c, lid, (bf16*)d_h_out))) return rc;
+  c->cur = nullptr;
+  CU(cudaGetLastError());
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_forward_split(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* h_out,
+                               const FstMlaSeqStep* steps, int32_t n_seqs, int32_t causal) {
+  if (!c || !h_in || !h_out) return fail(FST_MLA_ERR_ARG, "null argument");
+  int rc = fst_cuda_mla_plan(c, steps, n_seqs, causal);
+  if (rc) return rc;
+  if ((rc = check_run(c, lid))) return rc;
+  if (c->T == 0) return FST_MLA_OK;
+  CU(cudaSetDevice(c->cfg.device));
+  const size_t bytes = (size_t)c->T * c->d.hidden * sizeof(uint16_t);
+  memcpy(c->h_pinned, h_in, bytes);
+  CU(cudaMemcpyAsync(c->d_h, c->h_pinned, bytes, cudaMemcpyHostToDevice, c->stream));
+  c->out_src = c->d_out;
+  if ((rc = fst_cuda_mla_run_split_device(c, lid, c->d_h, c->d_out))) return rc;
+  CU(cudaMemcpyAsync(c->h_pinned, c->d_out, bytes, cudaMemcpyDeviceToHost, c->stream));
+  if ((rc = fst_cuda_mla_sync(c))) return rc;
+  memcpy(h_out, c->h_pinned, bytes);
+  return FST_MLA_OK;
 }
 
 /* ---- measurement ---------------------------------------------------------------------- */

@@ -202,6 +202,24 @@ void FSTEngine::process_mla_batch(int lid, bf16_t* h, const int* seq_ids, const 
   check(fst_cuda_mla_forward(ctx_, lid, h, h, seq_ids, pos0, q_lens, B, causal ? 1 : 0), "process_mla_batch");
 }
 
+void FSTEngine::join_split_group(const uint8_t id[128], int rank, int world) {
+  check(fst_cuda_mla_comm_init(ctx_, id, rank, world), "comm_init");
+}
+
+void FSTEngine::process_mla_split(int lid, bf16_t* h, int M, bool owns_new_rows) {
+  int32_t local_len = 0;
+  check(fst_cuda_mla_seq_len(ctx_, seq_, &local_len), "seq_len");
+  FstMlaSeqStep st;
+  st.seq = seq_;
+  st.pos0 = owns_new_rows ? seq_pos_ - slice_begin_ : local_len;  // local row of the first new token / rows held
+  st.q_len = M;
+  st.rope_pos0 = seq_pos_;  // RoPE uses the global position
+  st.append = owns_new_rows ? 1 : 0;
+  st.window = 0;
+  if (owns_new_rows && st.pos0 + M > config_.max_seq) throw std::runtime_error("process_mla_split: the slice exceeds max_seq");
+  check(fst_cuda_mla_forward_split(ctx_, lid, h, h, &st, 1, 0), "process_mla_split");
+}
+
 void FSTEngine::reset_session() {
   check(fst_cuda_mla_reset(ctx_), "reset");
   int32_t s = -1;

@@ -98,6 +98,17 @@ class FSTEngine {
   // attends to the last `window` rows only; 0 switches it off.
   void set_window(int window);
 
+  // One long sequence with its cache split along the KV axis over `world` engines, one per GPU
+  // (the reference has no counterpart: one NPU, 128 rows).  This engine's cache holds the global
+  // rows from slice_begin on; seq_pos_ stays the GLOBAL position.  join_split_group is collective
+  // (ncclCommInitRank; id: the 128 bytes of fst_cuda_mla_comm_unique_id from rank 0).
+  // process_mla_split: every engine computes the query, attends to its slice, one all-gather
+  // exchanges the per-GPU partials, every engine merges and projects; `owns_new_rows` is true on the
+  // engine whose slice the new rows extend.  Decode only (no causal block).
+  void join_split_group(const uint8_t id[128], int rank, int world);
+  void set_kv_slice(int slice_begin) { slice_begin_ = slice_begin; }
+  void process_mla_split(int lid, bf16_t* h, int M, bool owns_new_rows);
+
   // Extra sequences for batched decode.
   int new_sequence();
   void free_sequence(int seq);
@@ -119,5 +130,6 @@ class FSTEngine {
   int seq_ = -1;
   int seq_pos_ = 0;
   bool is_prefill_ = true;
+  int slice_begin_ = 0;
   void check(int rc, const char* what);
 };

@@ -125,4 +125,12 @@ int fst_engine_randmat_test(FSTEngine* e, double* cosine, double* ratio, double*
   return n;
 }
 FstMlaCtx* fst_engine_ctx(FSTEngine* e) { return e->ctx(); }
+int fst_engine_join_split_group(FSTEngine* e, const uint8_t* id, int rank, int world) {
+  return guard([&] { e->join_split_group(id, rank, world); });
+}
+void fst_engine_set_kv_slice(FSTEngine* e, int slice_begin) { e->set_kv_slice(slice_begin); }
+void fst_engine_set_seq_pos(FSTEngine* e, int pos) { e->set_seq_pos(pos); }
+int fst_engine_process_mla_split(FSTEngine* e, int lid, uint16_t* h, int M, int owns_new_rows) {
+  return guard([&] { e->process_mla_split(lid, h, M, owns_new_rows != 0); });
+}
 }

@@ -19,10 +19,13 @@ PRESET_BASELINE = 0
 PRESET_FASTAR_V4 = 1
 IMPL_AUTO, IMPL_TENSOR, IMPL_SIMT = 0, 1, 2
 STAGE_QC, STAGE_KV, STAGE_QEFF, STAGE_OLAT, STAGE_LOW, STAGE_OUT = range(6)
-KERNEL_NAMES = ["compress", "norm_append", "q_expand", "q_absorb", "attn", "merge", "oproj_a", "oproj_b"]
+KERNEL_NAMES = ["compress", "norm_append", "q_expand", "q_absorb", "attn", "merge", "exchange", "merge_gathered",
+                "oproj_a", "oproj_b"]
 K_ATTN, K_MERGE = 4, 5
 
 ERR_ARG, ERR_PAGES, ERR_CAPACITY, ERR_CUDA, ERR_DEVICE_CHECK, ERR_STATE, ERR_NO_DEVICE = -1, -2, -3, -4, -5, -6, -7
+ERR_COMM = -8
+GATHER_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p)
 
 
 class MlaError(RuntimeError):
@@ -115,6 +118,12 @@ def load_library() -> C.CDLL:
     L.fst_cuda_mla_plan_counts.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
     L.fst_cuda_mla_set_layer_rope.argtypes = [vp, C.c_int, i32]
     L.fst_cuda_mla_set_rope_theta.argtypes = [vp, C.c_float]
+    L.fst_cuda_mla_comm_unique_id.argtypes = [C.POINTER(C.c_uint8)]
+    L.fst_cuda_mla_comm_init.argtypes = [vp, C.POINTER(C.c_uint8), i32, i32]
+    L.fst_cuda_mla_comm_set_gather.argtypes = [vp, GATHER_FN, vp, i32, i32]
+    L.fst_cuda_mla_comm_destroy.argtypes = [vp]
+    L.fst_cuda_mla_run_split_device.argtypes = [vp, C.c_int, vp, vp]
+    L.fst_cuda_mla_forward_split.argtypes = [vp, C.c_int, u16p, u16p, C.POINTER(SeqStep), i32, i32]
     L.fst_cuda_mla_family_counts.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
     L.fst_cuda_mla_selftest_wait_expiry.argtypes = [vp, i32]
     L.fst_cuda_mla_debug_set_status.argtypes = [vp, i32]
@@ -320,6 +329,35 @@ class MlaContext:
         self._check(self.lib.fst_cuda_mla_run_merge_device(self._h, lid, C.c_void_p(d_partials), n_parts,
                                                           C.c_void_p(d_out)))
 
+    # -- split-KV across GPUs --
+    def comm_init(self, unique_id: bytes, rank: int, world: int) -> None:
+        """Join an NCCL communicator of `world` ranks (collective).  unique_id: comm_unique_id() of rank 0."""
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        self._check(self.lib.fst_cuda_mla_comm_init(self._h, buf, rank, world))
+
+    def comm_set_gather(self, fn, rank: int, world: int) -> None:
+        """A host-supplied all-gather: fn(d_send, d_recv, bytes_per_rank, stream) -> 0."""
+        self._gather_cb = GATHER_FN(lambda user, s, r, n, st: int(fn(s, r, n, st) or 0))
+        self._check(self.lib.fst_cuda_mla_comm_set_gather(self._h, self._gather_cb, None, rank, world))
+
+    def comm_destroy(self) -> None:
+        self._check(self.lib.fst_cuda_mla_comm_destroy(self._h))
+
+    def run_split_device(self, lid: int, d_in: int, d_out: int) -> None:
+        self._check(self.lib.fst_cuda_mla_run_split_device(self._h, lid, C.c_void_p(d_in), C.c_void_p(d_out)))
+
+    def forward_split(self, lid: int, h: np.ndarray, steps, causal: bool = False) -> np.ndarray:
+        """The split-KV layer call with host buffers; steps as for plan()."""
+        h = np.ascontiguousarray(h, np.uint16)
+        out = np.empty_like(h)
+        arr = (SeqStep * len(steps))()
+        for i, s in enumerate(steps):
+            s = tuple(s)
+            arr[i] = SeqStep(s[0], s[1], s[2], s[3] if len(s) > 3 else -1, s[4] if len(s) > 4 else 1,
+                             s[5] if len(s) > 5 else 0)
+        self._check(self.lib.fst_cuda_mla_forward_split(self._h, lid, _u16(h), _u16(out), arr, len(steps), int(causal)))
+        return out
+
     def forward(self, lid: int, h: np.ndarray, seq_ids, pos0, q_lens, causal: bool = False) -> np.ndarray:
         """process_mla with host buffers.  h: uint16 [T, hidden] bf16 bits.  Returns the same shape."""
         h = np.ascontiguousarray(h, np.uint16)
@@ -409,6 +447,15 @@ def attention_noalloc(d_q_eff: int, d_cache: int, n_rows: int, n_heads: int, d_q
     not allocate (see include/fst_cuda_mla.h).  Device pointers as integers; returns the status."""
     return load_library().fst_cuda_mla_attention_noalloc(C.c_void_p(d_q_eff), C.c_void_p(d_cache), n_rows, n_heads,
                                                          d_qk, d_v, scale, C.c_void_p(d_o_lat), C.c_void_p(stream))
+
+
+def comm_unique_id() -> bytes:
+    """The 128 bytes rank 0 creates for comm_init (ncclGetUniqueId)."""
+    buf = (C.c_uint8 * 128)()
+    rc = load_library().fst_cuda_mla_comm_unique_id(buf)
+    if rc != 0:
+        raise MlaError(rc, load_library().fst_cuda_mla_last_error().decode())
+    return bytes(buf)
 
 
 def default_scale(cfg: Config) -> float:

@@ -34,6 +34,7 @@ extern "C" {
 #define FST_MLA_ERR_DEVICE_CHECK (-5) /* a kernel gave up a bounded wait or failed a check */
 #define FST_MLA_ERR_STATE (-6)        /* call order: no weights, no plan */
 #define FST_MLA_ERR_NO_DEVICE (-7)    /* no CUDA device: there is no CPU fallback */
+#define FST_MLA_ERR_COMM (-8)         /* the exchange between GPUs failed (NCCL missing or a call of it) */
 
 #define FST_MLA_PRESET_BASELINE 0  /* 576-wide rows [512 latent | 64 k_pe], W_UK absorb, per-head W_UV */
 #define FST_MLA_PRESET_FASTAR_V4 1 /* live engine: 512-wide rows, RoPE tail, sink, grouped wo_a */
@@ -128,9 +129,11 @@ typedef struct FstMlaSeqStep {
 #define FST_MLA_K_Q_ABSORB 3 /* RoPE(q_pe) + W_UK absorb (V4: head RMSNorm + RoPE) */
 #define FST_MLA_K_ATTN 4     /* split-KV QK / online softmax / SV over the paged cache */
 #define FST_MLA_K_MERGE 5    /* log-sum-exp merge of the split partials */
-#define FST_MLA_K_OPROJ_A 6
-#define FST_MLA_K_OPROJ_B 7
-#define FST_MLA_K_COUNT 8
+#define FST_MLA_K_EXCHANGE 6 /* split-KV across GPUs: the all-gather of the per-GPU partials */
+#define FST_MLA_K_MERGE_GATHERED 7 /* ... and the merge of the gathered partials */
+#define FST_MLA_K_OPROJ_A 8
+#define FST_MLA_K_OPROJ_B 9
+#define FST_MLA_K_COUNT 10
 
 /* ---- lifetime ------------------------------------------------------------------------- */
 /* Replaces device probe + buffer allocation of FSTEngine::FSTEngine (src/fst_engine.cpp:
@@ -227,6 +230,38 @@ int fst_cuda_mla_run_partial_device(FstMlaCtx* ctx, int lid, const void* d_h_in,
  * output projections into d_h_out. */
 int fst_cuda_mla_run_merge_device(FstMlaCtx* ctx, int lid, const void* d_partials, int32_t n_parts,
                                   void* d_h_out);
+/* ---- split-KV across GPUs, exchange included -------------------------------------------------
+ * One long sequence, its cache cut along the KV axis into one slice per GPU (one context per GPU,
+ * one process per GPU or one process for all).  A layer call is: every GPU runs the front of the
+ * layer and attends to its slice (as fst_cuda_mla_run_partial_device), ONE all-gather exchanges the
+ * per-GPU (max, sum, un-normalised O) partials -- T*H rows of 2 + d_v floats per GPU, 131.6 KB for
+ * one query token -- and every GPU merges them by log-sum-exp and runs the output projections.  The
+ * reference has no counterpart (one NPU, 128 rows); the engine-side call is FSTEngine::process_mla_split.
+ *
+ * The transport is NCCL (ncclAllGather on the context's stream; no kernel reads another GPU's
+ * memory), or a function the host supplies.  NCCL is not linked: the library already loaded in the
+ * process is used, else libnccl.so.2 is opened when the first of these calls needs it. */
+/* The 128 bytes every rank needs to join (ncclGetUniqueId); rank 0 creates them, the host hands
+ * them to the other ranks by whatever means it has. */
+int fst_cuda_mla_comm_unique_id(uint8_t id_out[128]);
+/* Joins the context to a communicator of `world` ranks as rank `rank` (ncclCommInitRank on the
+ * context's device; collective: every rank calls it) and allocates the exchange buffers. */
+int fst_cuda_mla_comm_init(FstMlaCtx* ctx, const uint8_t id[128], int32_t rank, int32_t world);
+/* A host-supplied transport instead: gather(user, d_send, d_recv, bytes_per_rank, cuda_stream) must
+ * leave rank r's bytes at d_recv + r * bytes_per_rank on every rank, ordered on cuda_stream, and
+ * return 0.  For hosts with their own collective layer, and for tests on one GPU. */
+typedef int (*FstMlaGatherFn)(void* user, const void* d_send, void* d_recv, size_t bytes_per_rank, void* cuda_stream);
+int fst_cuda_mla_comm_set_gather(FstMlaCtx* ctx, FstMlaGatherFn fn, void* user, int32_t rank, int32_t world);
+int fst_cuda_mla_comm_destroy(FstMlaCtx* ctx);
+/* The layer call for the current plan (the plan of a KV slice: FstMlaSeqStep.append = 1 on the rank
+ * that owns the new rows, 0 elsewhere; rope_pos0 = the global position).  Device buffers as for
+ * fst_cuda_mla_run_device; enqueued on the context's stream, no host synchronisation. */
+int fst_cuda_mla_run_split_device(FstMlaCtx* ctx, int lid, const void* d_h_in, void* d_h_out);
+/* The same with host buffers, as the engine calls it: plan (the steps of this GPU's slice) + H2D +
+ * the split layer call + D2H + sync.  h_in / h_out: host bf16 [sum q_len, hidden], may alias. */
+int fst_cuda_mla_forward_split(FstMlaCtx* ctx, int lid, const uint16_t* h_in, uint16_t* h_out,
+                               const FstMlaSeqStep* steps, int32_t n_seqs, int32_t causal);
+
 /* Number of new tokens T of the current plan. */
 int fst_cuda_mla_plan_tokens(FstMlaCtx* ctx, int32_t* t_out);
 int fst_cuda_mla_get_stage(FstMlaCtx* ctx, int stage, uint16_t* host_out, size_t bytes);
