@@ -326,6 +326,9 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
       TileCursor cur;
       cur.init(p.segs, seg0, seg1);
       bool ok = true;
+      // cache tiles are read once and are more than L2 holds: they leave L2 first, so that the
+      // partials written here are still there when the merge reads them
+      const uint64_t stream_policy = tc::l2_policy_evict_first();
       // the chunks of slot g that this producer copies, from rows row0 .. row0+63 of `map`
       auto fill = [&](int g, const CUtensorMap* map, int row0) -> bool {
         const int c0 = (r + 3 - (g * NCH) % 3) % 3;
@@ -334,7 +337,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
         for (int c = c0; c < NCH; c += 3) {
           const int slot = (g % 3) * NCH + c;
           tc::mbar_expect_tx(&mi->full_t[g & 3][c / 3], CHUNK);
-          tc::tma_load_3d(s_ring + slot * CHUNK, map, &mi->full_t[g & 3][c / 3], c * 64, row0, 0);
+          tc::tma_load_3d_hint(s_ring + slot * CHUNK, map, &mi->full_t[g & 3][c / 3], c * 64, row0, 0, stream_policy);
         }
         return true;
       };

@@ -103,6 +103,21 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
       : "memory");
 }
 
+// L2 eviction policy for data that is read exactly once (a stream larger than L2): its lines are
+// the first to go, so that what the kernel writes for its successor stays resident.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_3d_hint(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "l"(policy)
+      : "memory");
+}
+
 // ---- TMEM --------------------------------------------------------------------------------------
 // Warp-collective.  n_cols: power of two in [32, 512].  The base address lands in *dst (shared).
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst, uint32_t n_cols) {
