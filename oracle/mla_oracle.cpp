@@ -249,31 +249,51 @@ void fst_oracle_gemm(const float* A, const float* B, float* C, int M, int N, int
 
 namespace {
 
-/* One (query token, head) row of QK -> softmax -> SV over rows [0, S) of `cache`. */
+/* One (query token, head) row of QK -> softmax -> SV over rows [0, S) of `cache` and, when the
+ * layer has a compressor, over the first n_cmp rows of `cmp` as further columns (3565-3586). */
 void attention_row(const FstOracleCfg* c, const Dims& d, const float* q, const float* cache, int S,
-                   bool has_sink, float sink, std::vector<float>& sc, std::vector<double>& acc, float* o) {
+                   bool has_sink, float sink, std::vector<float>& sc, std::vector<double>& acc, float* o,
+                   const float* cmp = nullptr, int n_cmp = 0) {
   const float scale = c->softmax_scale;
   const int rb = c->round_bf16;
-  if ((int)sc.size() < S) sc.resize(S);
+  const int Stot = S + n_cmp;
+  if ((int)sc.size() < Stot) sc.resize(Stot);
+  auto row_of = [&](int s) { return s < S ? cache + (size_t)s * d.row : cmp + (size_t)(s - S) * d.row; };
   float mx = has_sink ? sink : -INFINITY;
-  for (int s = 0; s < S; ++s) {
-    sc[s] = dot(q, cache + (size_t)s * d.row, d.d_qk) * scale;
+  for (int s = 0; s < Stot; ++s) {
+    sc[s] = dot(q, row_of(s), d.d_qk) * scale;
     mx = std::max(mx, sc[s]);
   }
-  if (S <= 0 && !has_sink) {
+  if (Stot <= 0 && !has_sink) {
     for (int j = 0; j < d.d_v; ++j) o[j] = 0.0f;
     return;
   }
   float sum = has_sink ? std::exp(sink - mx) : 0.0f;
-  for (int s = 0; s < S; ++s) sum += std::exp(sc[s] - mx);
+  for (int s = 0; s < Stot; ++s) sum += std::exp(sc[s] - mx);
   const float inv = 1.0f / (sum + 1e-12f);
   std::fill(acc.begin(), acc.end(), 0.0);
-  for (int s = 0; s < S; ++s) {
+  for (int s = 0; s < Stot; ++s) {
     const float p = rnd(std::exp(sc[s] - mx) * inv, rb);
-    const float* v = cache + (size_t)s * d.row;
+    const float* v = row_of(s);
     for (int j = 0; j < d.d_v; ++j) acc[j] += (double)p * v[j];
   }
   for (int j = 0; j < d.d_v; ++j) o[j] = rnd((float)acc[j], rb);
+}
+
+/* The 127 non-negative E4M3 values (3070-3083). */
+const float* e4m3_grid() {
+  static float g[127];
+  static bool init = false;
+  if (!init) {
+    static const float exp_scale[16] = {0.0f, 0.015625f, 0.03125f, 0.0625f, 0.125f, 0.25f, 0.5f, 1.0f,
+                                        2.0f, 4.0f,      8.0f,     16.0f,   32.0f,  64.0f, 128.0f, 256.0f};
+    for (int i = 0; i < 127; ++i) {
+      const int e = (i >> 3) & 15, m = i & 7;
+      g[i] = e == 0 ? (float)m * 0.001953125f : (1.0f + (float)m * 0.125f) * exp_scale[e];
+    }
+    init = true;
+  }
+  return g;
 }
 
 }  // namespace
@@ -369,9 +389,114 @@ void fst_oracle_merge_partials(const FstOracleCfg* c, const float* m, const floa
  * (one product over T = sum q_lens rows, the weights read once), and the per-sequence stages
  * (RoPE position, cache push, attention) follow each row's own sequence.  h[T, hidden] holds the
  * sequences' rows back to back; trace buffers are sized for T rows. */
+int fst_oracle_compressor_width(int ratio, int kv_lora) { return ratio == 4 ? 2 * kv_lora : (ratio > 0 ? kv_lora : 0); }
+int fst_oracle_compressor_rows(int ratio) { return ratio == 4 ? 8 : ratio; }
+
+float fst_oracle_e4m3_roundtrip(float v) {
+  const float* g = e4m3_grid();
+  const float sign = v < 0.0f ? -1.0f : 1.0f;
+  const float ax = std::min(std::fabs(v), 448.0f);
+  int lo = 0, hi = 126;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (g[mid] <= ax) lo = mid; else hi = mid - 1;
+  }
+  int best = lo;
+  if (best < 126) {
+    const float bd = std::fabs(ax - g[best]), nd = std::fabs(ax - g[best + 1]);
+    if (nd < bd || (nd == bd && ((best + 1) & 1) == 0 && (best & 1) != 0)) ++best;
+  }
+  return sign * g[best];
+}
+
+/* compress_token, src/fst_engine.cpp:3171-3318.  The two projections are bf16 tile outputs there
+ * (3189-3193); with round_bf16 they are rounded here too.  The compressed row is stored as bf16
+ * (3268-3271; the reference truncates, this build rounds to nearest like everywhere else -- the
+ * nope part is exactly representable either way, only the 64 tail values can differ by one step). */
+int fst_oracle_compress_token(const FstOracleCfg* c, const FstOracleCompressorW* w, FstOracleCompressorState* st,
+                              const float* hidden_normed, int pos) {
+  const Dims d = dims_of(c);
+  const int ratio = w->ratio, hd = d.kv_lora;
+  if (ratio <= 0) return 0;
+  const int width = fst_oracle_compressor_width(ratio, hd);
+  const int pos_mod = pos % ratio;
+  const int row = ratio == 4 ? ratio + pos_mod : pos_mod;
+  const bool should = ((pos + 1) % ratio) == 0;
+  std::vector<float> kv_cur(width), sc_cur(width);
+  for (int j = 0; j < width; ++j) {
+    kv_cur[j] = rnd(dot(hidden_normed, w->wkv + (size_t)j * d.hidden, d.hidden), c->round_bf16);
+    sc_cur[j] = rnd(dot(hidden_normed, w->wgate + (size_t)j * d.hidden, d.hidden), c->round_bf16) +
+                w->ape[(size_t)pos_mod * width + j]; /* APE add, 3197-3198 */
+  }
+  std::memcpy(st->state_kv + (size_t)row * width, kv_cur.data(), width * sizeof(float));
+  std::memcpy(st->state_sc + (size_t)row * width, sc_cur.data(), width * sizeof(float));
+  if (!should) return 0;
+  if (st->n_comp >= st->cap) return -1;
+
+  /* per-dim softmax pool over the window rows, two lanes for ratio 4 (3206-3242) */
+  std::vector<float> pooled(hd, 0.0f);
+  for (int j = 0; j < hd; ++j) {
+    float mx = -1e30f;
+    for (int r = 0; r < ratio; ++r) {
+      mx = std::max(mx, st->state_sc[(size_t)r * width + j]);
+      if (ratio == 4) mx = std::max(mx, st->state_sc[(size_t)(ratio + r) * width + hd + j]);
+    }
+    if (mx <= -0.5e30f) continue;
+    float denom = 0.0f, sum = 0.0f;
+    for (int r = 0; r < ratio; ++r) {
+      const float wp = std::exp(st->state_sc[(size_t)r * width + j] - mx);
+      denom += wp;
+      sum += wp * st->state_kv[(size_t)r * width + j];
+      if (ratio == 4) {
+        const float wc = std::exp(st->state_sc[(size_t)(ratio + r) * width + hd + j] - mx);
+        denom += wc;
+        sum += wc * st->state_kv[(size_t)(ratio + r) * width + hd + j];
+      }
+    }
+    pooled[j] = denom > 0.0f ? sum / denom : 0.0f;
+  }
+  /* RMS norm with the compressor's weight (3244-3250) */
+  double ss = 0;
+  for (int i = 0; i < hd; ++i) ss += (double)pooled[i] * pooled[i];
+  const float rms = 1.0f / std::sqrt((float)(ss / (double)hd) + 1e-6f);
+  std::vector<float> out(hd);
+  for (int i = 0; i < hd; ++i) out[i] = pooled[i] * rms * w->norm[i];
+  /* RoPE on the tail at comp_pos = pos + 1 - ratio (3252-3254, rope_tail_yarn 3108-3153) */
+  fst_oracle_rope_apply(out.data() + hd - d.rope, pos + 1 - ratio, d.rope, c->rope_theta, c->rope_yarn, 0, 0);
+  /* E4M3 round trip of the nope part in 64-blocks (3256-3267) */
+  for (int off = 0; off < hd - d.rope; off += 64) {
+    float amax = 0.0f;
+    for (int i = 0; i < 64; ++i) amax = std::max(amax, std::fabs(out[off + i]));
+    if (amax < 1.0e-4f) amax = 1.0e-4f;
+    const float scale = std::ldexp(1.0f, (int)std::ceil(std::log2(amax / 448.0f)));
+    for (int i = 0; i < 64; ++i) {
+      float v = out[off + i] / scale;
+      v = std::min(448.0f, std::max(-448.0f, v));
+      out[off + i] = fst_oracle_e4m3_roundtrip(v) * scale;
+    }
+  }
+  for (int i = 0; i < hd; ++i) st->cache[(size_t)st->n_comp * hd + i] = bf16_rne(out[i]);
+  st->n_comp++;
+  /* window rotation, ratio 4 only (3302-3317): both lanes become the window just processed */
+  if (ratio == 4) {
+    for (int r = 0; r < ratio; ++r) {
+      std::memcpy(st->state_kv + (size_t)r * width, st->state_kv + (size_t)(ratio + r) * width, width * sizeof(float));
+      std::memcpy(st->state_sc + (size_t)r * width, st->state_sc + (size_t)(ratio + r) * width, width * sizeof(float));
+    }
+  }
+  return 1;
+}
+
 int fst_oracle_mla_forward_batch(const FstOracleCfg* c, const FstOracleWeights* w, const float* h, int B,
                                  const int32_t* q_lens, const int32_t* pos0, int causal, float* const* caches,
                                  const int32_t* caps, float* out, FstOracleTrace* trace) {
+  return fst_oracle_mla_forward_batch_cmp(c, w, nullptr, nullptr, h, B, q_lens, pos0, causal, caches, caps, out, trace);
+}
+
+int fst_oracle_mla_forward_batch_cmp(const FstOracleCfg* c, const FstOracleWeights* w,
+                                     const FstOracleCompressorW* cw, FstOracleCompressorState* states,
+                                     const float* h, int B, const int32_t* q_lens, const int32_t* pos0, int causal,
+                                     float* const* caches, const int32_t* caps, float* out, FstOracleTrace* trace) {
   const Dims d = dims_of(c);
   const int rb = c->round_bf16, nt = c->n_threads;
   if (B < 0) return -1;
@@ -460,6 +585,12 @@ int fst_oracle_mla_forward_batch(const FstOracleCfg* c, const FstOracleWeights* 
       std::memcpy(caches[b] + (size_t)pos0[b] * d.row, kv.data() + (size_t)tok0[b] * d.row,
                   (size_t)q_lens[b] * d.row * sizeof(float));
 
+  /* KV compressor (3545-3568): the new rows, in order, after the push and before the attention. */
+  const bool has_cmp = cw && cw->ratio > 0 && states;
+  if (has_cmp)
+    for (int t = 0; t < T; ++t)
+      if (fst_oracle_compress_token(c, cw, &states[seq_of[t]], h + (size_t)t * d.hidden, pos_of[t]) < 0) return -1;
+
   /* QK, softmax, SV (3573-3683): a row (token, head) attends to S = pos0 + M rows of its own
    * sequence, minus the rows the causal mask drops (3626). */
   std::vector<float> o_lat((size_t)T * d.H * d.d_v);
@@ -472,8 +603,16 @@ int fst_oracle_mla_forward_batch(const FstOracleCfg* c, const FstOracleWeights* 
       const int t = (int)(r / d.H), hh = (int)(r % d.H), b = seq_of[t];
       int S = pos0[b] + q_lens[b];
       if (causal) S = std::min(S, pos_of[t] + 1);
+      /* compressed column k was emitted at position (k + 1) * ratio - 1: visible to every row in
+       * decode, to rows at or after that position when causal (3630-3635) */
+      int n_cmp = 0;
+      if (has_cmp) {
+        n_cmp = states[b].n_comp;
+        if (causal) n_cmp = std::min(n_cmp, (pos_of[t] + 1) / cw->ratio);
+      }
       attention_row(c, d, q_eff.data() + (size_t)r * d.d_qk, caches[b], S, has_sink,
-                    has_sink ? w->attn_sinks[hh] : 0.0f, sc, acc, o_lat.data() + (size_t)r * d.d_v);
+                    has_sink ? w->attn_sinks[hh] : 0.0f, sc, acc, o_lat.data() + (size_t)r * d.d_v,
+                    has_cmp ? states[b].cache : nullptr, n_cmp);
     });
   }
 

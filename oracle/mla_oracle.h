@@ -144,6 +144,40 @@ int fst_oracle_mla_forward(const FstOracleCfg* c, const FstOracleWeights* w, con
                            int pos0, int causal, float* cache, int cap, float* out,
                            FstOracleTrace* trace);
 
+/* ---- V4 KV compressor (reference src/fst_engine.cpp:3063-3318) ---------------------------------
+ * Layers whose compress ratio is 4 or 128 stream every token's attn-normed hidden row through a
+ * per-layer compressor: two projections (wkv, wgate: [width, hidden], width = 1024 for ratio 4, 512
+ * for ratio 128), a positional bias (ape [ratio, width]) on the gate, a window state, and on every
+ * ratio-th token one pooled, normed (norm [kv_lora]), tail-rotated, E4M3-round-tripped row of
+ * kv_lora values that joins the attention as one more column (3565-3586, 3630-3635). */
+typedef struct {
+  int32_t ratio;       /* 4 or 128 (0: no compressor) */
+  const float* wkv;    /* [width, hidden] */
+  const float* wgate;  /* [width, hidden] */
+  const float* ape;    /* [ratio, width] */
+  const float* norm;   /* [kv_lora] */
+} FstOracleCompressorW;
+
+/* Streaming state of one (layer, sequence): state_kv / state_sc are [rows, width] with rows = 8 for
+ * ratio 4 (two lanes of four) and `ratio` otherwise; the engine starts them at zero
+ * (reset_compressor_state, 3160-3169).  cache[cap, kv_lora] receives the compressed rows. */
+typedef struct {
+  float* state_kv;
+  float* state_sc;
+  float* cache;
+  int32_t n_comp;
+  int32_t cap;
+} FstOracleCompressorState;
+
+int fst_oracle_compressor_width(int ratio, int kv_lora);
+int fst_oracle_compressor_rows(int ratio);
+/* e4m3_roundtrip (3084-3100): nearest of the 127 non-negative E4M3 values, the reference's tie rule. */
+float fst_oracle_e4m3_roundtrip(float v);
+/* compress_token (3171-3318) for the token at position `pos` (the sequence's positions must arrive
+ * in order from 0).  Returns 1 when a row was emitted, 0 when not, -1 when the cache is full. */
+int fst_oracle_compress_token(const FstOracleCfg* c, const FstOracleCompressorW* w, FstOracleCompressorState* st,
+                              const float* hidden_normed, int pos);
+
 /* The same layer for B sequences in one call (batched decode): h[T, hidden] holds the rows of
  * the sequences back to back (T = sum q_lens), caches[b] is sequence b's [caps[b], row] buffer.
  * Every row gets exactly the arithmetic of fst_oracle_mla_forward; the projections run over all
@@ -151,6 +185,14 @@ int fst_oracle_mla_forward(const FstOracleCfg* c, const FstOracleWeights* w, con
 int fst_oracle_mla_forward_batch(const FstOracleCfg* c, const FstOracleWeights* w, const float* h, int B,
                                  const int32_t* q_lens, const int32_t* pos0, int causal, float* const* caches,
                                  const int32_t* caps, float* out, FstOracleTrace* trace);
+/* ... with the layer's KV compressor: cw (ratio 4 or 128) and one state per sequence.  The new rows
+ * go through the compressor after the cache push and before the attention (3545-3568), and every
+ * query row attends to its raw rows AND to the compressed rows it may see: all of them in decode,
+ * those emitted at a position <= its own when causal (3630-3635). */
+int fst_oracle_mla_forward_batch_cmp(const FstOracleCfg* c, const FstOracleWeights* w,
+                                     const FstOracleCompressorW* cw, FstOracleCompressorState* states,
+                                     const float* h, int B, const int32_t* q_lens, const int32_t* pos0, int causal,
+                                     float* const* caches, const int32_t* caps, float* out, FstOracleTrace* trace);
 
 /* Host twin of the paged-cache bookkeeping: a LIFO free list of n_pages pages.
  * Used to check page mapping bit-exactly.  Opaque handle. */

@@ -44,6 +44,15 @@ class _Weights(C.Structure):
                 ("wq_a", "wq_b", "wkv_a", "wkv_b", "wo_a", "wo_b", "q_norm", "kv_norm", "attn_sinks", "attn_norm")]
 
 
+class _CompressorW(C.Structure):
+    _fields_ = [("ratio", C.c_int32)] + [(n, C.POINTER(C.c_float)) for n in ("wkv", "wgate", "ape", "norm")]
+
+
+class _CompressorState(C.Structure):
+    _fields_ = [("state_kv", C.POINTER(C.c_float)), ("state_sc", C.POINTER(C.c_float)),
+                ("cache", C.POINTER(C.c_float)), ("n_comp", C.c_int32), ("cap", C.c_int32)]
+
+
 class _Trace(C.Structure):
     _fields_ = [(n, C.POINTER(C.c_float)) for n in ("qc", "kv", "q_eff", "o_lat", "low")]
 
@@ -102,6 +111,16 @@ def lib() -> C.CDLL:
         L.fst_oracle_mla_forward_batch.argtypes = [cp, C.POINTER(_Weights), fp, C.c_int, i32p, i32p, C.c_int,
                                                    C.POINTER(fp), i32p, fp, C.POINTER(_Trace)]
         L.fst_oracle_mla_forward_batch.restype = C.c_int
+        L.fst_oracle_mla_forward_batch_cmp.argtypes = [cp, C.POINTER(_Weights), C.POINTER(_CompressorW),
+                                                       C.POINTER(_CompressorState), fp, C.c_int, i32p, i32p, C.c_int,
+                                                       C.POINTER(fp), i32p, fp, C.POINTER(_Trace)]
+        L.fst_oracle_mla_forward_batch_cmp.restype = C.c_int
+        L.fst_oracle_compress_token.argtypes = [cp, C.POINTER(_CompressorW), C.POINTER(_CompressorState), fp, C.c_int]
+        L.fst_oracle_compress_token.restype = C.c_int
+        L.fst_oracle_e4m3_roundtrip.argtypes = [C.c_float]
+        L.fst_oracle_e4m3_roundtrip.restype = C.c_float
+        L.fst_oracle_compressor_width.argtypes = [C.c_int, C.c_int]
+        L.fst_oracle_compressor_rows.argtypes = [C.c_int]
         for n in ("row_width", "d_qk", "d_v", "low_dim", "threads"):
             getattr(L, "fst_oracle_" + n).argtypes = [cp]
         L.fst_oracle_pager_create.restype = C.c_void_p
@@ -280,7 +299,52 @@ def mla_forward(cfg, weights: dict, h, pos0, cache, causal=False, want_trace=Tru
     return ForwardResult(out, tr)
 
 
-def mla_forward_batch(cfg, weights: dict, h, q_lens, pos0, caches, causal=False, want_trace=False) -> ForwardResult:
+class Compressor:
+    """Weights of one layer's KV compressor (wkv, wgate [width, hidden]; ape [ratio, width];
+    norm [kv_lora]) and the streaming state of ONE sequence: window state, compressed rows."""
+
+    def __init__(self, cfg, ratio: int, wkv, wgate, ape, norm, cap: int = 4096, score_init: float = 0.0):
+        self.ratio, self.kv_lora = ratio, cfg.kv_lora
+        self.width = lib().fst_oracle_compressor_width(ratio, cfg.kv_lora)
+        self.rows = lib().fst_oracle_compressor_rows(ratio)
+        self.wkv, self.wgate, self.ape, self.norm = _f(wkv), _f(wgate), _f(ape), _f(norm)
+        assert self.wkv.shape == (self.width, cfg.hidden) and self.ape.shape == (ratio, self.width)
+        self.w = _CompressorW(ratio, _p(self.wkv), _p(self.wgate), _p(self.ape), _p(self.norm))
+        self.cap, self.score_init = cap, score_init
+        self.reset()
+
+    def reset(self):
+        # the engine starts both states at zero (reset_compressor_state, src/fst_engine.cpp:3160-3169);
+        # the HF model starts the scores at -inf (score_init)
+        self.state_kv = np.zeros((self.rows, self.width), np.float32)
+        self.state_sc = np.full((self.rows, self.width), self.score_init, np.float32)
+        self.cache = np.zeros((self.cap, self.kv_lora), np.float32)
+        self.st = _CompressorState(_p(self.state_kv), _p(self.state_sc), _p(self.cache), 0, self.cap)
+
+    def fork(self):
+        """A second sequence with the same weights and a fresh state."""
+        o = object.__new__(Compressor)
+        o.__dict__.update(self.__dict__)
+        o.reset()
+        return o
+
+    @property
+    def n_comp(self) -> int:
+        return self.st.n_comp
+
+    def rows_out(self) -> np.ndarray:
+        return self.cache[:self.st.n_comp]
+
+    def push(self, cfg, hidden_normed, pos: int) -> int:
+        return lib().fst_oracle_compress_token(C.byref(cfg), C.byref(self.w), C.byref(self.st), _p(_f(hidden_normed)), pos)
+
+
+def e4m3_roundtrip(v: float) -> float:
+    return lib().fst_oracle_e4m3_roundtrip(float(v))
+
+
+def mla_forward_batch(cfg, weights: dict, h, q_lens, pos0, caches, causal=False, want_trace=False,
+                      compressors=None) -> ForwardResult:
     """The layer for B sequences in one call: h [sum q_lens, hidden] holds the sequences' rows back to
     back, caches[b] is sequence b's float32 [cap_b, row] array (updated in place).  Row for row the
     arithmetic of mla_forward; the projections run over all rows at once."""
@@ -308,9 +372,19 @@ def mla_forward_batch(cfg, weights: dict, h, q_lens, pos0, caches, causal=False,
               "low": np.empty((T, d["low"]), np.float32)}
         t = _Trace(**{k: _p(v) for k, v in tr.items()})
     i32p = C.POINTER(C.c_int32)
-    rc = lib().fst_oracle_mla_forward_batch(C.byref(cfg), C.byref(w), _p(h), B, q.ctypes.data_as(i32p),
-                                            p0.ctypes.data_as(i32p), int(causal), cptr, caps.ctypes.data_as(i32p),
-                                            _p(out), C.byref(t))
+    if compressors is not None:
+        # one Compressor per sequence (same weights, own state): the layer's KV compressor
+        assert len(compressors) == B
+        sts = (_CompressorState * B)(*[c.st for c in compressors])
+        rc = lib().fst_oracle_mla_forward_batch_cmp(C.byref(cfg), C.byref(w), C.byref(compressors[0].w), sts, _p(h), B,
+                                                    q.ctypes.data_as(i32p), p0.ctypes.data_as(i32p), int(causal), cptr,
+                                                    caps.ctypes.data_as(i32p), _p(out), C.byref(t))
+        for c, st in zip(compressors, sts):
+            c.st.n_comp = st.n_comp
+    else:
+        rc = lib().fst_oracle_mla_forward_batch(C.byref(cfg), C.byref(w), _p(h), B, q.ctypes.data_as(i32p),
+                                                p0.ctypes.data_as(i32p), int(causal), cptr, caps.ctypes.data_as(i32p),
+                                                _p(out), C.byref(t))
     if rc != 0:
         raise ValueError("oracle: a sequence's pos0 + q_len exceeds its cache capacity")
     return ForwardResult(out, tr)

@@ -158,3 +158,104 @@ def test_window_attention_is_attention_over_the_last_rows():
     for W in (1, 63, 64, 100, 299):
         cut = np.ascontiguousarray(cache[L - W:])
         assert np.allclose(O.attention_window(cfg, q, cache, L, 1, W), O.attention(cfg, q, cut, W, 1), atol=1.6e-2), W
+
+
+# ---- the V4 layer and its KV compressor against the reference's own Python (tests/golden/make_golden_v4.py) ----
+import os  # noqa: E402
+
+import pytest  # noqa: E402
+
+_V4 = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_v4_layer.npz")
+GEOM = dict(hidden=128, n_heads=4, q_lora=64, kv_lora=192, qk_rope=64, o_groups=2, o_lora=32)
+
+
+@pytest.fixture(scope="module")
+def v4():
+    return np.load(_V4)
+
+
+def _layer_weights(v4, tag):
+    g = lambda n: v4[f"{tag}_w_{n}"]  # noqa: E731
+    return {"wq_a": g("attn.wq_a.weight"), "wq_b": g("attn.wq_b.weight"), "wkv_a": g("attn.wkv.weight"),
+            "wo_a": g("attn.wo_a.weight"), "wo_b": g("attn.wo_b.weight"), "q_norm": g("attn.q_norm.weight"),
+            "kv_norm": g("attn.kv_norm.weight"), "attn_sinks": g("attn.attn_sink")}
+
+
+def _compressor(cfg, v4, tag, ratio, **kw):
+    g = lambda n: v4[f"{tag}_w_attn.compressor.{n}"]  # noqa: E731
+    return O.Compressor(cfg, ratio, g("wkv.weight"), g("wgate.weight"), g("ape"), g("norm.weight"), **kw)
+
+
+def test_e4m3_round_trip_is_the_fp8_cast():
+    # e4m3_roundtrip (src/fst_engine.cpp:3084-3100) == a cast to float8_e4m3fn and back, ties to even
+    import torch
+    rng = np.random.default_rng(3)
+    x = np.concatenate([rng.uniform(-448, 448, 4000), rng.standard_normal(2000) * 0.01, [0.0, 448.0, -448.0, 500.0],
+                        np.arange(0, 16, 0.0625)]).astype(np.float32)
+    want = torch.from_numpy(np.clip(x, -448, 448)).to(torch.float8_e4m3fn).to(torch.float32).numpy()
+    got = np.array([O.e4m3_roundtrip(v) for v in x], np.float32)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("tag,ratio", [("cmp4", 4), ("cmp128", 128)])
+def test_compressor_matches_the_reference_compressor(v4, tag, ratio):
+    """compress_token (src/fst_engine.cpp:3171-3318) streamed token by token == the HF model's
+    Compressor.forward (scripts/hf_gen_ref.py:266-353) on the same rows, with the score state started
+    at -inf as that model starts it.  Nope values are E4M3 grid values times a power of two: equal
+    up to an occasional neighbouring grid value where the pooled value sits on a rounding boundary."""
+    cfg = O.make_cfg(O.PRESET_FASTAR_V4, round_bf16=False, rope_yarn=True, **GEOM)
+    comp = _compressor(cfg, v4, tag, ratio, score_init=-np.inf)
+    x = v4[f"{tag}_x"]
+    emitted = [comp.push(cfg, x[t], t) for t in range(x.shape[0])]
+    assert emitted == [1 if (t + 1) % ratio == 0 else 0 for t in range(x.shape[0])]
+    got, want = comp.rows_out(), v4[f"{tag}_rows"]
+    assert got.shape == want.shape and got.shape[0] == x.shape[0] // ratio
+    nope = slice(0, 128)
+    same = np.isclose(got[:, nope], want[:, nope], rtol=0, atol=0)
+    assert same.mean() > 0.995
+    assert np.max(np.abs(got[:, nope] - want[:, nope]) / (np.abs(want[:, nope]) + 1e-6)) <= 0.13  # one grid step
+    # the rotated tail: fp32 there, rounded to bf16 here
+    assert np.max(np.abs(got[:, 128:] - want[:, 128:])) <= 2.0 ** -8 * np.max(np.abs(want[:, 128:])) + 1e-6
+
+
+def test_engine_starts_the_compressor_state_at_zero(v4):
+    """reset_compressor_state (3160-3169) zeroes the states, so the empty lane of the very first
+    ratio-4 window takes part in the pool with score 0 and value 0: the first row differs from the
+    HF model's, later rows do not."""
+    cfg = O.make_cfg(O.PRESET_FASTAR_V4, round_bf16=False, rope_yarn=True, **GEOM)
+    x = v4["cmp4_x"]
+    a, b = _compressor(cfg, v4, "cmp4", 4, score_init=0.0), _compressor(cfg, v4, "cmp4", 4, score_init=-np.inf)
+    for t in range(12):
+        a.push(cfg, x[t], t)
+        b.push(cfg, x[t], t)
+    assert not np.allclose(a.rows_out()[0], b.rows_out()[0])
+    assert np.array_equal(a.rows_out()[1:], b.rows_out()[1:])
+
+
+def test_v4_layer_composition_matches_layer_attn_forward(v4):
+    """The whole V4 attention layer -- head layout [M, 64, 512], per-head q norm before RoPE, sink
+    in the softmax, inverse RoPE on the output tail, grouped wo_a -- against LayerAttn.forward
+    (scripts/hf_gen_ref.py:389-467): a causal prefill of 11 rows, then two decode steps."""
+    cfg = O.make_cfg(O.PRESET_FASTAR_V4, round_bf16=False, rope_yarn=False, **GEOM)
+    w = _layer_weights(v4, "layer0")
+    x, want = v4["layer0_x"], v4["layer0_out"]
+    cache = np.zeros((x.shape[0], 192), np.float32)
+    for start, n in v4["layer0_plan"]:
+        got = O.mla_forward(cfg, w, x[start:start + n], int(start), cache, causal=n > 1, want_trace=False).out
+        ref = want[start:start + n]
+        assert np.max(np.abs(got - ref)) <= 2e-4 * np.max(np.abs(ref)), (start, n)
+
+
+def test_v4_layer_with_compressor_matches_layer_attn_forward(v4):
+    """A ratio-4 layer (YaRN tables) decoded token by token from position 0: the compressed rows join
+    the attention as extra columns (src/fst_engine.cpp:3565-3586), as LayerAttn.forward does it."""
+    cfg = O.make_cfg(O.PRESET_FASTAR_V4, round_bf16=False, rope_yarn=True, **GEOM)
+    w = _layer_weights(v4, "layer2")
+    comp = _compressor(cfg, v4, "layer2", 4, score_init=-np.inf)
+    x, want = v4["layer2_x"], v4["layer2_out"]
+    cache = np.zeros((x.shape[0], 192), np.float32)
+    for t in range(x.shape[0]):
+        got = O.mla_forward_batch(cfg, w, x[t:t + 1], [1], [t], [cache], compressors=[comp]).out
+        assert np.max(np.abs(got - want[t:t + 1])) <= 5e-3 * np.max(np.abs(want[t:t + 1])), t
+    assert comp.n_comp == x.shape[0] // 4
+    assert np.max(np.abs(comp.rows_out() - v4["layer2_cmp_rows"])) <= 0.13 * np.max(np.abs(v4["layer2_cmp_rows"]))
