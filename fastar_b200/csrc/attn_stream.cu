@@ -74,7 +74,6 @@ __device__ __forceinline__ int p_slot_off(int g) {
 struct StreamParams {
   const bf16* q_eff;
   const int32_t* tables;
-  const int32_t* tok_table;
   const AttnSeg* segs;
   const int32_t* cta_seg;
   const bf16* pool;
@@ -347,7 +346,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
           ok = fill(cur.gq, &tmQ, cur.sg.tok * HEADS);
           if (!ok) break;
         }
-        const int32_t* table = p.tables + p.tok_table[cur.sg.tok];
+        const int32_t* table = p.tables + cur.sg.table;
         const int row0 = table[(cur.sg.kv_begin >> 6) + cur.t] * TILE;
         ok = fill(cur.g, &tmKV, row0);
         cur.next(p.segs);
@@ -673,7 +672,7 @@ cudaError_t launch_attn_stream(const AttnArgs& a, cudaStream_t st) {
                        (uint64_t)a.d_qk * 2 * (uint64_t)a.q_rows, 64, HEADS, 1, &err))
     return cudaErrorInvalidValue;
   StreamParams p;
-  p.q_eff = a.q_eff; p.tables = a.tables; p.tok_table = a.tok_table; p.segs = a.segs; p.cta_seg = a.cta_seg;
+  p.q_eff = a.q_eff; p.tables = a.tables; p.segs = a.segs; p.cta_seg = a.cta_seg;
   p.part_m = a.part_m; p.part_l = a.part_l; p.part_o = a.part_o; p.d_status = a.d_status;
   p.pool = a.pool;
   p.d_qk = a.d_qk;

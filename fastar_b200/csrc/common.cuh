@@ -44,13 +44,16 @@ __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.laun
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 
-// One segment of the split-KV schedule: query token `tok` attends to cache rows
-// [kv_begin, kv_end) of its sequence and writes partial slot `part`.
+// One segment of the split-KV schedule: query token `tok` attends to rows [kv_begin, kv_end) of
+// the row space whose block table starts at entry `table` of the flat table array -- the raw rows
+// of its sequence, or (layers with a KV compressor) the compressed rows, which live in pages of
+// their own -- and writes partial slot `part`.
 struct AttnSeg {
   int32_t tok;
   int32_t kv_begin;
   int32_t kv_end;
   int32_t part;
+  int32_t table;
 };
 
 // Status word values written by kernels that give up a bounded wait.

@@ -139,8 +139,7 @@ void launch_q_prep(const QPrepArgs& a, cudaStream_t st);
 struct AttnArgs {
   const bf16* q_eff;        // [T * H, d_qk]
   const bf16* pool;         // [n_pages * page_tokens, row]
-  const int32_t* tables;    // flat block tables
-  const int32_t* tok_table; // [T] offset of the token's sequence table in `tables`
+  const int32_t* tables;    // flat block tables (a segment names where its table starts)
   const AttnSeg* segs;
   const int32_t* cta_seg;   // [n_ctas + 1] segment ranges of the persistent CTAs
   float* part_m;            // [P, H]
@@ -199,6 +198,32 @@ void launch_wait_selftest(int* d_status, uint32_t polls, cudaStream_t st);
 
 // The calling thread's last-error string (what fst_cuda_mla_last_error returns).
 void set_last_error(const char* msg);
+
+// V4 KV compressor (reference compress_token, src/fst_engine.cpp:3171-3318) for the new rows of a
+// layer call, one thread block per sequence, its rows in order: gate bias, window state, and on
+// every ratio-th position the pooled / normed / tail-rotated / E4M3-round-tripped row, written to
+// the compressed-row pages.
+struct CompressTok {
+  long long dst;   // element offset of the compressed row this token emits in the pool, or -1
+  int32_t pos;     // position of the token in its sequence
+  int32_t pad;
+};
+struct CompressStep {
+  int32_t tok0, q_len, slot;  // first row of the sequence in this call, rows, state slot of the sequence
+  int32_t pad;
+};
+struct CompressArgs {
+  const bf16* proj;          // [T, 2 * width]: wkv product then wgate product of every row
+  const float* ape;          // [ratio, width]
+  const bf16* norm;          // [kv_lora]
+  const float* lut;          // [T, rope] (cos, sin) of the compressed position of an emitting row
+  const CompressTok* toks;   // [T]
+  const CompressStep* steps; // [n_steps]
+  float* state;              // [slots][2][rows, width] window state (values, then scores)
+  bf16* pool;
+  int n_steps, ratio, width, kv_lora, rope;
+};
+void launch_compress(const CompressArgs& a, cudaStream_t st);
 
 void launch_zero_rows(bf16* pool, const long long* row_off, int n_rows, int row, cudaStream_t st);
 

@@ -316,7 +316,7 @@ __global__ void __launch_bounds__(256, 1) k_attn_simt(AttnArgs a) {
   unsigned char* s_tile = smem + (size_t)a.H * a.d_qk * 2;
   const AttnSeg seg = a.segs[blockIdx.x];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int32_t* table = a.tables + a.tok_table[seg.tok];
+  const int32_t* table = a.tables + seg.table;
 
   for (int h0 = 0; h0 < a.H; h0 += 8 * SIMT_HPW) {
     __syncthreads();
@@ -683,6 +683,123 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge_gathered(MergeGatheredA
 void launch_merge_gathered(const MergeGatheredArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
   launch_pdl(k_merge_gathered, dim3(a.T * a.H), dim3(a.n_parts <= 4 ? 128 : MERGE_THREADS), 0, st, 1, a);
+}
+
+// ---- V4 KV compressor ----------------------------------------------------------------------------
+// The 127 non-negative E4M3 values, ascending (reference init_e4m3_grid, src/fst_engine.cpp:3070-3083).
+__device__ __forceinline__ float e4m3_value(int i) {
+  const int e = (i >> 3) & 15, m = i & 7;
+  return e == 0 ? (float)m * 0.001953125f : ldexpf(1.0f + (float)m * 0.125f, e - 7);
+}
+// e4m3_roundtrip (3084-3100): the nearest grid value, ties to the even index.
+__device__ __forceinline__ float e4m3_roundtrip(float v) {
+  const float sign = v < 0.0f ? -1.0f : 1.0f;
+  const float ax = fminf(fabsf(v), 448.0f);
+  int lo = 0, hi = 126;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (e4m3_value(mid) <= ax) lo = mid; else hi = mid - 1;
+  }
+  int best = lo;
+  if (best < 126) {
+    const float bd = fabsf(ax - e4m3_value(best)), nd = fabsf(ax - e4m3_value(best + 1));
+    if (nd < bd || (nd == bd && ((best + 1) & 1) == 0 && (best & 1) != 0)) ++best;
+  }
+  return sign * e4m3_value(best);
+}
+
+// One block per sequence of the call; thread j owns dim j of the pooled row (kv_lora <= 1024).
+__global__ void __launch_bounds__(512) k_compress(CompressArgs a) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float s_out[];  // [kv_lora]
+  __shared__ float scratch[32];
+  const CompressStep st = a.steps[blockIdx.x];
+  const int ratio = a.ratio, width = a.width, hd = a.kv_lora;
+  const int rows = ratio == 4 ? 8 : ratio;
+  float* skv = a.state + (long long)st.slot * 2 * rows * width;
+  float* ssc = skv + (long long)rows * width;
+  for (int m = 0; m < st.q_len; ++m) {
+    const int t = st.tok0 + m;
+    const CompressTok tk = a.toks[t];
+    const int pos_mod = tk.pos % ratio;
+    const int row = ratio == 4 ? ratio + pos_mod : pos_mod;
+    // state write: the value row, and the gate row with its positional bias (3194-3202)
+    const bf16* pr = a.proj + (long long)t * 2 * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+      skv[(long long)row * width + j] = bf2f(pr[j]);
+      ssc[(long long)row * width + j] = bf2f(pr[width + j]) + a.ape[(long long)pos_mod * width + j];
+    }
+    __syncthreads();
+    if (((tk.pos + 1) % ratio) != 0) continue;  // (uniform over the block)
+    // per-dim softmax pool over the window rows, two lanes for ratio 4 (3206-3242)
+    float pooled = 0.0f;
+    const int j = threadIdx.x;
+    if (j < hd) {
+      float mx = -1e30f;
+      for (int r = 0; r < ratio; ++r) {
+        mx = fmaxf(mx, ssc[(long long)r * width + j]);
+        if (ratio == 4) mx = fmaxf(mx, ssc[(long long)(ratio + r) * width + hd + j]);
+      }
+      if (mx > -0.5e30f) {
+        float denom = 0.0f, sum = 0.0f;
+        for (int r = 0; r < ratio; ++r) {
+          const float wp = expf(ssc[(long long)r * width + j] - mx);
+          if (ratio == 4) {
+            const float wc = expf(ssc[(long long)(ratio + r) * width + hd + j] - mx);
+            denom += wp + wc;
+            sum += wp * skv[(long long)r * width + j];
+            sum += wc * skv[(long long)(ratio + r) * width + hd + j];
+          } else {
+            denom += wp;
+            sum += wp * skv[(long long)r * width + j];
+          }
+        }
+        pooled = denom > 0.0f ? sum / denom : 0.0f;
+      }
+    }
+    // RMS norm with the compressor's weight (3244-3250)
+    const float ss = block_sum(pooled * pooled, scratch);
+    const float rms = 1.0f / sqrtf(ss / (float)hd + 1e-6f);
+    if (j < hd) s_out[j] = pooled * rms * bf2f(a.norm[j]);
+    __syncthreads();
+    // RoPE on the tail at the compressed position (3252-3254): interleaved pairs
+    if (j < a.rope / 2) {
+      const float* lut = a.lut + (long long)t * a.rope;
+      const int k = hd - a.rope + 2 * j;
+      const float c = lut[2 * j], s = lut[2 * j + 1], x0 = s_out[k], x1 = s_out[k + 1];
+      s_out[k] = x0 * c - x1 * s;
+      s_out[k + 1] = x0 * s + x1 * c;
+    }
+    __syncthreads();
+    // E4M3 round trip of the nope part in blocks of 64 with a power-of-two scale (3256-3267)
+    float v = 0.0f;
+    if (j < hd) {
+      v = s_out[j];
+      if (j < hd - a.rope) {
+        const int b0 = j & ~63;
+        float amax = 0.0f;
+        for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(s_out[b0 + i]));
+        amax = fmaxf(amax, 1.0e-4f);
+        const float scale = ldexpf(1.0f, (int)ceilf(log2f(amax / 448.0f)));
+        v = e4m3_roundtrip(fminf(448.0f, fmaxf(-448.0f, v / scale))) * scale;
+      }
+      if (tk.dst >= 0) a.pool[tk.dst + j] = f2bf(v);
+    }
+    // window rotation, ratio 4 (3302-3317): the window just processed becomes the previous one
+    if (ratio == 4) {
+      for (int i = threadIdx.x; i < ratio * width; i += blockDim.x) {
+        skv[i] = skv[(long long)ratio * width + i];
+        ssc[i] = ssc[(long long)ratio * width + i];
+      }
+    }
+    __syncthreads();
+  }
+}
+
+void launch_compress(const CompressArgs& a, cudaStream_t st) {
+  if (a.n_steps <= 0) return;
+  launch_pdl(k_compress, dim3(a.n_steps), dim3(512), a.kv_lora * sizeof(float), st, 1, a);
 }
 
 // ---- bounded-wait self-test ----------------------------------------------------------------------

@@ -61,6 +61,34 @@ struct LayerW {
   bf16* attn_norm = nullptr;  // [hidden] or null: the norm in front of the layer
   float* sinks = nullptr;
   bool set = false;
+  // V4 KV compressor (reference LayerWeightsC cmp_*, include/fst_engine.h:172-180): 0 = none
+  int cmp_ratio = 0;
+  bf16* w_cmp_proj = nullptr;   // [2 * width, hidden]: wkv rows, then wgate rows
+  float* cmp_ape = nullptr;     // [ratio, width]
+  bf16* cmp_norm = nullptr;     // [kv_lora]
+  float* cmp_state = nullptr;   // [max_seqs][2][rows, width] window state per sequence (values, scores)
+  float* cmp_snap = nullptr;    // the same, saved by fst_cuda_mla_seq_snapshot
+  std::vector<int32_t> cmp_pos, cmp_pos_snap;  // per sequence: rows [0, cmp_pos) have gone through the compressor
+};
+
+// Layers fall into classes by their compress ratio (0: no compressor, 4, 128): the split-KV
+// schedule of a plan differs between classes, because compressed rows are further columns.
+constexpr int N_CLASSES = 3;
+inline int class_of_ratio(int ratio) { return ratio == 0 ? 0 : ratio == 4 ? 1 : 2; }
+constexpr int CLASS_RATIO[N_CLASSES] = {0, 4, 128};
+
+struct Sched {
+  bool built = false;
+  int32_t *d_cta_seg = nullptr, *d_tok_part = nullptr;
+  AttnSeg* d_segs = nullptr;
+  int n_segs = 0, n_parts = 0, n_ctas = 0;
+  long long kv_rows = 0;
+  int max_tok_parts = 0, min_tok_parts = 0, n_single_part = 0;
+  // what the compressor kernel of this class reads (classes 1, 2)
+  CompressTok* d_ctoks = nullptr;
+  CompressStep* d_csteps = nullptr;
+  float* d_lut_cmp = nullptr;
+  int n_csteps = 0;
 };
 
 constexpr int ATTN_TILE = 128;      // split boundaries are multiples of this many cached rows
@@ -94,8 +122,13 @@ struct FstMlaCtx {
   float *d_part_m = nullptr, *d_part_l = nullptr, *d_part_o = nullptr;
   int max_parts = 0;
   bool fused_merge = true;       // the attention kernel finishes single-partial tokens itself
-  int max_tok_parts = 0, min_tok_parts = 0;  // most / fewest partials of one token in the current plan
-  int n_single_part = 0;                     // tokens of the current plan with exactly one partial
+  Sched sched[N_CLASSES];        // the current plan's schedule per layer class
+  int info_class = 0;            // class of the layer that ran last (plan_info reports its schedule)
+  bool has_cmp = false;          // some layer has a KV compressor
+  int cmp_min_ratio = 0;         // the smallest compress ratio in use: sizes the compressed-row pages
+  std::vector<std::vector<int32_t>> comp_tables;  // per sequence: pages of its compressed rows (all layers)
+  std::vector<int32_t> snap_len;                  // per sequence: length at its snapshot, or -1
+  bf16* d_cproj = nullptr;       // [T, 2 * width] compressor projections of a call
   uint16_t* h_pinned = nullptr;  // [max_tokens, hidden] staging for the host-buffer entry point
   int* d_status = nullptr;
   const bf16* out_src = nullptr;  // where the last layer call left its output rows
@@ -108,8 +141,7 @@ struct FstMlaCtx {
   // plan (device)
   float* d_lut_k[2] = {nullptr, nullptr};  // [T, rope] (cos, sin) per RoPE kind that some layer uses
   long long* d_dst = nullptr;
-  int32_t *d_tables = nullptr, *d_tok_table = nullptr, *d_cta_seg = nullptr, *d_tok_part = nullptr;
-  AttnSeg* d_segs = nullptr;
+  int32_t* d_tables = nullptr;
   int tables_cap = 0, segs_cap = 0;
   // the plan arrays above are slices of one device blob, filled through one pinned host blob
   // with a single copy per plan
@@ -123,7 +155,7 @@ struct FstMlaCtx {
   // plan (host): the per-token arrays live here between the two phases of a plan
   std::vector<float> pl_lut[2];
   std::vector<long long> pl_dst;
-  std::vector<int32_t> pl_tok_table, pl_tables, pl_kvlen, pl_kvlo, pl_tok_part;
+  std::vector<int32_t> pl_tok_table, pl_tables, pl_kvlen, pl_kvlo, pl_tok_ctable, pl_tok_step;
   std::vector<FstMlaSeqStep> pl_steps;
   int pl_causal = 0;
   size_t pl_off_b = 0;          // where the second part of the blob starts
@@ -136,8 +168,7 @@ struct FstMlaCtx {
   int32_t window = 0;  // sliding window applied by fst_cuda_mla_forward (0: none)
   int64_t plans_built = 0, plans_reused = 0;
   bool planned = false;
-  int T = 0, n_segs = 0, n_parts = 0, n_ctas = 0;
-  long long kv_rows = 0;
+  int T = 0;
 
   // split-KV across GPUs: the exchange of the per-GPU partials
   void* nccl_comm = nullptr;         // ncclComm_t
@@ -243,6 +274,11 @@ void rope_kinds(const FstMlaCtx* c, bool need[2]) {
   for (int8_t k : c->layer_yarn) need[k ? 1 : 0] = true;
 }
 const float* lut_of(const FstMlaCtx* c, int lid) { return c->d_lut_k[c->layer_yarn[lid] ? 1 : 0]; }
+int class_of(const FstMlaCtx* c, int lid) { return class_of_ratio(c->layers[lid].cmp_ratio); }
+Sched& sched_of(FstMlaCtx* c, int lid) { return c->sched[class_of(c, lid)]; }
+int cmp_width(const FstMlaCtx* c, int ratio) { return ratio == 4 ? 2 * c->d.kv_lora : c->d.kv_lora; }
+int cmp_rows(int ratio) { return ratio == 4 ? 8 : ratio; }
+size_t cmp_slot_floats(const FstMlaCtx* c, int ratio) { return (size_t)2 * cmp_rows(ratio) * cmp_width(c, ratio); }
 
 bool seq_ok(const FstMlaCtx* c, int32_t s) { return s >= 0 && s < c->cfg.max_seqs && c->live[s]; }
 
@@ -252,8 +288,19 @@ int reserve_pages(FstMlaCtx* c, int32_t seq, int32_t n_tokens) {
   if (need > t.size() && need - t.size() > c->free_pages.size())
     return fail(FST_MLA_ERR_PAGES, "page pool exhausted: sequence %d needs %zu more pages, %zu free", seq,
                 need - t.size(), c->free_pages.size());
+  // layers with a KV compressor keep one compressed row per `ratio` rows, in pages of their own
+  auto& ct = c->comp_tables[seq];
+  const size_t need_c = c->has_cmp ? ((size_t)(n_tokens / c->cmp_min_ratio) + c->cfg.page_tokens - 1) / c->cfg.page_tokens : 0;
+  const size_t more = (need > t.size() ? need - t.size() : 0) + (need_c > ct.size() ? need_c - ct.size() : 0);
+  if (more > c->free_pages.size())
+    return fail(FST_MLA_ERR_PAGES, "page pool exhausted: sequence %d needs %zu more pages, %zu free", seq, more,
+                c->free_pages.size());
   while (t.size() < need) {
     t.push_back(c->free_pages.back());
+    c->free_pages.pop_back();
+  }
+  while (ct.size() < need_c) {
+    ct.push_back(c->free_pages.back());
     c->free_pages.pop_back();
   }
   c->lens[seq] = std::max(c->lens[seq], n_tokens);
@@ -352,15 +399,15 @@ AttnArgs attn_args(FstMlaCtx* c, int lid, const bf16* q_eff, bool may_fuse = fal
   a.q_eff = q_eff;
   a.pool = c->pools[lid];
   a.tables = c->d_tables;
-  a.tok_table = c->d_tok_table;
-  a.segs = c->d_segs;
-  a.cta_seg = c->d_cta_seg;
+  const Sched& S = sched_of(c, lid);
+  a.segs = S.d_segs;
+  a.cta_seg = S.d_cta_seg;
   a.part_m = c->d_part_m;
   a.part_l = c->d_part_l;
   a.part_o = c->d_part_o;
   a.d_status = c->d_status;
-  a.n_segs = c->n_segs;
-  a.n_ctas = c->n_ctas;
+  a.n_segs = S.n_segs;
+  a.n_ctas = S.n_ctas;
   a.H = c->d.H;
   a.d_qk = c->d.d_qk;
   a.d_v = c->d.d_v;
@@ -369,9 +416,9 @@ AttnArgs attn_args(FstMlaCtx* c, int lid, const bf16* q_eff, bool may_fuse = fal
   a.pool_rows = (long long)c->cfg.n_pages * c->cfg.page_tokens;
   a.q_rows = (long long)c->T * c->d.H;
   a.scale = c->cfg.softmax_scale;
-  if (may_fuse && c->fused_merge && c->n_single_part > 0) {
+  if (may_fuse && c->fused_merge && S.n_single_part > 0) {
     a.direct_single = true;
-    a.tok_part = c->d_tok_part;
+    a.tok_part = S.d_tok_part;
     a.o_lat = c->d_olat;
     a.sinks = c->d.v4 ? c->layers[lid].sinks : nullptr;
     a.lut = lut_of(c, lid);
@@ -385,7 +432,8 @@ AttnArgs attn_args(FstMlaCtx* c, int lid, const bf16* q_eff, bool may_fuse = fal
 // token that has exactly one partial; the merge that follows skips them.
 int run_attention(FstMlaCtx* c, int lid, const bf16* q_eff, bool* direct = nullptr) {
   if (direct) *direct = false;
-  if (c->n_segs == 0) return FST_MLA_OK;
+  c->info_class = class_of(c, lid);
+  if (sched_of(c, lid).n_segs == 0) return FST_MLA_OK;
   AttnArgs a = attn_args(c, lid, q_eff, direct != nullptr);
   const bool tc_ok = attn_stream_supported(a);
   if (!(c->cfg.attn_impl != FST_MLA_IMPL_SIMT && tc_ok)) a.direct_single = false;
@@ -419,6 +467,30 @@ int run_front(FstMlaCtx* c, int lid, const bf16* h_in) {
   }
   if (!c->compress_done && (rc = run_gemm(c, plain_gemm(h_in, w.w_cmp, c->d_cmp, T, d.cmp_n, d.hidden)))) return rc;
   c->compress_done = false;
+  if (w.cmp_ratio) {
+    // KV compressor (reference 3545-3568): the rows' two projections as one GEMM, then the state
+    // machine of every sequence, its rows in order; compressed rows land in their pages before the
+    // attention reads them
+    const Sched& S = sched_of(c, lid);
+    const int width = cmp_width(c, w.cmp_ratio);
+    for (const FstMlaSeqStep& st : c->pl_steps) {
+      if (st.q_len == 0) continue;
+      if (!st.append) return fail(FST_MLA_ERR_STATE, "layer %d has a KV compressor: its sequences must own their new rows", lid);
+      if (w.cmp_pos[st.seq] != st.pos0)
+        return fail(FST_MLA_ERR_STATE,
+                    "layer %d: the compressor of sequence %d has seen rows [0, %d), the call starts at row %d "
+                    "(rows must arrive in order; fst_cuda_mla_seq_snapshot / _truncate undo a block)",
+                    lid, st.seq, w.cmp_pos[st.seq], st.pos0);
+    }
+    if ((rc = run_gemm(c, plain_gemm(h_in, w.w_cmp_proj, c->d_cproj, T, 2 * width, d.hidden)))) return rc;
+    CompressArgs ca;
+    ca.proj = c->d_cproj; ca.ape = w.cmp_ape; ca.norm = w.cmp_norm; ca.lut = S.d_lut_cmp; ca.toks = S.d_ctoks;
+    ca.steps = S.d_csteps; ca.state = w.cmp_state; ca.pool = c->pools[lid]; ca.n_steps = S.n_csteps;
+    ca.ratio = w.cmp_ratio; ca.width = width; ca.kv_lora = d.kv_lora; ca.rope = d.rope;
+    launch_compress(ca, c->stream);
+    c->launches += 1;
+    for (const FstMlaSeqStep& st : c->pl_steps) c->layers[lid].cmp_pos[st.seq] = st.pos0 + st.q_len;
+  }
   prof_mark(c, FST_MLA_K_NORM_APPEND);
   NormAppendArgs na;
   na.cmp = c->d_cmp; na.q_norm = w.q_norm; na.kv_norm = w.kv_norm; na.lut = lut_of(c, lid);
@@ -493,14 +565,15 @@ int run_back(FstMlaCtx* c, int lid, bf16* h_out) {
 // sink-only rows from the merge kernel).
 int run_merge_local(FstMlaCtx* c, int lid, int mode, float* rank_partial, bool skip_single = false) {
   const Dims& d = c->d;
-  if (skip_single && c->min_tok_parts == 1 && c->max_tok_parts == 1) return FST_MLA_OK;
+  const Sched& S = sched_of(c, lid);
+  if (skip_single && S.min_tok_parts == 1 && S.max_tok_parts == 1) return FST_MLA_OK;
   MergeArgs m;
   m.skip_single = skip_single ? 1 : 0;
-  m.part_m = c->d_part_m; m.part_l = c->d_part_l; m.part_o = c->d_part_o; m.tok_part = c->d_tok_part;
+  m.part_m = c->d_part_m; m.part_l = c->d_part_l; m.part_o = c->d_part_o; m.tok_part = S.d_tok_part;
   m.sinks = (d.v4 && mode == 0) ? c->layers[lid].sinks : nullptr;
   m.lut = lut_of(c, lid); m.o_lat = c->d_olat; m.rank_partial = rank_partial;
   m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope; m.inv_rope = d.v4 ? 1 : 0; m.mode = mode;
-  m.threads = c->n_parts <= 6 * c->T ? 128 : 256;
+  m.threads = S.n_parts <= 6 * c->T ? 128 : 256;
   launch_merge(m, c->stream);
   c->launches += 1;
   return FST_MLA_OK;
@@ -568,6 +641,8 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
   for (int i = c.n_pages - 1; i >= 0; --i) x->free_pages.push_back(i);
   for (int i = c.max_seqs - 1; i >= 0; --i) x->free_seqs.push_back(i);
   x->tables.resize(c.max_seqs);
+  x->comp_tables.resize(c.max_seqs);
+  x->snap_len.assign(c.max_seqs, -1);
   x->lens.assign(c.max_seqs, 0);
   x->live.assign(c.max_seqs, 0);
   *out = x;  // from here on destroy() cleans up after a failure
@@ -580,7 +655,9 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
     if (!rc && cudaMemset(x->pools[l], 0, pool_elems * sizeof(bf16)) != cudaSuccess)
       rc = fail(FST_MLA_ERR_CUDA, "cudaMemset(pool) failed");
   }
-  x->max_parts = x->n_sm + (int)T;
+  // partials: one per thread block plus one per stream of tiles that starts inside a block's run; a
+  // token has one stream, two in layers with a KV compressor (V4 form only)
+  x->max_parts = x->n_sm + (int)T * (d.v4 ? 2 : 1);
   if (!rc) rc = dev_alloc(&x->d_h, T * d.hidden);
   if (!rc) rc = dev_alloc(&x->d_cmp, T * d.cmp_n);
   if (!rc) rc = dev_alloc(&x->d_an, T * d.hidden);
@@ -591,14 +668,19 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
   if (!rc) rc = dev_alloc(&x->d_olat, T * d.H * d.d_v);
   if (!rc) rc = dev_alloc(&x->d_low, T * d.low);
   if (!rc) rc = dev_alloc(&x->d_out, T * d.hidden);
+  if (!rc && d.v4) rc = dev_alloc(&x->d_cproj, T * 4 * d.kv_lora);
   if (!rc) rc = dev_alloc(&x->d_part_m, (size_t)x->max_parts * d.H);
   if (!rc) rc = dev_alloc(&x->d_part_l, (size_t)x->max_parts * d.H);
   if (!rc) rc = dev_alloc(&x->d_part_o, (size_t)x->max_parts * d.H * d.d_v);
   x->segs_cap = x->max_parts;
   x->tables_cap = c.n_pages + c.max_seqs;
-  x->plan_cap = 2 * T * d.rope * sizeof(float) + T * sizeof(long long) + (2 * T + 1) * sizeof(int32_t) +
-                ((size_t)x->n_sm + 1) * sizeof(int32_t) + (size_t)x->segs_cap * sizeof(AttnSeg) +
-                (size_t)x->tables_cap * sizeof(int32_t) + 8 * 256;
+  // first part: two RoPE tables, append addresses, per compressed class the compressor's inputs;
+  // second part: per class (token partial ranges, block ranges, segments), then the block tables
+  x->plan_cap = 2 * T * d.rope * sizeof(float) + T * sizeof(long long) +
+                2 * (T * sizeof(CompressTok) + (size_t)c.max_seqs * sizeof(CompressStep) + T * d.rope * sizeof(float)) +
+                N_CLASSES * ((T + 1) * sizeof(int32_t) + ((size_t)x->n_sm + 1) * sizeof(int32_t) +
+                             (size_t)x->segs_cap * sizeof(AttnSeg)) +
+                (size_t)x->tables_cap * sizeof(int32_t) + 32 * 256;
   if (!rc) rc = dev_alloc(&x->d_plan, x->plan_cap);
   if (!rc && cudaHostAlloc((void**)&x->h_plan, x->plan_cap, cudaHostAllocDefault) != cudaSuccess)
     rc = fail(FST_MLA_ERR_CUDA, "cudaHostAlloc(plan) failed");
@@ -633,7 +715,9 @@ void fst_cuda_mla_destroy(FstMlaCtx* c) {
   for (auto& l : c->layers) {
     cudaFree(l.w_cmp); cudaFree(l.wq_b); cudaFree(l.wkv_b); cudaFree(l.wo_a); cudaFree(l.wo_b);
     cudaFree(l.q_norm); cudaFree(l.kv_norm); cudaFree(l.sinks); cudaFree(l.attn_norm);
+    cudaFree(l.w_cmp_proj); cudaFree(l.cmp_ape); cudaFree(l.cmp_norm); cudaFree(l.cmp_state); cudaFree(l.cmp_snap);
   }
+  cudaFree(c->d_cproj);
   for (auto p : c->pools) cudaFree(p);
   cudaFree(c->d_an);
   cudaFree(c->d_h); cudaFree(c->d_cmp); cudaFree(c->d_qc); cudaFree(c->d_kvnew); cudaFree(c->d_qfull);
@@ -749,6 +833,86 @@ int fst_cuda_mla_set_layer_rope(FstMlaCtx* c, int lid, int32_t yarn) {
   return FST_MLA_OK;
 }
 
+int fst_cuda_mla_set_layer_compressor(FstMlaCtx* c, int lid, const FstMlaCompressor* w) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (lid < 0 || lid >= c->cfg.n_layers) return fail(FST_MLA_ERR_ARG, "layer %d out of range", lid);
+  if (!c->d.v4) return fail(FST_MLA_ERR_ARG, "the KV compressor belongs to the V4 form (512-wide rows)");
+  const int ratio = w ? w->ratio : 0;
+  if (ratio != 0 && ratio != 4 && ratio != 128) return fail(FST_MLA_ERR_ARG, "compress ratio %d (0, 4 or 128)", ratio);
+  if (ratio && (!w->wkv || !w->wgate || !w->ape || !w->norm)) return fail(FST_MLA_ERR_ARG, "a compressor tensor is NULL");
+  for (int s = 0; s < c->cfg.max_seqs; ++s)
+    if (c->live[s] && c->lens[s] > 0)
+      return fail(FST_MLA_ERR_STATE, "set the compressors before any sequence holds rows");
+  CU(cudaSetDevice(c->cfg.device));
+  LayerW& L = c->layers[lid];
+  cudaFree(L.w_cmp_proj); cudaFree(L.cmp_ape); cudaFree(L.cmp_norm); cudaFree(L.cmp_state); cudaFree(L.cmp_snap);
+  L.w_cmp_proj = nullptr; L.cmp_ape = nullptr; L.cmp_norm = nullptr; L.cmp_state = nullptr; L.cmp_snap = nullptr;
+  L.cmp_ratio = ratio;
+  if (ratio) {
+    const Dims& d = c->d;
+    const size_t width = cmp_width(c, ratio), slot = cmp_slot_floats(c, ratio);
+    int rc = dev_alloc(&L.w_cmp_proj, 2 * width * d.hidden);
+    if (!rc) rc = dev_alloc(&L.cmp_ape, (size_t)ratio * width);
+    if (!rc) rc = dev_alloc(&L.cmp_norm, (size_t)d.kv_lora);
+    if (!rc) rc = dev_alloc(&L.cmp_state, slot * c->cfg.max_seqs);
+    if (rc) return rc;
+    CU(cudaMemcpy(L.w_cmp_proj, w->wkv, width * d.hidden * 2, cudaMemcpyHostToDevice));
+    CU(cudaMemcpy(L.w_cmp_proj + width * d.hidden, w->wgate, width * d.hidden * 2, cudaMemcpyHostToDevice));
+    CU(cudaMemcpy(L.cmp_ape, w->ape, (size_t)ratio * width * sizeof(float), cudaMemcpyHostToDevice));
+    CU(cudaMemcpy(L.cmp_norm, w->norm, (size_t)d.kv_lora * 2, cudaMemcpyHostToDevice));
+    CU(cudaMemset(L.cmp_state, 0, slot * c->cfg.max_seqs * sizeof(float)));
+    L.cmp_pos.assign(c->cfg.max_seqs, 0);
+    L.cmp_pos_snap.assign(c->cfg.max_seqs, 0);
+  }
+  c->has_cmp = false;
+  c->cmp_min_ratio = 0;
+  for (const LayerW& l : c->layers)
+    if (l.cmp_ratio) {
+      c->has_cmp = true;
+      c->cmp_min_ratio = c->cmp_min_ratio ? std::min(c->cmp_min_ratio, l.cmp_ratio) : l.cmp_ratio;
+    }
+  c->planned = false;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_seq_snapshot(FstMlaCtx* c, int32_t seq) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (!seq_ok(c, seq)) return fail(FST_MLA_ERR_ARG, "sequence %d is not allocated", seq);
+  CU(cudaSetDevice(c->cfg.device));
+  for (LayerW& l : c->layers)
+    if (l.cmp_ratio) {
+      const size_t n = cmp_slot_floats(c, l.cmp_ratio);
+      if (!l.cmp_snap) {
+        int rc = dev_alloc(&l.cmp_snap, n * c->cfg.max_seqs);
+        if (rc) return rc;
+      }
+      CU(cudaMemcpyAsync(l.cmp_snap + (size_t)seq * n, l.cmp_state + (size_t)seq * n, n * sizeof(float),
+                         cudaMemcpyDeviceToDevice, c->stream));
+      l.cmp_pos_snap[seq] = l.cmp_pos[seq];
+    }
+  c->snap_len[seq] = c->lens[seq];
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_cmp_read(FstMlaCtx* c, int lid, int32_t seq, uint16_t* rows, int32_t cap, int32_t* n_out) {
+  if (!c || !n_out) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (lid < 0 || lid >= c->cfg.n_layers) return fail(FST_MLA_ERR_ARG, "layer %d out of range", lid);
+  if (!seq_ok(c, seq)) return fail(FST_MLA_ERR_ARG, "sequence %d is not allocated", seq);
+  const LayerW& L = c->layers[lid];
+  const int n = L.cmp_ratio ? L.cmp_pos[seq] / L.cmp_ratio : 0;
+  *n_out = n;
+  if (!rows) return FST_MLA_OK;
+  if (cap < n) return fail(FST_MLA_ERR_ARG, "%d compressed rows, room for %d", n, cap);
+  CU(cudaSetDevice(c->cfg.device));
+  const int pt = c->cfg.page_tokens, row = c->d.row;
+  for (int r = 0; r < n; ++r) {
+    const bf16* src = c->pools[lid] + ((long long)c->comp_tables[seq][r / pt] * pt + r % pt) * row;
+    CU(cudaMemcpyAsync(rows + (size_t)r * row, src, (size_t)row * 2, cudaMemcpyDeviceToHost, c->stream));
+  }
+  CU(cudaStreamSynchronize(c->stream));
+  return FST_MLA_OK;
+}
+
 /* ---- paged cache ---------------------------------------------------------------------- */
 int fst_cuda_mla_seq_alloc(FstMlaCtx* c, int32_t* seq_out) {
   if (!c || !seq_out) return fail(FST_MLA_ERR_ARG, "null argument");
@@ -758,6 +922,18 @@ int fst_cuda_mla_seq_alloc(FstMlaCtx* c, int32_t* seq_out) {
   c->live[s] = 1;
   c->lens[s] = 0;
   c->tables[s].clear();
+  c->comp_tables[s].clear();
+  c->snap_len[s] = -1;
+  if (c->has_cmp) {
+    // a new sequence starts with an empty compressor window (reset_compressor_state, reference 3160-3169)
+    CU(cudaSetDevice(c->cfg.device));
+    for (LayerW& l : c->layers)
+      if (l.cmp_ratio) {
+        const size_t n = cmp_slot_floats(c, l.cmp_ratio);
+        CU(cudaMemsetAsync(l.cmp_state + (size_t)s * n, 0, n * sizeof(float), c->stream));
+        l.cmp_pos[s] = 0;
+      }
+  }
   *seq_out = s;
   c->planned = false;
   return FST_MLA_OK;
@@ -790,6 +966,31 @@ int fst_cuda_mla_seq_truncate(FstMlaCtx* c, int32_t seq, int32_t n_tokens) {
   while (t.size() > keep) {
     c->free_pages.push_back(t.back());
     t.pop_back();
+  }
+  if (c->has_cmp) {
+    // The compressed rows emitted by the dropped rows go with them.  The window state comes back
+    // from the snapshot taken at this length (the reference restores cmp_snap, 6149-6152); without
+    // one the state keeps what the dropped rows wrote, which only a truncation to 0 makes harmless.
+    const size_t keep_c = ((size_t)(n_tokens / c->cmp_min_ratio) + c->cfg.page_tokens - 1) / c->cfg.page_tokens;
+    auto& ct = c->comp_tables[seq];
+    while (ct.size() > keep_c) {
+      c->free_pages.push_back(ct.back());
+      ct.pop_back();
+    }
+    const bool restore = c->snap_len[seq] == n_tokens;
+    for (LayerW& l : c->layers)
+      if (l.cmp_ratio && l.cmp_pos[seq] > n_tokens) {
+        const size_t n = cmp_slot_floats(c, l.cmp_ratio);
+        if (restore && l.cmp_snap) {
+          CU(cudaMemcpyAsync(l.cmp_state + (size_t)seq * n, l.cmp_snap + (size_t)seq * n, n * sizeof(float),
+                             cudaMemcpyDeviceToDevice, c->stream));
+          l.cmp_pos[seq] = l.cmp_pos_snap[seq];
+        } else {
+          if (n_tokens == 0) CU(cudaMemsetAsync(l.cmp_state + (size_t)seq * n, 0, n * sizeof(float), c->stream));
+          l.cmp_pos[seq] = n_tokens;
+        }
+      }
+    if (n_tokens < c->snap_len[seq]) c->snap_len[seq] = -1;
   }
   c->lens[seq] = n_tokens;
   c->planned = false;
@@ -828,6 +1029,13 @@ int fst_cuda_mla_reset(FstMlaCtx* c) {
   for (int i = c->cfg.n_pages - 1; i >= 0; --i) c->free_pages.push_back(i);
   for (int i = c->cfg.max_seqs - 1; i >= 0; --i) c->free_seqs.push_back(i);
   for (auto& t : c->tables) t.clear();
+  for (auto& t : c->comp_tables) t.clear();
+  std::fill(c->snap_len.begin(), c->snap_len.end(), -1);
+  for (LayerW& l : c->layers)
+    if (l.cmp_ratio) {
+      CU(cudaMemsetAsync(l.cmp_state, 0, cmp_slot_floats(c, l.cmp_ratio) * c->cfg.max_seqs * sizeof(float), c->stream));
+      std::fill(l.cmp_pos.begin(), l.cmp_pos.end(), 0);
+    }
   std::fill(c->lens.begin(), c->lens.end(), 0);
   std::fill(c->live.begin(), c->live.end(), 0);
   const size_t bytes = (size_t)c->cfg.n_pages * c->cfg.page_tokens * c->d.row * sizeof(bf16);
@@ -965,17 +1173,22 @@ int plan_tokens_part(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, i
   for (int k = 0; k < 2; ++k) c->pl_lut[k].resize(need[k] ? (size_t)T * d.rope : 0);
   dst.resize(T);
   tok_table.resize(T);
+  c->pl_tok_ctable.resize(T);
+  c->pl_tok_step.resize(T);
   kvlen.resize(T);
   kvlo.resize(T);
   tables.clear();
-  c->pl_tok_part.assign(T + 1, 0);
   int t = 0;
   for (int b = 0; b < n_seqs; ++b) {
     const FstMlaSeqStep& s = steps[b];
     const int toff = (int)tables.size();
     tables.insert(tables.end(), c->tables[s.seq].begin(), c->tables[s.seq].end());
+    const int ctoff = (int)tables.size();  // the pages of the sequence's compressed rows
+    tables.insert(tables.end(), c->comp_tables[s.seq].begin(), c->comp_tables[s.seq].end());
     const int rp0 = s.rope_pos0 >= 0 ? s.rope_pos0 : s.pos0;
     for (int i = 0; i < s.q_len; ++i, ++t) {
+      c->pl_tok_ctable[t] = ctoff;
+      c->pl_tok_step[t] = b;
       for (int k = 0; k < 2; ++k)
         if (need[k]) memcpy(&c->pl_lut[k][(size_t)t * d.rope], lut_row_cached(c, k, rp0 + i), (size_t)d.rope * sizeof(float));
       dst[t] = s.append ? row_offset(c, s.seq, s.pos0 + i) : -1;
@@ -1006,6 +1219,44 @@ int plan_tokens_part(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, i
   for (int k = 0; k < 2; ++k)
     c->d_lut_k[k] = need[k] ? reinterpret_cast<float*>(put(c->pl_lut[k].data(), c->pl_lut[k].size() * sizeof(float))) : nullptr;
   c->d_dst = reinterpret_cast<long long*>(put(dst.data(), (size_t)T * sizeof(long long)));
+  // what the compressor kernels read, per class of compressed layers present
+  for (int k = 1; k < N_CLASSES; ++k) {
+    Sched& S = c->sched[k];
+    S.d_ctoks = nullptr;
+    S.n_csteps = 0;
+    bool present = false;
+    int kind = 0;
+    for (int l = 0; l < c->cfg.n_layers; ++l)
+      if (c->layers[l].cmp_ratio == CLASS_RATIO[k]) {
+        present = true;
+        kind = c->layer_yarn[l] ? 1 : 0;
+      }
+    if (!present) continue;
+    const int ratio = CLASS_RATIO[k], pt = c->cfg.page_tokens;
+    std::vector<CompressTok> ctoks(T);
+    std::vector<CompressStep> csteps;
+    std::vector<float> lut_cmp((size_t)T * d.rope, 0.0f);
+    int tt = 0;
+    for (int b = 0; b < n_seqs; ++b) {
+      const FstMlaSeqStep& st = steps[b];
+      if (st.q_len > 0) csteps.push_back(CompressStep{tt, st.q_len, st.seq, 0});
+      for (int i = 0; i < st.q_len; ++i, ++tt) {
+        const int pos = st.pos0 + i;
+        ctoks[tt] = CompressTok{-1, pos, 0};
+        if (st.append && (pos + 1) % ratio == 0) {
+          // compressed row number (pos + 1) / ratio - 1, rotated at position pos + 1 - ratio (3252-3254)
+          const int cr = (pos + 1) / ratio - 1;
+          ctoks[tt].dst = ((long long)c->comp_tables[st.seq][cr / pt] * pt + cr % pt) * d.row;
+          memcpy(&lut_cmp[(size_t)tt * d.rope], lut_row_cached(c, kind, pos + 1 - ratio), (size_t)d.rope * sizeof(float));
+        }
+      }
+    }
+    S.d_ctoks = reinterpret_cast<CompressTok*>(put(ctoks.data(), ctoks.size() * sizeof(CompressTok)));
+    S.d_csteps = reinterpret_cast<CompressStep*>(put(csteps.data(), csteps.size() * sizeof(CompressStep)));
+    S.d_lut_cmp = reinterpret_cast<float*>(put(lut_cmp.data(), lut_cmp.size() * sizeof(float)));
+    S.n_csteps = (int)csteps.size();
+  }
+  if (off > c->plan_cap) return fail(FST_MLA_ERR_CAPACITY, "plan blob overflow");
   c->pl_off_b = off;
   c->front_uploaded = upload_now && off > 0;
   if (c->front_uploaded) {
@@ -1015,98 +1266,153 @@ int plan_tokens_part(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, i
   return FST_MLA_OK;
 }
 
-// The second part: schedule and block tables.  on_copy_stream: upload it beside the kernels that
-// already run on the context's stream (which then waits for it); else one copy of the whole blob
-// (or of the second part, if the first went ahead) on the context's stream.
-int plan_schedule_part(FstMlaCtx* c, bool on_copy_stream) {
-  const int T = c->T;
-  std::vector<int32_t>&tok_table = c->pl_tok_table, &tables = c->pl_tables, &kvlen = c->pl_kvlen, &kvlo = c->pl_kvlo,
-      &tok_part = c->pl_tok_part;
+// One stream of cache tiles in the schedule: a query token's raw rows [lo, hi) of the table that
+// starts at `table`, or its visible compressed rows.  A token's streams are adjacent.
+struct TileStream {
+  int32_t tok, table, lo, hi;
+};
 
-  // split-KV schedule: the concatenated tiles of all query tokens are cut into n_ctas contiguous
-  // runs of about equal COST; a run that crosses a token boundary yields one segment (and one
-  // partial) per token it touches.  The unit is a cache page where pages hold 64 tokens, else
-  // ATTN_TILE rows.  Cost, in half units: 2 per tile plus SEG_COST2 per segment -- a segment
-  // pays for its Q_eff block (one ring slot), refilling the pipeline and writing its partial
-  // (measured inside the pipelined layer: about three 64-token tiles of the streaming kernel).
+// The split-KV schedule of one layer class.  The concatenated tiles of all streams are cut into
+// n_ctas contiguous runs of about equal COST; a run that crosses a stream boundary yields one segment
+// (and one partial) per stream it touches.  The unit is a cache page where pages hold 64 tokens,
+// else ATTN_TILE rows.  Cost, in half units: 2 per tile plus SEG_COST2 per segment -- a segment
+// pays for its Q_eff block (one ring slot), refilling the pipeline and writing its partial
+// (measured inside the pipelined layer: about three 64-token tiles of the streaming kernel).
+void cut_schedule(const FstMlaCtx* c, const std::vector<TileStream>& streams, int T, std::vector<AttnSeg>* segs_out,
+                  std::vector<int32_t>* cta_seg_out, std::vector<int32_t>* tok_part_out, long long* kv_rows_out) {
   const int unit = c->cfg.page_tokens == 64 ? 64 : ATTN_TILE;
   const long long SEG_COST2 = unit == 64 ? 6 : 5;
+  const int n_streams = (int)streams.size();
   long long total_tiles = 0, kv_rows = 0, n_nonempty = 0;
   // tiles are counted from the tile that holds the first visible row
-  auto tile0_of = [&](int i) { return kvlo[i] / unit; };
-  auto tiles_of = [&](int i) { return (kvlen[i] + unit - 1) / unit - tile0_of(i); };
-  for (int i = 0; i < T; ++i) {
+  auto tile0_of = [&](int i) { return streams[i].lo / unit; };
+  auto tiles_of = [&](int i) { return (streams[i].hi + unit - 1) / unit - tile0_of(i); };
+  for (int i = 0; i < n_streams; ++i) {
     total_tiles += tiles_of(i);
-    kv_rows += kvlen[i] - kvlo[i];
-    n_nonempty += kvlen[i] > 0;
+    kv_rows += streams[i].hi - streams[i].lo;
+    n_nonempty += streams[i].hi > 0;
   }
-  const int max_ctas = c->n_sm;
-  const int n_ctas = (int)std::min<long long>(max_ctas, std::max<long long>(total_tiles, 1));
-  std::vector<AttnSeg> segs;
-  std::vector<int32_t> cta_seg(n_ctas + 1, 0);
-  {
-    int tok = 0, tile_in_tok = 0, part = 0;
-    tok_part[0] = 0;
-    auto skip_empty = [&]() {
-      while (tok < T && tile_in_tok >= tiles_of(tok)) {
-        ++tok;
-        tile_in_tok = 0;
-        if (tok <= T) tok_part[tok] = part;
-      }
-    };
-    skip_empty();
-    long long tiles_left = total_tiles, toks_left = n_nonempty;  // tokens not yet started
-    for (int k = 0; k < n_ctas; ++k) {
-      cta_seg[k] = (int)segs.size();
-      const bool last = k == n_ctas - 1;
-      // what is left, shared equally among the CTAs that are left: the tiles, a segment for
-      // every token still to start (and for the one this CTA resumes), and one more segment
-      // for every later CTA, which will most likely resume a token
-      const long long mid = tile_in_tok > 0 ? 1 : 0;
-      const long long left2 = 2 * tiles_left + SEG_COST2 * (toks_left + mid + (n_ctas - k - 1));
-      long long budget2 = left2 / (n_ctas - k);
-      while (tok < T) {
-        long long room = last ? (1ll << 40) : (budget2 - SEG_COST2) / 2;  // tiles that still fit
-        if (room < 1) {
-          if (cta_seg[k] != (int)segs.size()) break;
-          room = 1;  // every CTA takes at least one tile
-        }
-        const int take = (int)std::min<long long>(room, tiles_of(tok) - tile_in_tok);
-        AttnSeg sg;
-        sg.tok = tok;
-        sg.kv_begin = std::max(kvlo[tok], (tile0_of(tok) + tile_in_tok) * unit);  // unaligned only at a window's edge
-        sg.kv_end = std::min(kvlen[tok], (tile0_of(tok) + tile_in_tok + take) * unit);
-        sg.part = part++;
-        segs.push_back(sg);
-        if (tile_in_tok == 0) --toks_left;
-        tile_in_tok += take;
-        tiles_left -= take;
-        budget2 -= SEG_COST2 + 2 * take;
-        skip_empty();
-      }
+  const int n_ctas = (int)std::min<long long>(c->n_sm, std::max<long long>(total_tiles, 1));
+  std::vector<AttnSeg>& segs = *segs_out;
+  std::vector<int32_t>& cta_seg = *cta_seg_out;
+  std::vector<int32_t> parts_of(T, 0);
+  segs.clear();
+  cta_seg.assign(n_ctas + 1, 0);
+  int st = 0, tile_in = 0, part = 0;
+  auto skip_empty = [&]() {
+    while (st < n_streams && tile_in >= tiles_of(st)) {
+      ++st;
+      tile_in = 0;
     }
-    cta_seg[n_ctas] = (int)segs.size();
-    while (tok < T) {
-      ++tok;
-      tok_part[tok] = part;
+  };
+  skip_empty();
+  long long tiles_left = total_tiles, streams_left = n_nonempty;  // streams not yet started
+  for (int k = 0; k < n_ctas; ++k) {
+    cta_seg[k] = (int)segs.size();
+    const bool last = k == n_ctas - 1;
+    // what is left, shared equally among the CTAs that are left: the tiles, a segment for every
+    // stream still to start (and for the one this CTA resumes), and one more segment for every
+    // later CTA, which will most likely resume a stream
+    const long long mid = tile_in > 0 ? 1 : 0;
+    const long long left2 = 2 * tiles_left + SEG_COST2 * (streams_left + mid + (n_ctas - k - 1));
+    long long budget2 = left2 / (n_ctas - k);
+    while (st < n_streams) {
+      long long room = last ? (1ll << 40) : (budget2 - SEG_COST2) / 2;  // tiles that still fit
+      if (room < 1) {
+        if (cta_seg[k] != (int)segs.size()) break;
+        room = 1;  // every CTA takes at least one tile
+      }
+      const TileStream& ts = streams[st];
+      const int take = (int)std::min<long long>(room, tiles_of(st) - tile_in);
+      AttnSeg sg;
+      sg.tok = ts.tok;
+      sg.kv_begin = std::max(ts.lo, (tile0_of(st) + tile_in) * unit);  // unaligned only at a window's edge
+      sg.kv_end = std::min(ts.hi, (tile0_of(st) + tile_in + take) * unit);
+      sg.part = part++;
+      sg.table = ts.table;
+      segs.push_back(sg);
+      parts_of[ts.tok] += 1;
+      if (tile_in == 0) --streams_left;
+      tile_in += take;
+      tiles_left -= take;
+      budget2 -= SEG_COST2 + 2 * take;
+      skip_empty();
     }
   }
-  if ((int)segs.size() > c->segs_cap || (int)segs.size() > c->max_parts)
-    return fail(FST_MLA_ERR_CAPACITY, "split schedule overflow");
+  cta_seg[n_ctas] = (int)segs.size();
+  // a token's streams are adjacent and segments are numbered in stream order: its partials are
+  // the contiguous range [tok_part[t], tok_part[t + 1])
+  tok_part_out->assign(T + 1, 0);
+  for (int t = 0; t < T; ++t) (*tok_part_out)[t + 1] = (*tok_part_out)[t] + parts_of[t];
+  *kv_rows_out = kv_rows;
+}
+
+// The second part: schedules (one per layer class in use) and block tables.  on_copy_stream:
+// upload it beside the kernels that already run on the context's stream (which then waits for
+// it); else one copy of the whole blob (or of the second part, if the first went ahead) on the
+// context's stream.
+int plan_schedule_part(FstMlaCtx* c, bool on_copy_stream) {
+  const int T = c->T;
+  std::vector<int32_t>&tok_table = c->pl_tok_table, &tables = c->pl_tables, &kvlen = c->pl_kvlen, &kvlo = c->pl_kvlo;
 
   // the second part of the pinned blob, behind the first; the device arrays are slices of the
   // device blob
   size_t off = c->pl_off_b;
   auto put = [&](const void* src, size_t bytes) -> unsigned char* {
     unsigned char* dev = c->d_plan + off;
-    if (bytes) memcpy(c->h_plan + off, src, bytes);
+    if (off + bytes <= c->plan_cap && bytes) memcpy(c->h_plan + off, src, bytes);
     off = (off + bytes + 255) & ~(size_t)255;
     return dev;
   };
-  c->d_tok_table = reinterpret_cast<int32_t*>(put(tok_table.data(), (size_t)T * sizeof(int32_t)));
-  c->d_tok_part = reinterpret_cast<int32_t*>(put(tok_part.data(), (size_t)(T + 1) * sizeof(int32_t)));
-  c->d_cta_seg = reinterpret_cast<int32_t*>(put(cta_seg.data(), cta_seg.size() * sizeof(int32_t)));
-  c->d_segs = reinterpret_cast<AttnSeg*>(put(segs.data(), segs.size() * sizeof(AttnSeg)));
+  bool in_use[N_CLASSES] = {true, false, false};  // class 0 is always built (plan_info, callers without layers)
+  for (const LayerW& l : c->layers) in_use[class_of_ratio(l.cmp_ratio)] = true;
+  std::vector<TileStream> streams;
+  std::vector<AttnSeg> segs;
+  std::vector<int32_t> cta_seg, tok_part;
+  for (int k = 0; k < N_CLASSES; ++k) {
+    Sched& S = c->sched[k];
+    S.built = false;
+    if (!in_use[k]) continue;
+    streams.clear();
+    for (int t = 0; t < T; ++t) {
+      streams.push_back(TileStream{t, tok_table[t], kvlo[t], kvlen[t]});
+      if (k > 0) {
+        // compressed row r was emitted at position (r + 1) * ratio - 1 (reference 3630-3635): every
+        // row of this call sees all of them in decode, those at or before its own position when
+        // causal.  (All rows of the sequence have gone through the compressor when the attention
+        // runs: the call's own rows are compressed in front of it.)
+        const FstMlaSeqStep& st = c->pl_steps[c->pl_tok_step[t]];
+        const int ratio = CLASS_RATIO[k];
+        int n_vis = st.append ? (st.pos0 + st.q_len) / ratio : 0;
+        if (c->pl_causal) {
+          int tok_in_step = t;
+          for (int b = 0; b < c->pl_tok_step[t]; ++b) tok_in_step -= c->pl_steps[b].q_len;
+          n_vis = std::min(n_vis, (st.pos0 + tok_in_step + 1) / ratio);
+        }
+        if (n_vis > 0) streams.push_back(TileStream{t, c->pl_tok_ctable[t], 0, n_vis});
+      }
+    }
+    long long kv_rows = 0;
+    cut_schedule(c, streams, T, &segs, &cta_seg, &tok_part, &kv_rows);
+    if ((int)segs.size() > c->segs_cap || (int)segs.size() > c->max_parts)
+      return fail(FST_MLA_ERR_CAPACITY, "split schedule overflow");
+    S.d_tok_part = reinterpret_cast<int32_t*>(put(tok_part.data(), (size_t)(T + 1) * sizeof(int32_t)));
+    S.d_cta_seg = reinterpret_cast<int32_t*>(put(cta_seg.data(), cta_seg.size() * sizeof(int32_t)));
+    S.d_segs = reinterpret_cast<AttnSeg*>(put(segs.data(), segs.size() * sizeof(AttnSeg)));
+    S.max_tok_parts = 0;
+    S.n_single_part = 0;
+    S.min_tok_parts = T > 0 ? (1 << 30) : 0;
+    for (int i = 0; i < T; ++i) {
+      const int np = tok_part[i + 1] - tok_part[i];
+      S.max_tok_parts = std::max(S.max_tok_parts, np);
+      S.min_tok_parts = std::min(S.min_tok_parts, np);
+      S.n_single_part += np == 1;
+    }
+    S.n_segs = S.n_parts = (int)segs.size();
+    S.n_ctas = (int)cta_seg.size() - 1;
+    S.kv_rows = kv_rows;
+    S.built = true;
+  }
   c->d_tables = reinterpret_cast<int32_t*>(put(tables.data(), tables.size() * sizeof(int32_t)));
   if (off > c->plan_cap) return fail(FST_MLA_ERR_CAPACITY, "plan blob overflow");
   const size_t from = c->front_uploaded ? c->pl_off_b : 0;
@@ -1121,18 +1427,6 @@ int plan_schedule_part(FstMlaCtx* c, bool on_copy_stream) {
     CU(cudaMemcpyAsync(c->d_plan + from, c->h_plan + from, off - from, cudaMemcpyHostToDevice, c->stream));
     CU(cudaEventRecord(c->plan_ev, c->stream));
   }
-  c->max_tok_parts = 0;
-  c->n_single_part = 0;
-  c->min_tok_parts = T > 0 ? (1 << 30) : 0;
-  for (int i = 0; i < T; ++i) {
-    c->max_tok_parts = std::max(c->max_tok_parts, tok_part[i + 1] - tok_part[i]);
-    c->min_tok_parts = std::min(c->min_tok_parts, tok_part[i + 1] - tok_part[i]);
-    c->n_single_part += tok_part[i + 1] - tok_part[i] == 1;
-  }
-  c->n_segs = (int)segs.size();
-  c->n_parts = (int)segs.size();
-  c->n_ctas = n_ctas;
-  c->kv_rows = kv_rows;
   c->last_steps = c->pl_steps;
   c->last_causal = c->pl_causal;
   ++c->plans_built;
@@ -1187,9 +1481,10 @@ int fst_cuda_mla_plan_tokens(FstMlaCtx* c, int32_t* t_out) {
 int fst_cuda_mla_plan_info(FstMlaCtx* c, int32_t* n_partials, int32_t* n_ctas, int64_t* kv_rows) {
   if (!c) return fail(FST_MLA_ERR_ARG, "null context");
   if (!c->planned) return fail(FST_MLA_ERR_STATE, "no plan");
-  if (n_partials) *n_partials = c->n_parts;
-  if (n_ctas) *n_ctas = c->n_ctas;
-  if (kv_rows) *kv_rows = c->kv_rows;
+  const Sched& S = c->sched[c->sched[c->info_class].built ? c->info_class : 0];
+  if (n_partials) *n_partials = S.n_parts;
+  if (n_ctas) *n_ctas = S.n_ctas;
+  if (kv_rows) *kv_rows = S.kv_rows;
   return FST_MLA_OK;
 }
 

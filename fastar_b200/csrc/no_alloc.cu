@@ -33,7 +33,7 @@ constexpr size_t OFF_PART_M = OFF_PART_O + SZ_PART_O;
 constexpr size_t SZ_PART_ML = (size_t)NA_MAX_SPLITS * NA_MAX_HEADS * sizeof(float);
 constexpr size_t OFF_PART_L = OFF_PART_M + SZ_PART_ML;
 constexpr size_t OFF_SEGS = OFF_PART_L + SZ_PART_ML;
-constexpr size_t OFF_TABLE = OFF_SEGS + 1024;                                   // 32 segments x 16 bytes, padded
+constexpr size_t OFF_TABLE = OFF_SEGS + 1024;                                   // 32 segments x 20 bytes, padded
 constexpr size_t OFF_TOK = OFF_TABLE + (NA_MAX_ROWS / NA_PAGE) * sizeof(int32_t);  // tok_table[1], tok_part[2]
 constexpr size_t OFF_LUT = OFF_TOK + 256;                                       // unused RoPE table slot
 constexpr size_t SCRATCH_BYTES = OFF_LUT + 256;
@@ -63,6 +63,7 @@ __global__ void k_na_setup(unsigned char* scratch, int n_rows, int n_splits) {
     sg.kv_begin = (int)((long long)tiles * s / n_splits) * 32;
     sg.kv_end = min(n_rows, (int)((long long)tiles * (s + 1) / n_splits) * 32);
     sg.part = s;
+    sg.table = 0;  // the identity block table starts at entry 0
     segs[s] = sg;
   }
   if (threadIdx.x == 0) {
@@ -125,7 +126,6 @@ extern "C" int fst_cuda_mla_attention_noalloc(const void* d_q_eff, const void* d
   a.q_eff = static_cast<const bf16*>(d_q_eff);
   a.pool = static_cast<const bf16*>(d_cache);
   a.tables = reinterpret_cast<const int32_t*>(sc + OFF_TABLE);
-  a.tok_table = reinterpret_cast<const int32_t*>(sc + OFF_TOK);
   a.segs = reinterpret_cast<const AttnSeg*>(sc + OFF_SEGS);
   a.cta_seg = nullptr;
   a.part_m = reinterpret_cast<float*>(sc + OFF_PART_M);

@@ -52,6 +52,11 @@ class Weights(C.Structure):
                [("attn_sinks", C.POINTER(C.c_float)), ("attn_norm", C.POINTER(C.c_uint16))]
 
 
+class CompressorW(C.Structure):
+    _fields_ = [("ratio", C.c_int32), ("wkv", C.POINTER(C.c_uint16)), ("wgate", C.POINTER(C.c_uint16)),
+                ("ape", C.POINTER(C.c_float)), ("norm", C.POINTER(C.c_uint16))]
+
+
 class SeqStep(C.Structure):
     _fields_ = [("seq", C.c_int32), ("pos0", C.c_int32), ("q_len", C.c_int32),
                 ("rope_pos0", C.c_int32), ("append", C.c_int32), ("window", C.c_int32)]
@@ -118,6 +123,9 @@ def load_library() -> C.CDLL:
     L.fst_cuda_mla_plan_counts.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
     L.fst_cuda_mla_set_layer_rope.argtypes = [vp, C.c_int, i32]
     L.fst_cuda_mla_set_rope_theta.argtypes = [vp, C.c_float]
+    L.fst_cuda_mla_set_layer_compressor.argtypes = [vp, C.c_int, C.POINTER(CompressorW)]
+    L.fst_cuda_mla_cmp_read.argtypes = [vp, C.c_int, i32, u16p, i32, i32p]
+    L.fst_cuda_mla_seq_snapshot.argtypes = [vp, i32]
     L.fst_cuda_mla_comm_unique_id.argtypes = [C.POINTER(C.c_uint8)]
     L.fst_cuda_mla_comm_init.argtypes = [vp, C.POINTER(C.c_uint8), i32, i32]
     L.fst_cuda_mla_comm_set_gather.argtypes = [vp, GATHER_FN, vp, i32, i32]
@@ -223,6 +231,29 @@ class MlaContext:
     def set_layer_rope(self, lid: int, yarn: bool) -> None:
         """RoPE kind of one layer: plain, or the YaRN tables of the compressed V4 layers."""
         self._check(self.lib.fst_cuda_mla_set_layer_rope(self._h, lid, 1 if yarn else 0))
+
+    def set_layer_compressor(self, lid: int, ratio: int, wkv=None, wgate=None, ape=None, norm=None) -> None:
+        """The layer's V4 KV compressor: wkv / wgate bf16 bits [width, hidden], ape fp32 [ratio, width],
+        norm bf16 bits [kv_lora]; ratio 0 removes it."""
+        if not ratio:
+            self._check(self.lib.fst_cuda_mla_set_layer_compressor(self._h, lid, None))
+            return
+        wkv, wgate = np.ascontiguousarray(wkv, np.uint16), np.ascontiguousarray(wgate, np.uint16)
+        ape, norm = np.ascontiguousarray(ape, np.float32), np.ascontiguousarray(norm, np.uint16)
+        w = CompressorW(ratio, _u16(wkv), _u16(wgate), ape.ctypes.data_as(C.POINTER(C.c_float)), _u16(norm))
+        self._check(self.lib.fst_cuda_mla_set_layer_compressor(self._h, lid, C.byref(w)))
+
+    def cmp_read(self, lid: int, seq: int) -> np.ndarray:
+        """The compressed rows of a sequence in one layer, uint16 bf16 bits [n, kv_lora]."""
+        n = C.c_int32()
+        self._check(self.lib.fst_cuda_mla_cmp_read(self._h, lid, seq, None, 0, C.byref(n)))
+        out = np.empty((n.value, self.dims["row"]), np.uint16)
+        if n.value:
+            self._check(self.lib.fst_cuda_mla_cmp_read(self._h, lid, seq, _u16(out), n.value, C.byref(n)))
+        return out
+
+    def seq_snapshot(self, seq: int) -> None:
+        self._check(self.lib.fst_cuda_mla_seq_snapshot(self._h, seq))
 
     def set_rope_theta(self, theta: float) -> None:
         self._check(self.lib.fst_cuda_mla_set_rope_theta(self._h, theta))

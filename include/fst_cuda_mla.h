@@ -160,6 +160,31 @@ int fst_cuda_mla_set_layer_rope(FstMlaCtx* ctx, int lid, int32_t yarn);
  * src/fst_engine.cpp:1505). */
 int fst_cuda_mla_set_rope_theta(FstMlaCtx* ctx, float theta);
 
+/* V4 KV compressor of one layer (reference LayerWeightsC cmp_*, include/fst_engine.h:172-180,
+ * loaded at src/fst_engine.cpp:1657-1690; compress_token 3171-3318).  Layers whose compress ratio
+ * is 4 or 128 stream every row through the compressor in front of the attention (3545-3568): every
+ * ratio-th row emits one pooled, normed, tail-rotated, E4M3-round-tripped row of kv_lora values, and
+ * those rows are further attention columns (3565-3586) with the causal rule of 3630-3635.  Here they
+ * live in pages of their own (a second block table per sequence); the window state is kept per
+ * (layer, sequence) on the device.  width = 2 * kv_lora for ratio 4, kv_lora for ratio 128.
+ * Host pointers, copied once.  V4 form only.  Set before any sequence holds rows; w == NULL or
+ * ratio 0 removes the compressor.  A sequence's rows must then reach the layer in order from row 0
+ * (fst_cuda_mla_cache_write does not go through the compressor). */
+typedef struct FstMlaCompressor {
+  int32_t ratio;         /* 4 or 128 */
+  const uint16_t* wkv;   /* bf16 [width, hidden] */
+  const uint16_t* wgate; /* bf16 [width, hidden] */
+  const float* ape;      /* fp32 [ratio, width] */
+  const uint16_t* norm;  /* bf16 [kv_lora] */
+} FstMlaCompressor;
+int fst_cuda_mla_set_layer_compressor(FstMlaCtx* ctx, int lid, const FstMlaCompressor* w);
+/* The compressed rows of a sequence in one layer [n, kv_lora] to host; rows == NULL: only the count. */
+int fst_cuda_mla_cmp_read(FstMlaCtx* ctx, int lid, int32_t seq, uint16_t* rows, int32_t cap, int32_t* n_out);
+/* Saves the compressor window state of a sequence (all layers) at its present length: a later
+ * fst_cuda_mla_seq_truncate to exactly that length restores it, as the reference restores its
+ * snapshot when it rejects speculative rows (src/fst_engine.cpp:6149-6152). */
+int fst_cuda_mla_seq_snapshot(FstMlaCtx* ctx, int32_t seq);
+
 /* ---- paged latent cache --------------------------------------------------------------- */
 /* The reference cache is one flat [max_seq, 512] bf16 buffer per layer indexed by seq_pos_
  * (include/fst_engine.h:108-113; alloc src/fst_engine.cpp:1469-1474).  Here token t of a

@@ -445,12 +445,14 @@ int fst_oracle_compress_token(const FstOracleCfg* c, const FstOracleCompressorW*
     float denom = 0.0f, sum = 0.0f;
     for (int r = 0; r < ratio; ++r) {
       const float wp = std::exp(st->state_sc[(size_t)r * width + j] - mx);
-      denom += wp;
-      sum += wp * st->state_kv[(size_t)r * width + j];
       if (ratio == 4) {
         const float wc = std::exp(st->state_sc[(size_t)(ratio + r) * width + hd + j] - mx);
-        denom += wc;
+        denom += wp + wc;
+        sum += wp * st->state_kv[(size_t)r * width + j];
         sum += wc * st->state_kv[(size_t)(ratio + r) * width + hd + j];
+      } else {
+        denom += wp;
+        sum += wp * st->state_kv[(size_t)r * width + j];
       }
     }
     pooled[j] = denom > 0.0f ? sum / denom : 0.0f;
