@@ -43,7 +43,11 @@ FSTEngine::FSTEngine(const ModelConfig& cfg) : config_(cfg) {
   c.n_layers = cfg.n_layers;
   c.page_tokens = cfg.page_tokens;
   const int pages_per_seq = (cfg.max_seq + cfg.page_tokens - 1) / cfg.page_tokens;
-  c.n_pages = pages_per_seq * cfg.max_seqs;
+  // the rows of a sequence, plus (V4 form) its compressed rows: at most one per four rows, in
+  // pages of their own
+  const int cmp_pages_per_seq = cfg.preset == FST_MLA_PRESET_FASTAR_V4
+                                    ? (cfg.max_seq / 4 + cfg.page_tokens - 1) / cfg.page_tokens : 0;
+  c.n_pages = (pages_per_seq + cmp_pages_per_seq) * cfg.max_seqs;
   c.max_seqs = cfg.max_seqs;
   c.max_tokens = cfg.max_tokens;
   c.device = cfg.device;
@@ -152,6 +156,19 @@ void FSTEngine::load_shared_weights(const std::string& fst_path) {
     take_bf16(fst_path, dir, fstfile::TID_KV_NORM, l, 0, z.kv_norm, "kv_norm", &w.kv_norm);
     take_bf16(fst_path, dir, fstfile::TID_INPUT_NORM, l, 0, z.attn_norm, "attn_norm", &w.attn_norm);
     take_sinks(fst_path, dir, l, z.sinks, &w.attn_sinks);
+    // V4 KV compressor weights, TIDs 32-35, only for layers with a ratio (1657-1690)
+    w.cmp_ratio = v4 && l < (int)config_.compress_ratios.size() ? config_.compress_ratios[l] : 0;
+    w.cmp_comp_width = w.cmp_ratio == 4 ? 2 * MLA_KV_LORA : (w.cmp_ratio == 128 ? MLA_KV_LORA : 0);
+    if (w.cmp_comp_width) {
+      const size_t cw = (size_t)w.cmp_comp_width;
+      if (const fstfile::Entry* e = fstfile::find(dir, 32, l, 0)) {
+        std::vector<float> ape = fstfile::load_f32(fst_path, *e);
+        if (ape.size() >= (size_t)w.cmp_ratio * cw) w.cmp_ape.assign(ape.begin(), ape.begin() + (size_t)w.cmp_ratio * cw);
+      }
+      take_bf16(fst_path, dir, 33, l, 0, cw * hdim, "cmp_wkv", &w.cmp_wkv);
+      take_bf16(fst_path, dir, 34, l, 0, cw * hdim, "cmp_wgate", &w.cmp_wgate);
+      take_bf16(fst_path, dir, 35, l, 0, MLA_KV_LORA, "cmp_norm", &w.cmp_norm);
+    }
   }
 }
 
@@ -185,6 +202,16 @@ void FSTEngine::preload_all_layers() {
     fw.attn_norm = p(w.attn_norm);
     check(fst_cuda_mla_set_layer_weights(ctx_, l, &fw), "set_layer_weights");
     check(fst_cuda_mla_set_layer_rope(ctx_, l, layer_is_compressed(l) ? 1 : 0), "set_layer_rope");
+    if (use_compressor_ && w.cmp_ratio != 0 && !w.cmp_wkv.empty() && !w.cmp_wgate.empty() && !w.cmp_ape.empty() &&
+        !w.cmp_norm.empty()) {  // (the conditions of compress_token, 3173-3175)
+      FstMlaCompressor cw;
+      cw.ratio = w.cmp_ratio;
+      cw.wkv = w.cmp_wkv.data();
+      cw.wgate = w.cmp_wgate.data();
+      cw.ape = w.cmp_ape.data();
+      cw.norm = w.cmp_norm.data();
+      check(fst_cuda_mla_set_layer_compressor(ctx_, l, &cw), "set_layer_compressor");
+    }
   }
 }
 
@@ -230,6 +257,8 @@ void FSTEngine::reset_session() {
 }
 
 void FSTEngine::set_window(int window) { check(fst_cuda_mla_set_window(ctx_, window), "set_window"); }
+
+void FSTEngine::snapshot_before_verify() { check(fst_cuda_mla_seq_snapshot(ctx_, seq_), "seq_snapshot"); }
 
 void FSTEngine::rollback(int keep_len) {
   int32_t len = 0;

@@ -44,6 +44,13 @@ struct LayerWeightsC {
   std::vector<float> attn_sinks;    // per-head sink logit (empty: 0, src/fst_engine.cpp:3623)
   std::vector<bf16_t> attn_norm;    // [hidden]; when set, process_mla takes the rows BEFORE the norm
                                     // of process_layer (src/fst_engine.cpp:2687-2688) and applies it
+  // V4 KV compressor (reference include/fst_engine.h:172-180): cmp_ape F32 [ratio, comp_width],
+  // cmp_wkv / cmp_wgate BF16 [comp_width, hidden] native [N, K], cmp_norm BF16 [512]; empty for
+  // ratio-0 layers.  cmp_ratio 4 | 128, cmp_comp_width 1024 | 512.
+  std::vector<float> cmp_ape;
+  std::vector<bf16_t> cmp_wkv, cmp_wgate, cmp_norm;
+  int cmp_ratio = 0;
+  int cmp_comp_width = 0;
 };
 
 struct RandmatResult {  // one line of randmat_test (src/fst_engine.cpp:586-685)
@@ -92,8 +99,14 @@ class FSTEngine {
   void advance(int n) { seq_pos_ += n; }
   void set_prefill(bool p) { is_prefill_ = p; }
   bool is_prefill() const { return is_prefill_; }
-  // Speculative-decoding rollback (6132-6147): forget rows >= keep_len of the current sequence.
+  // Speculative-decoding rollback (6132-6152): forget rows >= keep_len of the current sequence.  The
+  // reference saves the compressor state before a verify block (cmp_snap) and restores it with the
+  // rollback: snapshot_before_verify() is that save, rollback() to the same length restores it.
+  void snapshot_before_verify();
   void rollback(int keep_len);
+  // The KV compressor runs for layers that carry its weights (the reference gates it behind the
+  // FST_COMPRESSOR environment variable, 3565): off by default here too; call before preload_all_layers.
+  void enable_compressor(bool on) { use_compressor_ = on; }
   // Sliding window of the draft model's attention (draft_cfg_.window_size, 2534-2576): process_mla
   // attends to the last `window` rows only; 0 switches it off.
   void set_window(int window);
@@ -131,5 +144,6 @@ class FSTEngine {
   int seq_pos_ = 0;
   bool is_prefill_ = true;
   int slice_begin_ = 0;
+  bool use_compressor_ = false;
   void check(int rc, const char* what);
 };

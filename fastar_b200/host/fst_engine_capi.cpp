@@ -125,6 +125,9 @@ int fst_engine_randmat_test(FSTEngine* e, double* cosine, double* ratio, double*
   return n;
 }
 FstMlaCtx* fst_engine_ctx(FSTEngine* e) { return e->ctx(); }
+void fst_engine_enable_compressor(FSTEngine* e, int on) { e->enable_compressor(on != 0); }
+int fst_engine_snapshot_before_verify(FSTEngine* e) { return guard([&] { e->snapshot_before_verify(); }); }
+int fst_engine_layer_cmp_ratio(FSTEngine* e, int lid) { return e->shared_.at(lid).cmp_ratio; }
 int fst_engine_join_split_group(FSTEngine* e, const uint8_t* id, int rank, int world) {
   return guard([&] { e->join_split_group(id, rank, world); });
 }

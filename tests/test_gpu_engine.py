@@ -204,13 +204,16 @@ def test_weights_loaded_from_a_fst_file(tmp_path):
         L.fst_engine_destroy(e_ref)
 
 
-def test_rope_kind_follows_each_layers_compress_ratio(tmp_path):
+@pytest.mark.parametrize("with_compressor", [False, True], ids=["plain", "compressor"])
+def test_rope_kind_follows_each_layers_compress_ratio(tmp_path, with_compressor):
     """build_rope_lut chooses per layer (src/fst_engine.cpp:1979-1982): plain RoPE with the file's
     rope_freq_base for layers whose compress ratio is 0, YaRN for the others.  A three-layer engine
     reads ratios {0, 0, 4} (TID 40) and a non-default base from a file written in the converter's
     other form (wq_a / wq_b and wo_a / wo_b under one tensor id AND sub id 0, found by shape as the
     engine finds them, 1610-1615); every layer is prefilled in 15-row chunks -- rows 60..74 straddle
-    a page boundary -- and compared with the oracle that uses that layer's RoPE kind."""
+    a page boundary -- and compared with the oracle that uses that layer's RoPE kind.  With the
+    compressor switched on (the reference gates it behind FST_COMPRESSOR, 3565) layer 2 also reads
+    its compressor tensors (TIDs 32-35, 1657-1690) and attends to its compressed rows."""
     import struct
     L = load()
     L.fst_engine_load_shared_weights.argtypes = [C.c_void_p, C.c_char_p]
@@ -222,6 +225,12 @@ def test_rope_kind_follows_each_layers_compress_ratio(tmp_path):
                     (8, l, 0, 2, bits["wo_a"]), (8, l, 0, 2, bits["wo_b"]), (14, l, 0, 2, bits["q_norm"]),
                     (15, l, 0, 2, bits["kv_norm"]), (22, l, 0, 3, np.ascontiguousarray(bits["attn_sinks"], np.float32))]
     tensors.append((40, 0xFFFF, 0, 3, np.array([0.0, 0.0, 4.0], np.float32)))
+    cfg = mla.make_config(mla.PRESET_FASTAR_V4)
+    comp = None
+    if with_compressor:
+        from tests.test_gpu_compressor import compressor_weights
+        cb, cr = compressor_weights(cfg, 4, 77)
+        tensors += [(32, 2, 0, 3, cb["ape"]), (33, 2, 0, 2, cb["wkv"]), (34, 2, 0, 2, cb["wgate"]), (35, 2, 0, 2, cb["norm"])]
     path = str(tmp_path / "three.fst")
     _write_fst(path, 3, [(t, l, s, q, np.ascontiguousarray(a)) for t, l, s, q, a in tensors])
     with open(path, "r+b") as f:  # the header's rope_freq_base
@@ -230,9 +239,12 @@ def test_rope_kind_follows_each_layers_compress_ratio(tmp_path):
     e = L.fst_engine_create(mla.PRESET_FASTAR_V4, 3, 128, 1, 16, 0, mla.IMPL_AUTO, mla.IMPL_AUTO)
     assert e, L.fst_engine_last_error()
     try:
+        L.fst_engine_enable_compressor.argtypes = [C.c_void_p, C.c_int]
+        L.fst_engine_layer_cmp_ratio.argtypes = [C.c_void_p, C.c_int]
+        L.fst_engine_enable_compressor(e, int(with_compressor))
         assert L.fst_engine_load_shared_weights(e, path.encode()) == 0, L.fst_engine_last_error()
         assert L.fst_engine_preload(e) == 0, L.fst_engine_last_error()
-        cfg = mla.make_config(mla.PRESET_FASTAR_V4)
+        assert [L.fst_engine_layer_cmp_ratio(e, l) for l in range(3)] == [0, 0, 4]
         caches = [np.zeros((128, 512), np.float32) for _ in range(3)]
         ocfgs = []
         for l in range(3):
@@ -240,6 +252,8 @@ def test_rope_kind_follows_each_layers_compress_ratio(tmp_path):
             oc.rope_yarn = 1 if l == 2 else 0
             oc.rope_theta = theta
             ocfgs.append(oc)
+        if with_compressor:
+            comp = O.Compressor(ocfgs[2], 4, cr["wkv"], cr["wgate"], cr["ape"], cr["norm"], cap=40)
         L.fst_engine_set_prefill(e, 1)
         outs = {}
         for chunk in range(5):
@@ -250,8 +264,8 @@ def test_rope_kind_follows_each_layers_compress_ratio(tmp_path):
                 buf = np.ascontiguousarray(h, np.uint16).copy()
                 rc = L.fst_engine_process_mla(e, l, buf.ctypes.data_as(C.POINTER(C.c_uint16)), 15)
                 assert rc == 0, L.fst_engine_last_error()
-                want = O.mla_forward(ocfgs[l], rounded, synth.from_bf16_bits(h), pos, caches[l], causal=True,
-                                     want_trace=False).out
+                want = O.mla_forward_batch(ocfgs[l], rounded, synth.from_bf16_bits(h), [15], [pos], [caches[l]], causal=True,
+                                           compressors=[comp] if (comp is not None and l == 2) else None).out
                 check_close(buf, want, f"chunk {chunk} layer {l}", ulps=2)
                 outs[chunk, l] = buf
             L.fst_engine_advance(e, 15)
