@@ -90,7 +90,7 @@ struct StreamParams {
   const int32_t* tok_part;  // [T + 1] partial slots of every token
   bf16* o_lat;              // [T * 64, 512]
   const float* sinks;       // [64] or null
-  const float* lut;         // [T, rope] (cos, sin): inverse RoPE of the output tail when inv_rope
+  const float* lut;         // [T, rope] (cos, sin): inverse RoPE of the output tail of heads 0 .. inv_rope-1
   int rope, inv_rope;
 };
 
@@ -228,7 +228,7 @@ __device__ __forceinline__ void finish_token(const StreamParams& p, int tok, int
     tmem_ld16x64(lane_addr + LANE16 + COL_O + half * 256 + cc * 64, o);
 #pragma unroll
     for (int j = 0; j < 32; ++j) o[j] = rbf(fmaf(w, o[j], 0.0f) * inv);
-    if (p.inv_rope && col0 + 32 > D_V - p.rope) {
+    if (row < p.inv_rope && col0 + 32 > D_V - p.rope) {
       // inverse RoPE of the rounded output tail: pairs (2i, 2i+1) sit in one thread
 #pragma unroll
       for (int j = 0; j < 32; j += 2) {

@@ -133,6 +133,10 @@ struct QPrepArgs {
   bf16* q_eff;         // [T * H, d_qk]
   int T, H, q_head, nope, rope, d_qk, v4;
   float eps;
+  // V4 only.  head_norm: the per-head weightless RMSNorm (reference 3487-3495); rope_heads: heads
+  // 0 .. rope_heads-1 get their tail rotated.  The main model: 1 and all heads; the draft model's
+  // layer has no head norm and rotates head 0 only (process_draft_mla, 4967-4983).
+  int head_norm = 1, rope_heads = 1 << 30;
 };
 void launch_q_prep(const QPrepArgs& a, cudaStream_t st);
 
@@ -158,7 +162,7 @@ struct AttnArgs {
   bf16* o_lat = nullptr;              // [T * H, d_v]
   const float* sinks = nullptr;       // [H] or null
   const float* lut = nullptr;         // [T, rope]
-  int rope = 0, inv_rope = 0;
+  int rope = 0, inv_rope = 0;           // inv_rope: heads 0 .. inv_rope-1 get the inverse rotation of their output tail
 };
 void launch_attn_simt(const AttnArgs& a, cudaStream_t st);
 // tcgen05 kernel: a stream of 64-token tiles, Q_eff in tensor memory, ring of three tile frames.
@@ -172,7 +176,7 @@ struct MergeArgs {
   const float* part_o;
   const int32_t* tok_part;  // [T + 1]
   const float* sinks;       // [H] or null
-  const float* lut;         // [T, rope]: inverse RoPE of the output tail when inv_rope
+  const float* lut;         // [T, rope]: inverse RoPE of the output tail of heads 0 .. inv_rope-1
   bf16* o_lat;              // [T * H, d_v]                 (mode 0)
   float* rank_partial;      // [T * H, 2 + d_v] fp32        (mode 1, no sink)
   int T, H, d_v, rope, inv_rope, mode;

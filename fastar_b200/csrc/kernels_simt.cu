@@ -245,16 +245,19 @@ __global__ void __launch_bounds__(128) k_q_prep(QPrepArgs a) {
   bf16* out = a.q_eff + (long long)r * a.d_qk;
   const float* lut = a.lut + (long long)t * a.rope;
   if (a.v4) {
-    float ss = 0.0f;
-    for (int j = threadIdx.x; j < a.q_head; j += blockDim.x) {
-      const float x = bf2f(in[j]);
-      ss += x * x;
+    float sc = 1.0f;
+    if (a.head_norm) {
+      float ss = 0.0f;
+      for (int j = threadIdx.x; j < a.q_head; j += blockDim.x) {
+        const float x = bf2f(in[j]);
+        ss += x * x;
+      }
+      ss = block_sum(ss, scratch);
+      sc = 1.0f / sqrtf(ss / (float)a.q_head + a.eps);
     }
-    ss = block_sum(ss, scratch);
-    const float sc = 1.0f / sqrtf(ss / (float)a.q_head + a.eps);
     for (int j = threadIdx.x; j < a.q_head; j += blockDim.x) s_q[j] = rbf(bf2f(in[j]) * sc);
     __syncthreads();
-    for (int p = threadIdx.x; p < a.rope / 2; p += blockDim.x) {
+    for (int p = threadIdx.x; p < a.rope / 2 && r % a.H < a.rope_heads; p += blockDim.x) {
       const int j = a.nope + 2 * p;
       const float c = lut[2 * p], s = lut[2 * p + 1], x0 = s_q[j], x1 = s_q[j + 1];
       s_q[j] = x0 * c - x1 * s;
@@ -566,7 +569,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge(MergeArgs a) {
   }
   const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
   for (int j = threadIdx.x; j < a.d_v; j += blockDim.x) s_acc[j] = rbf(s_acc[j] * inv);
-  finish_row(s_acc, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope, a.inv_rope);
+  finish_row(s_acc, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope, h < a.inv_rope);
 }
 
 // Rows with few parts: one WARP per query row (token, head), eight rows per block, nothing
@@ -632,7 +635,7 @@ __global__ void __launch_bounds__(256) k_merge_rows(MergeArgs a) {
           float v[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) v[e] = rbf(acc[4 * j + e] * inv);
-          if (a.inv_rope && col >= a.d_v - a.rope) {
+          if (h < a.inv_rope && col >= a.d_v - a.rope) {
             // inverse RoPE of the rounded output tail (reference src/fst_engine.cpp:3716)
 #pragma unroll
             for (int e = 0; e < 4; e += 2) {
@@ -677,7 +680,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge_gathered(MergeGatheredA
   merge_row(a.n_parts, get, a.sinks, h, a.d_v, s_acc, s_red, M, den);
   const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
   for (int j = threadIdx.x; j < a.d_v; j += blockDim.x) s_acc[j] = rbf(s_acc[j] * inv);
-  finish_row(s_acc, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope, a.inv_rope);
+  finish_row(s_acc, a.o_lat + (long long)r * a.d_v, a.lut + (long long)t * a.rope, a.d_v, a.rope, h < a.inv_rope);
 }
 
 void launch_merge_gathered(const MergeGatheredArgs& a, cudaStream_t st) {

@@ -61,6 +61,7 @@ struct LayerW {
   bf16* attn_norm = nullptr;  // [hidden] or null: the norm in front of the layer
   float* sinks = nullptr;
   bool set = false;
+  bool draft_form = false;  // the draft model's layer: no per-head q norm, q / output tail rotation on head 0 only
   // V4 KV compressor (reference LayerWeightsC cmp_*, include/fst_engine.h:172-180): 0 = none
   int cmp_ratio = 0;
   bf16* w_cmp_proj = nullptr;   // [2 * width, hidden]: wkv rows, then wgate rows
@@ -274,6 +275,8 @@ void rope_kinds(const FstMlaCtx* c, bool need[2]) {
   for (int8_t k : c->layer_yarn) need[k ? 1 : 0] = true;
 }
 const float* lut_of(const FstMlaCtx* c, int lid) { return c->d_lut_k[c->layer_yarn[lid] ? 1 : 0]; }
+// heads whose output tail gets the inverse rotation (reference 3716; the draft layer: head 0, 5077-5093)
+int inv_rope_heads(const FstMlaCtx* c, int lid) { return !c->d.v4 ? 0 : c->layers[lid].draft_form ? 1 : c->d.H; }
 int class_of(const FstMlaCtx* c, int lid) { return class_of_ratio(c->layers[lid].cmp_ratio); }
 Sched& sched_of(FstMlaCtx* c, int lid) { return c->sched[class_of(c, lid)]; }
 int cmp_width(const FstMlaCtx* c, int ratio) { return ratio == 4 ? 2 * c->d.kv_lora : c->d.kv_lora; }
@@ -423,7 +426,7 @@ AttnArgs attn_args(FstMlaCtx* c, int lid, const bf16* q_eff, bool may_fuse = fal
     a.sinks = c->d.v4 ? c->layers[lid].sinks : nullptr;
     a.lut = lut_of(c, lid);
     a.rope = c->d.rope;
-    a.inv_rope = c->d.v4 ? 1 : 0;
+    a.inv_rope = inv_rope_heads(c, lid);
   }
   return a;
 }
@@ -506,6 +509,10 @@ int run_front(FstMlaCtx* c, int lid, const bf16* h_in) {
   qp.q_full = c->d_qfull; qp.lut = lut_of(c, lid); qp.q_eff = c->d_qeff;
   qp.T = T; qp.H = d.H; qp.q_head = d.q_head; qp.nope = d.nope; qp.rope = d.rope; qp.d_qk = d.d_qk;
   qp.v4 = d.v4; qp.eps = c->cfg.rms_eps;
+  if (w.draft_form) {
+    qp.head_norm = 0;
+    qp.rope_heads = 1;
+  }
   if (d.v4) {
     launch_q_prep(qp, c->stream);
     c->launches += 1;
@@ -572,7 +579,7 @@ int run_merge_local(FstMlaCtx* c, int lid, int mode, float* rank_partial, bool s
   m.part_m = c->d_part_m; m.part_l = c->d_part_l; m.part_o = c->d_part_o; m.tok_part = S.d_tok_part;
   m.sinks = (d.v4 && mode == 0) ? c->layers[lid].sinks : nullptr;
   m.lut = lut_of(c, lid); m.o_lat = c->d_olat; m.rank_partial = rank_partial;
-  m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope; m.inv_rope = d.v4 ? 1 : 0; m.mode = mode;
+  m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope; m.inv_rope = inv_rope_heads(c, lid); m.mode = mode;
   m.threads = S.n_parts <= 6 * c->T ? 128 : 256;
   launch_merge(m, c->stream);
   c->launches += 1;
@@ -830,6 +837,14 @@ int fst_cuda_mla_set_layer_rope(FstMlaCtx* c, int lid, int32_t yarn) {
     c->layer_yarn[lid] = (int8_t)yarn;
     c->planned = false;  // the next plan uploads the tables of every kind in use
   }
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_set_layer_draft_form(FstMlaCtx* c, int lid, int32_t on) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (lid < 0 || lid >= c->cfg.n_layers) return fail(FST_MLA_ERR_ARG, "layer %d out of range", lid);
+  if (on && !c->d.v4) return fail(FST_MLA_ERR_ARG, "the draft model's layer has the V4 form (512-wide rows)");
+  c->layers[lid].draft_form = on != 0;
   return FST_MLA_OK;
 }
 
@@ -1593,6 +1608,41 @@ int fst_cuda_mla_forward(FstMlaCtx* c, int lid, const uint16_t* h_in, uint16_t* 
   return FST_MLA_OK;
 }
 
+int fst_cuda_mla_append_rows(FstMlaCtx* c, int lid, const uint16_t* h_in, const int32_t* seq_ids, const int32_t* pos0,
+                             const int32_t* q_lens, int32_t n_seqs) {
+  if (!c || !h_in || !seq_ids || !pos0 || !q_lens) return fail(FST_MLA_ERR_ARG, "null argument");
+  if (n_seqs < 0) return fail(FST_MLA_ERR_ARG, "negative sequence count");
+  std::vector<FstMlaSeqStep> steps(n_seqs);
+  for (int b = 0; b < n_seqs; ++b) steps[b] = FstMlaSeqStep{seq_ids[b], pos0[b], q_lens[b], -1, 1, 0};
+  int rc = fst_cuda_mla_plan(c, steps.data(), n_seqs, 0);
+  if (rc) return rc;
+  if ((rc = check_run(c, lid))) return rc;
+  if (c->T == 0) return FST_MLA_OK;
+  if (c->layers[lid].cmp_ratio) return fail(FST_MLA_ERR_STATE, "layer %d has a KV compressor: its rows come with a layer call", lid);
+  CU(cudaSetDevice(c->cfg.device));
+  const Dims& d = c->d;
+  const LayerW& w = c->layers[lid];
+  const size_t bytes = (size_t)c->T * d.hidden * sizeof(uint16_t);
+  memcpy(c->h_pinned, h_in, bytes);
+  CU(cudaMemcpyAsync(c->d_h, c->h_pinned, bytes, cudaMemcpyHostToDevice, c->stream));
+  const bf16* rows = c->d_h;
+  if (w.attn_norm) {
+    launch_rmsnorm_rows(c->d_h, w.attn_norm, c->d_an, c->T, d.hidden, c->cfg.rms_eps, c->stream);
+    c->launches += 1;
+    rows = c->d_an;
+  }
+  if ((rc = run_gemm(c, plain_gemm(rows, w.w_cmp, c->d_cmp, c->T, d.cmp_n, d.hidden)))) return rc;
+  NormAppendArgs na;
+  na.cmp = c->d_cmp; na.q_norm = w.q_norm; na.kv_norm = w.kv_norm; na.lut = lut_of(c, lid);
+  na.dst_row = c->d_dst; na.qc = c->d_qc; na.kv_new = c->d_kvnew; na.pool = c->pools[lid];
+  na.T = c->T; na.q_lora = d.q_lora; na.kv_lora = d.kv_lora; na.row = d.row; na.rope = d.rope;
+  na.eps = c->cfg.rms_eps;
+  launch_norm_append(na, c->stream);
+  c->launches += 1;
+  CU(cudaGetLastError());
+  return fst_cuda_mla_sync(c);
+}
+
 int fst_cuda_mla_attention_only(FstMlaCtx* c, int lid, const uint16_t* q_eff, uint16_t* o_lat) {
   int rc = check_run(c, lid);
   if (rc) return rc;
@@ -1643,7 +1693,7 @@ int fst_cuda_mla_run_merge_device(FstMlaCtx* c, int lid, const void* d_partials,
   MergeGatheredArgs m;
   m.parts = (const float*)d_partials; m.sinks = d.v4 ? c->layers[lid].sinks : nullptr; m.lut = lut_of(c, lid);
   m.o_lat = c->d_olat; m.n_parts = n_parts; m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope;
-  m.inv_rope = d.v4 ? 1 : 0;
+  m.inv_rope = inv_rope_heads(c, lid);
   launch_merge_gathered(m, c->stream);
   c->launches += 1;
   if ((rc = run_back(c, lid, (bf16*)d_h_out))) return rc;
@@ -1840,7 +1890,7 @@ int fst_cuda_mla_run_split_device(FstMlaCtx* c, int lid, const void* d_h_in, voi
   MergeGatheredArgs m;
   m.parts = c->d_xgath; m.sinks = d.v4 ? c->layers[lid].sinks : nullptr; m.lut = lut_of(c, lid);
   m.o_lat = c->d_olat; m.n_parts = c->comm_world; m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope;
-  m.inv_rope = d.v4 ? 1 : 0;
+  m.inv_rope = inv_rope_heads(c, lid);
   launch_merge_gathered(m, c->stream);
   c->launches += 1;
   if ((rc = run_back(c, lid, (bf16*)d_h_out))) return rc;

@@ -202,6 +202,7 @@ void FSTEngine::preload_all_layers() {
     fw.attn_norm = p(w.attn_norm);
     check(fst_cuda_mla_set_layer_weights(ctx_, l, &fw), "set_layer_weights");
     check(fst_cuda_mla_set_layer_rope(ctx_, l, layer_is_compressed(l) ? 1 : 0), "set_layer_rope");
+    if (config_.draft) check(fst_cuda_mla_set_layer_draft_form(ctx_, l, 1), "set_layer_draft_form");
     if (use_compressor_ && w.cmp_ratio != 0 && !w.cmp_wkv.empty() && !w.cmp_wgate.empty() && !w.cmp_ape.empty() &&
         !w.cmp_norm.empty()) {  // (the conditions of compress_token, 3173-3175)
       FstMlaCompressor cw;
@@ -220,6 +221,25 @@ void FSTEngine::process_mla(int lid, bf16_t* h, int M) {
     throw std::runtime_error("process_mla: seq_pos_ + M exceeds max_seq");
   const int32_t seq = seq_, pos = seq_pos_, q = M;
   check(fst_cuda_mla_forward(ctx_, lid, h, h, &seq, &pos, &q, 1, is_prefill_ ? 1 : 0), "process_mla");
+}
+
+void FSTEngine::process_draft_mla(int lid, bf16_t* h, int M, const bf16_t* main_x) {
+  const int anchor = seq_pos_;
+  if (anchor + 1 + M > config_.max_seq) throw std::runtime_error("process_draft_mla: anchor + 1 + M exceeds max_seq");
+  const int32_t seq = seq_, one = 1;
+  int32_t pos = anchor, q = M;
+  // main_kv = kv_norm(wkv(main_x)), rotary at the anchor, into the window (4913-4940)
+  check(fst_cuda_mla_append_rows(ctx_, lid, main_x, &seq, &pos, &one, 1), "process_draft_mla (main row)");
+  // q and kv of the block at anchor+1+m, dense attention over [window ; block] with the sink, inverse
+  // rotation, grouped wo_a, wo_b (4942-5131).  The ring of window_size slots becomes a window on the
+  // paged rows: the last window_size main rows and the M block rows.
+  const int win = config_.window_size;
+  check(fst_cuda_mla_set_window(ctx_, anchor + 1 > win ? win + M : 0), "set_window");
+  pos = anchor + 1;
+  check(fst_cuda_mla_forward(ctx_, lid, h, h, &seq, &pos, &q, 1, 0), "process_draft_mla");
+  check(fst_cuda_mla_set_window(ctx_, 0), "set_window");
+  // only main rows stay in the cache: the block's rows go again
+  check(fst_cuda_mla_seq_truncate(ctx_, seq_, anchor + 1), "process_draft_mla (drop the block)");
 }
 
 void FSTEngine::process_mla_batch(int lid, bf16_t* h, const int* seq_ids, const int* pos0, const int* q_lens, int B,

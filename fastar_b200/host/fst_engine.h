@@ -35,6 +35,10 @@ struct ModelConfig {
   int device = 0;
   int attn_impl = FST_MLA_IMPL_AUTO;
   int gemm_impl = FST_MLA_IMPL_AUTO;
+  // the draft model (reference draft_cfg_): its layers have the draft form of the attention and
+  // keep window_size main rows (draft_cfg_.window_size, 128)
+  bool draft = false;
+  int window_size = 128;
 };
 
 // reference LayerWeightsC (include/fst_engine.h:165-188), MLA members; bf16 [N_out, K_in].
@@ -87,6 +91,14 @@ class FSTEngine {
   // Causal among the M rows when is_prefill_ (3626).  Throws std::runtime_error on failure;
   // seq_pos_ + M > max_seq is an error (the reference asserts, 3327).
   void process_mla(int lid, bf16_t* h, int M);
+
+  // The draft model's attention (process_draft_mla, src/fst_engine.cpp:4884-5131): main_x[hidden] is
+  // the projected main hidden row -- its KV row enters the cache at the anchor position seq_pos_ --
+  // and h[M, hidden] is the block of candidates at positions seq_pos_+1 .. seq_pos_+M, which attend
+  // (densely, no causal mask) to the last window_size main rows and to the whole block; h is
+  // overwritten with the attention output, and the block's own rows are not kept.  The caller
+  // advances seq_pos_ (forward_draft does, one anchor per accepted row).
+  void process_draft_mla(int lid, bf16_t* h, int M, const bf16_t* main_x);
 
   // Batched sibling: B sequences, q_lens[b] new rows each at pos0[b]; h is [sum q_lens, hidden].
   void process_mla_batch(int lid, bf16_t* h, const int* seq_ids, const int* pos0, const int* q_lens, int B,

@@ -125,6 +125,13 @@ int fst_engine_randmat_test(FSTEngine* e, double* cosine, double* ratio, double*
   return n;
 }
 FstMlaCtx* fst_engine_ctx(FSTEngine* e) { return e->ctx(); }
+void fst_engine_set_draft(FSTEngine* e, int window_size) {
+  e->config_.draft = true;
+  e->config_.window_size = window_size;
+}
+int fst_engine_process_draft_mla(FSTEngine* e, int lid, uint16_t* h, int M, const uint16_t* main_x) {
+  return guard([&] { e->process_draft_mla(lid, h, M, main_x); });
+}
 void fst_engine_enable_compressor(FSTEngine* e, int on) { e->enable_compressor(on != 0); }
 int fst_engine_snapshot_before_verify(FSTEngine* e) { return guard([&] { e->snapshot_before_verify(); }); }
 int fst_engine_layer_cmp_ratio(FSTEngine* e, int lid) { return e->shared_.at(lid).cmp_ratio; }

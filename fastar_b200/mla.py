@@ -124,6 +124,8 @@ def load_library() -> C.CDLL:
     L.fst_cuda_mla_set_layer_rope.argtypes = [vp, C.c_int, i32]
     L.fst_cuda_mla_set_rope_theta.argtypes = [vp, C.c_float]
     L.fst_cuda_mla_set_layer_compressor.argtypes = [vp, C.c_int, C.POINTER(CompressorW)]
+    L.fst_cuda_mla_set_layer_draft_form.argtypes = [vp, C.c_int, i32]
+    L.fst_cuda_mla_append_rows.argtypes = [vp, C.c_int, u16p, i32p, i32p, i32p, i32]
     L.fst_cuda_mla_cmp_read.argtypes = [vp, C.c_int, i32, u16p, i32, i32p]
     L.fst_cuda_mla_seq_snapshot.argtypes = [vp, i32]
     L.fst_cuda_mla_comm_unique_id.argtypes = [C.POINTER(C.c_uint8)]
@@ -242,6 +244,16 @@ class MlaContext:
         ape, norm = np.ascontiguousarray(ape, np.float32), np.ascontiguousarray(norm, np.uint16)
         w = CompressorW(ratio, _u16(wkv), _u16(wgate), ape.ctypes.data_as(C.POINTER(C.c_float)), _u16(norm))
         self._check(self.lib.fst_cuda_mla_set_layer_compressor(self._h, lid, C.byref(w)))
+
+    def set_layer_draft_form(self, lid: int, on: bool = True) -> None:
+        """The draft model's form of the layer: no per-head q norm, q / output rotation on head 0 only."""
+        self._check(self.lib.fst_cuda_mla_set_layer_draft_form(self._h, lid, 1 if on else 0))
+
+    def append_rows(self, lid: int, h: np.ndarray, seq_ids, pos0, q_lens) -> None:
+        """KV side of the layer alone: rows -> kv compress, kv_norm, key RoPE, cache append."""
+        h = np.ascontiguousarray(h, np.uint16)
+        s, p, q = (np.ascontiguousarray(x, np.int32) for x in (seq_ids, pos0, q_lens))
+        self._check(self.lib.fst_cuda_mla_append_rows(self._h, lid, _u16(h), _i32(s), _i32(p), _i32(q), len(s)))
 
     def cmp_read(self, lid: int, seq: int) -> np.ndarray:
         """The compressed rows of a sequence in one layer, uint16 bf16 bits [n, kv_lora]."""

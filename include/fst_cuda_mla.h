@@ -160,6 +160,21 @@ int fst_cuda_mla_set_layer_rope(FstMlaCtx* ctx, int lid, int32_t yarn);
  * src/fst_engine.cpp:1505). */
 int fst_cuda_mla_set_rope_theta(FstMlaCtx* ctx, float theta);
 
+/* The draft model's form of the layer (process_draft_mla, src/fst_engine.cpp:4884-5131; V4 form
+ * only): no per-head query RMSNorm, the query's tail rotation and the inverse rotation of the
+ * output on head 0 only (4967-4983, 5077-5093), dense attention over the rows that are there.  The
+ * rest -- projections, norms, key RoPE by cache index, sink softmax, grouped wo_a, wo_b -- is the
+ * main layer's.  The host drives it as process_draft_mla does: the projected main hidden row is
+ * appended at the anchor position (fst_cuda_mla_append_rows), the candidate block is a
+ * non-causal layer call at anchor + 1 whose rows are dropped again afterwards
+ * (fst_cuda_mla_seq_truncate), and FstMlaSeqStep.window keeps the attention on the last
+ * window_size main rows plus the block. */
+int fst_cuda_mla_set_layer_draft_form(FstMlaCtx* ctx, int lid, int32_t on);
+/* KV side of the layer alone: h rows -> kv compress, kv_norm, key RoPE, cache append; no attention
+ * (the draft model's "main_kv from main_x", 4913-4940).  Host bf16 rows [sum q_lens, hidden]. */
+int fst_cuda_mla_append_rows(FstMlaCtx* ctx, int lid, const uint16_t* h_in, const int32_t* seq_ids,
+                             const int32_t* pos0, const int32_t* q_lens, int32_t n_seqs);
+
 /* V4 KV compressor of one layer (reference LayerWeightsC cmp_*, include/fst_engine.h:172-180,
  * loaded at src/fst_engine.cpp:1657-1690; compress_token 3171-3318).  Layers whose compress ratio
  * is 4 or 128 stream every row through the compressor in front of the attention (3545-3568): every

@@ -552,8 +552,10 @@ int fst_oracle_mla_forward_batch_cmp(const FstOracleCfg* c, const FstOracleWeigh
     parallel_for((int64_t)T * d.H, nt, [&](int64_t r0, int64_t r1) {
       for (int64_t r = r0; r < r1; ++r) {
         float* qh = q_full.data() + (size_t)r * d.q_head;
-        fst_oracle_rmsnorm(qh, nullptr, qh, 1, d.q_head, c->rms_eps, rb);
-        fst_oracle_rope_apply(qh + d.nope, pos_of[r / d.H], d.rope, c->rope_theta, c->rope_yarn, 0, rb);
+        /* the draft layer has no head norm and rotates head 0 only (4950-4983) */
+        if (!c->draft_form) fst_oracle_rmsnorm(qh, nullptr, qh, 1, d.q_head, c->rms_eps, rb);
+        if (!c->draft_form || r % d.H == 0)
+          fst_oracle_rope_apply(qh + d.nope, pos_of[r / d.H], d.rope, c->rope_theta, c->rope_yarn, 0, rb);
         std::memcpy(q_eff.data() + (size_t)r * d.d_qk, qh, d.q_head * sizeof(float));
       }
     });
@@ -612,7 +614,8 @@ int fst_oracle_mla_forward_batch_cmp(const FstOracleCfg* c, const FstOracleWeigh
         n_cmp = states[b].n_comp;
         if (causal) n_cmp = std::min(n_cmp, (pos_of[t] + 1) / cw->ratio);
       }
-      attention_row(c, d, q_eff.data() + (size_t)r * d.d_qk, caches[b], S, has_sink,
+      const int lo = c->window > 0 ? std::max(0, S - c->window) : 0;
+      attention_row(c, d, q_eff.data() + (size_t)r * d.d_qk, caches[b] + (size_t)lo * d.row, S - lo, has_sink,
                     has_sink ? w->attn_sinks[hh] : 0.0f, sc, acc, o_lat.data() + (size_t)r * d.d_v,
                     has_cmp ? states[b].cache : nullptr, n_cmp);
     });
@@ -621,8 +624,9 @@ int fst_oracle_mla_forward_batch_cmp(const FstOracleCfg* c, const FstOracleWeigh
   /* V4: inverse RoPE on every head's output tail (3716). */
   if (v4)
     for (int r = 0; r < T * d.H; ++r)
-      fst_oracle_rope_apply(o_lat.data() + (size_t)r * d.d_v + d.nope, pos_of[r / d.H], d.rope,
-                            c->rope_theta, c->rope_yarn, 1, rb);
+      if (!c->draft_form || r % d.H == 0) /* the draft layer: head 0 only (5077-5093) */
+        fst_oracle_rope_apply(o_lat.data() + (size_t)r * d.d_v + d.nope, pos_of[r / d.H], d.rope,
+                              c->rope_theta, c->rope_yarn, 1, rb);
   if (trace && trace->o_lat) std::memcpy(trace->o_lat, o_lat.data(), o_lat.size() * sizeof(float));
 
   /* O-proj a. V4 (3736-3839): low[:, g*o_lora:(g+1)*o_lora] = heads[:, g*gk:(g+1)*gk] *

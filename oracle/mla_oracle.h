@@ -45,6 +45,10 @@ typedef struct {
   int32_t use_sink;      /* V4: per-head sink logit in the softmax denominator */
   int32_t round_bf16;    /* 1: round every stage boundary to bf16 */
   int32_t n_threads;     /* worker threads (<=0: one per available core) */
+  int32_t draft_form;    /* V4: the draft model's layer (process_draft_mla, src/fst_engine.cpp:4884-5131):
+                            no per-head q norm, q and inverse output rotation on head 0 only */
+  int32_t window;        /* > 0: a query row attends only to the last `window` raw rows it may see (the
+                            draft model keeps window_size rows in a ring, 2534-2576); whole-layer calls only */
 } FstOracleCfg;
 
 /* Weights for one layer.  Unused members may be NULL.

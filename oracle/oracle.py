@@ -35,7 +35,8 @@ class OracleCfg(C.Structure):
         ("qk_rope", C.c_int32), ("v_head", C.c_int32), ("o_groups", C.c_int32),
         ("o_lora", C.c_int32), ("softmax_scale", C.c_float), ("rope_theta", C.c_float),
         ("rms_eps", C.c_float), ("rope_yarn", C.c_int32), ("use_sink", C.c_int32),
-        ("round_bf16", C.c_int32), ("n_threads", C.c_int32),
+        ("round_bf16", C.c_int32), ("n_threads", C.c_int32), ("draft_form", C.c_int32),
+        ("window", C.c_int32),
     ]
 
 
@@ -61,7 +62,7 @@ def make_cfg(preset: int = PRESET_BASELINE, *, round_bf16: bool = True, n_thread
              hidden: int = 4096, n_heads: int = 64, q_lora: int = 1024, kv_lora: int = 512,
              qk_nope: int = 128, qk_rope: int = 64, v_head: int = 128, o_groups: int = 8,
              o_lora: int = 1024, rope_yarn: bool = False, use_sink: bool | None = None,
-             softmax_scale: float | None = None) -> OracleCfg:
+             softmax_scale: float | None = None, draft_form: bool = False) -> OracleCfg:
     """Configuration of either preset.  BASELINE: 576-wide rows, scale 1/sqrt(nope+rope),
     no sink.  FASTAR_V4: 512-wide rows with a RoPE tail, scale 1/sqrt(512), sink on."""
     if preset == PRESET_BASELINE:
@@ -77,7 +78,7 @@ def make_cfg(preset: int = PRESET_BASELINE, *, round_bf16: bool = True, n_thread
         sink = use_sink
     return OracleCfg(preset, hidden, n_heads, q_lora, kv_lora, qk_nope, qk_rope, v_head, o_groups,
                      o_lora, scale, 10000.0, 1e-6, int(rope_yarn), int(sink), int(round_bf16),
-                     n_threads)
+                     n_threads, int(draft_form), 0)
 
 
 _lib = None

@@ -274,3 +274,59 @@ def test_rope_kind_follows_each_layers_compress_ratio(tmp_path, with_compressor)
         assert not np.array_equal(outs[4, 0], outs[4, 2])
     finally:
         L.fst_engine_destroy(e)
+
+
+@pytest.mark.parametrize("window", [128, 8], ids=["inside-the-window", "window-slides"])
+def test_draft_model_attention(window):
+    """process_draft_mla (src/fst_engine.cpp:4884-5131): the projected main hidden row becomes the KV
+    row at the anchor; a block of candidates at anchor+1 .. attends densely to the last window_size
+    main rows and to itself, with no per-head q norm and the q / output rotation on head 0 only; the
+    block's own rows are dropped again.  Against the oracle, anchor after anchor, with a window that
+    never fills (the reference's own regime) and one that slides."""
+    L = load()
+    L.fst_engine_set_draft.argtypes = [C.c_void_p, C.c_int]
+    L.fst_engine_process_draft_mla.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_uint16), C.c_int, C.POINTER(C.c_uint16)]
+    e = L.fst_engine_create(mla.PRESET_FASTAR_V4, 1, 128, 1, 16, 0, mla.IMPL_AUTO, mla.IMPL_AUTO)
+    assert e, L.fst_engine_last_error()
+    try:
+        L.fst_engine_set_draft(e, window)
+        bits, rounded = weights_for(mla.PRESET_FASTAR_V4)
+        for name, a in bits.items():
+            if name == "attn_sinks":
+                a = np.ascontiguousarray(a, np.float32)
+                assert L.fst_engine_set_sinks(e, 0, a.ctypes.data_as(C.POINTER(C.c_float)), a.size) == 0
+            else:
+                a = np.ascontiguousarray(a, np.uint16)
+                assert L.fst_engine_set_weight(e, 0, name.encode(), a.ctypes.data_as(C.POINTER(C.c_uint16)), a.size) == 0
+        assert L.fst_engine_preload(e) == 0, L.fst_engine_last_error()
+        cfg = mla.make_config(mla.PRESET_FASTAR_V4)
+        main_cfg = oracle_cfg(cfg)                      # the KV side is the main layer's
+        draft_cfg = oracle_cfg(cfg)
+        draft_cfg.draft_form = 1
+        cache = np.zeros((128, 512), np.float32)
+        rng = np.random.default_rng(9)
+        M = 5
+        for anchor in range(14):
+            assert L.fst_engine_seq_pos(e) == anchor
+            main_x = synth.to_bf16_bits(rng.standard_normal((1, 4096)).astype(np.float32))
+            h = synth.to_bf16_bits(rng.standard_normal((M, 4096)).astype(np.float32))
+            buf = h.copy()
+            rc = L.fst_engine_process_draft_mla(e, 0, buf.ctypes.data_as(C.POINTER(C.c_uint16)), M,
+                                                main_x.ctypes.data_as(C.POINTER(C.c_uint16)))
+            assert rc == 0, L.fst_engine_last_error()
+            # oracle: the main row enters the cache at the anchor; the block sees [window ; block]
+            O.mla_forward(main_cfg, rounded, synth.from_bf16_bits(main_x), anchor, cache, want_trace=False)
+            scratch = cache.copy()
+            draft_cfg.window = window + M if anchor + 1 > window else 0
+            want = O.mla_forward(draft_cfg, rounded, synth.from_bf16_bits(h), anchor + 1, scratch, causal=False,
+                                 want_trace=False).out
+            check_close(buf, want, f"anchor {anchor}", ulps=2)
+            L.fst_engine_advance(e, 1)
+        # only the main rows stayed in the cache
+        ctx = L.fst_engine_ctx
+        ctx.restype = C.c_void_p
+        n = C.c_int32()
+        lib = mla.load_library()
+        assert lib.fst_cuda_mla_seq_len(C.c_void_p(ctx(e)), 0, C.byref(n)) == 0 and n.value == 14
+    finally:
+        L.fst_engine_destroy(e)
