@@ -182,6 +182,7 @@ struct MergeArgs {
   int T, H, d_v, rope, inv_rope, mode;
   int threads;              // 128: rows have few parts (a thread per 4 columns); otherwise 256 (8 warps share the parts)
   int skip_single = 0;      // rows of tokens with exactly one partial are already in o_lat (AttnArgs::direct_single)
+  int wide = 0;             // few rows with many parts each: a block per (row, 128 columns) instead of per row
 };
 void launch_merge(const MergeArgs& a, cudaStream_t st);
 

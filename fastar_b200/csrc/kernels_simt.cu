@@ -656,8 +656,103 @@ __global__ void __launch_bounds__(256) k_merge_rows(MergeArgs a) {
   }
 }
 
+// Rows with MANY parts (one long sequence cut over all thread blocks): a block per (query row,
+// group of 128 columns), so that the partials of a row are read by four blocks side by side; the
+// eight warps of a block take the parts round-robin, a lane owns four columns, and the warps' sums
+// are added in warp order (deterministic).
+__global__ void __launch_bounds__(256) k_merge_wide(MergeArgs a) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ __align__(16) float s_acc[8][128];
+  __shared__ float s_red[16];
+  const int r = blockIdx.x, cg = blockIdx.y, t = r / a.H, h = r % a.H;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int p0 = a.tok_part[t], n_parts = a.tok_part[t + 1] - p0;
+  if (a.skip_single && n_parts == 1) return;
+  const bool sk = a.sinks != nullptr;
+  float M = sk ? a.sinks[h] : -INFINITY;
+  for (int p = threadIdx.x; p < n_parts; p += blockDim.x) M = fmaxf(M, a.part_m[(long long)(p0 + p) * a.H + h]);
+  M = warp_max(M);
+  if (lane == 0) s_red[warp] = M;
+  __syncthreads();
+  M = s_red[0];
+  for (int w = 1; w < 8; ++w) M = fmaxf(M, s_red[w]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float den = 0.0f;
+  const int col = cg * 128 + lane * 4;
+  // four parts per round, all their loads issued before the first use (a warp's parts are few and
+  // far apart in memory: the loop is bound by round trips, not by bytes)
+  for (int pb = warp; pb < n_parts; pb += 32) {
+    float m4[4], l4[4];
+    float4 v4[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int p = pb + 8 * q;
+      const bool on = p < n_parts;
+      const long long i = (long long)(p0 + (on ? p : pb)) * a.H + h;
+      m4[q] = on ? a.part_m[i] : -INFINITY;
+      l4[q] = a.part_l[i];
+      v4[q] = *reinterpret_cast<const float4*>(a.part_o + i * a.d_v + col);
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (m4[q] == -INFINITY) continue;
+      const float w = expf(m4[q] - M);
+      den += w * l4[q];
+      acc.x = fmaf(w, v4[q].x, acc.x);
+      acc.y = fmaf(w, v4[q].y, acc.y);
+      acc.z = fmaf(w, v4[q].z, acc.z);
+      acc.w = fmaf(w, v4[q].w, acc.w);
+    }
+  }
+  *reinterpret_cast<float4*>(&s_acc[warp][lane * 4]) = acc;
+  if (lane == 0) s_red[8 + warp] = den;
+  __syncthreads();
+  if (warp != 0) return;
+  den = sk ? expf(a.sinks[h] - M) : 0.0f;
+  for (int w = 0; w < 8; ++w) den += s_red[8 + w];
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int w = 0; w < 8; ++w) {
+    const float4 x = *reinterpret_cast<const float4*>(&s_acc[w][lane * 4]);
+    v[0] += x.x;
+    v[1] += x.y;
+    v[2] += x.z;
+    v[3] += x.w;
+  }
+  if (a.mode == 1) {
+    float* o = a.rank_partial + (long long)r * (2 + a.d_v);
+    if (cg == 0 && lane == 0) {
+      o[0] = M;
+      o[1] = den;
+    }
+    for (int e = 0; e < 4; ++e) o[2 + col + e] = v[e];
+    return;
+  }
+  const float inv = den > 0.0f ? 1.0f / (den + 1e-12f) : 0.0f;
+  for (int e = 0; e < 4; ++e) v[e] = rbf(v[e] * inv);
+  if (h < a.inv_rope && col >= a.d_v - a.rope) {
+    // inverse RoPE of the rounded output tail (reference src/fst_engine.cpp:3716)
+    const float* lut = a.lut + (long long)t * a.rope;
+    for (int e = 0; e < 4; e += 2) {
+      const int pr = (col + e - (a.d_v - a.rope)) / 2;
+      const float c = lut[2 * pr], sn = -lut[2 * pr + 1], x0 = v[e], x1 = v[e + 1];
+      v[e] = x0 * c - x1 * sn;
+      v[e + 1] = x0 * sn + x1 * c;
+    }
+  }
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 pk;
+  pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+  pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(a.o_lat + (long long)r * a.d_v + col) = pk;
+}
+
 void launch_merge(const MergeArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
+  if (a.threads != 128 && a.wide && a.d_v % 128 == 0 && a.rope % 4 == 0 && (a.d_v - a.rope) % 4 == 0) {
+    launch_pdl(k_merge_wide, dim3(a.T * a.H, a.d_v / 128), dim3(256), 0, st, 1, a);
+    return;
+  }
   if (a.threads == 128 && a.d_v <= 512 && a.d_v % 4 == 0 && (a.rope % 2) == 0 && ((a.d_v - a.rope) % 4) == 0) {
     launch_pdl(k_merge_rows, dim3((a.T * a.H + 7) / 8), dim3(256), 0, st, 1, a);
     return;

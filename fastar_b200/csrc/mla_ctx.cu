@@ -581,6 +581,7 @@ int run_merge_local(FstMlaCtx* c, int lid, int mode, float* rank_partial, bool s
   m.lut = lut_of(c, lid); m.o_lat = c->d_olat; m.rank_partial = rank_partial;
   m.T = c->T; m.H = d.H; m.d_v = d.d_v; m.rope = d.rope; m.inv_rope = inv_rope_heads(c, lid); m.mode = mode;
   m.threads = S.n_parts <= 6 * c->T ? 128 : 256;
+  m.wide = (long long)c->T * d.H < 2ll * c->n_sm ? 1 : 0;  // too few rows to fill the SMs with a block each
   launch_merge(m, c->stream);
   c->launches += 1;
   return FST_MLA_OK;
