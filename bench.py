@@ -64,6 +64,8 @@ def parse():
     ap.add_argument("--no-extras", action="store_true", help="skip the strong-scaling and long-context measurements")
     ap.add_argument("--merge-kernel", action="store_true", help="every token through its partial and the merge kernel")
     ap.add_argument("--min-timed-s", type=float, default=0.25)
+    ap.add_argument("--sequential-pages", action="store_true",
+                    help="leave the page pool in order (block tables ascend) instead of scrambling it")
     return ap.parse_args()
 
 
@@ -339,7 +341,8 @@ def measure_batch(a, torch, dist, timer, rank, world, local, sharding, with_e2e,
     from fastar_b200 import mla, workloads
     wl = workloads.build(a.workload if a.workload != "longctx" else "batched", seed=a.seed, rank=rank, world=world,
                          sharding=sharding, device=local, batch=a.batch, ctx_lo=a.ctx_lo, ctx_hi=a.ctx_hi,
-                         attn_impl=a.attn_impl, gemm_impl=a.gemm_impl, stream=torch.cuda.current_stream().cuda_stream)
+                         attn_impl=a.attn_impl, gemm_impl=a.gemm_impl, stream=torch.cuda.current_stream().cuda_stream,
+                         scramble=not a.sequential_pages)
     ctx = wl.ctx
     if a.merge_kernel:
         ctx.set_fused_merge(False)

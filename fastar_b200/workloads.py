@@ -67,19 +67,35 @@ class Workload:
         self.ctx.close()
 
 
+SCRAMBLE_SEQS = 64  # throw-away sequences of scramble_pool (the context needs that many spare slots)
+
+
 def scramble_pool(ctx: mla.MlaContext, n_pages: int, seed: int, rank: int) -> None:
-    """Leave the free list a random permutation of the pages, so that block tables are scattered."""
+    """Leave the free list a random permutation of the pages, page by page, so that every block
+    table the workload builds afterwards is a random page list.  (The pool hands out the page that
+    was freed last: pages are taken by throw-away sequences, a few hundred each, and given back one
+    sequence-truncation at a time in a seeded random order: 64 ascending runs shuffled together.)"""
     rng = synth.rng_for(seed, "perm", rank)
-    tmp = [ctx.seq_alloc() for _ in range(8)]
+    n_tmp = SCRAMBLE_SEQS
+    per = n_pages // n_tmp
+    tmp = [ctx.seq_alloc() for _ in range(n_tmp)]
     for s in tmp:
-        ctx.seq_reserve(s, 64 * (n_pages // 8))
-    for s in rng.permutation(tmp):
-        ctx.seq_free(int(s))
+        ctx.seq_reserve(s, 64 * per)
+    left = [per] * n_tmp
+    # a truncation gives back the LAST page of a throw-away sequence: picking the sequence at random
+    # every time interleaves the runs into one random order
+    order = rng.permutation(np.repeat(np.arange(n_tmp), per))
+    for i in order:
+        left[i] -= 1
+        ctx.seq_truncate(tmp[i], 64 * left[i])
+    for s in tmp:
+        ctx.seq_free(s)
 
 
 def build(name: str, *, seed: int = 0, rank: int = 0, world: int = 1, sharding: str = "replica", device: int = 0,
           batch: int = 0, ctx_lo: int = 0, ctx_hi: int = 0, attn_impl: int = mla.IMPL_AUTO,
-          gemm_impl: int = mla.IMPL_AUTO, preset: int = mla.PRESET_BASELINE, stream: int | None = None) -> Workload:
+          gemm_impl: int = mla.IMPL_AUTO, preset: int = mla.PRESET_BASELINE, stream: int | None = None,
+          scramble: bool = True) -> Workload:
     B, q_len, lo, hi, causal, desc = shape(name, batch, ctx_lo, ctx_hi)
     longctx = name == "longctx"
     cfg0 = mla.make_config(preset)
@@ -105,13 +121,14 @@ def build(name: str, *, seed: int = 0, rank: int = 0, world: int = 1, sharding: 
         h_f32 = synth.hidden_f32(cfg0, seed, B * q_len, (rank,))
     n_seq = len(my_rows)
     n_pages = sum((r + q_len + 63) // 64 for r in my_rows) + 16
-    cfg = mla.make_config(preset, n_pages=n_pages, max_tokens=max(n_seq * q_len, 1), max_seqs=n_seq + 8,
+    cfg = mla.make_config(preset, n_pages=n_pages, max_tokens=max(n_seq * q_len, 1), max_seqs=n_seq + SCRAMBLE_SEQS + 8,
                           device=device, attn_impl=attn_impl, gemm_impl=gemm_impl)
     ctx = mla.MlaContext(cfg)
     if stream is not None:
         ctx.set_stream(stream)
     ctx.set_layer_weights(0, synth.weights_to_bits(synth.layer_weights_f32(cfg, seed, 0)))
-    scramble_pool(ctx, n_pages, seed, rank)
+    if scramble:
+        scramble_pool(ctx, n_pages, seed, rank)
     seqs = []
     for b, rows in enumerate(my_rows):
         s = ctx.seq_alloc()
