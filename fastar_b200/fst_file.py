@@ -150,15 +150,47 @@ def find(entries, tid: int, layer: int, sub: int = 0):
     return None
 
 
-def load_mla_layer(path: str, lid: int, norm_path: str | None = None, entries=None) -> dict:
+def find_shape(entries, tid: int, layer: int, shape):
+    """First entry of this tensor id for the layer whose stored shape is `shape`: the way the engine
+    tells wq_a from wq_b and wo_a from wo_b (src/fst_engine.cpp:1553-1558, 1610-1615) -- one converter
+    path (scripts/fst_converter.py:636-644) stores both under the same tensor id AND sub id 0."""
+    shape = tuple(int(x) for x in shape)
+    for e in entries:
+        if e.tid == tid and e.layer in (layer, GLOBAL_LAYER) and tuple(e.shape) == shape:
+            return e
+    return None
+
+
+TID_COMPRESS_RATIOS = 40
+
+
+def compress_ratios(path: str, n_layers: int, entries=None) -> list:
+    """The per-layer KV compress ratios: TID 40 (F32 [n_layers], float -> int) when the file has
+    it, else the engine's default pattern 0, 0, 4, 128, 4, ... with layers from 41 on uncompressed
+    (src/fst_engine.cpp:1559-1590)."""
+    entries = entries if entries is not None else read_directory(path)
+    for e in entries:
+        if e.tid == TID_COMPRESS_RATIOS:
+            r = np.asarray(load_tensor(path, e)).reshape(-1)
+            if r.dtype == np.uint16:
+                r = (r.astype(np.uint32) << 16).view(np.float32)
+            return [int(r[l]) if l < r.size else 0 for l in range(n_layers)]
+    return [0 if (l < 2 or l >= 41) else (4 if l % 2 == 0 else 128) for l in range(n_layers)]
+
+
+def load_mla_layer(path: str, lid: int, norm_path: str | None = None, entries=None, shapes: dict | None = None) -> dict:
     """The MLA weights of layer `lid` as set_layer_weights takes them: bf16 bits in the reference's
     [N_out, K_in] layout, `attn_sinks` fp32.  Tensors the file does not hold are left out.  With
     norm_path, the norm weights and sinks found in that sidecar replace the main file's
-    (load_norm_override, src/fst_engine.cpp:1873)."""
+    (load_norm_override, src/fst_engine.cpp:1873).  `shapes` ({name: shape}, what the model
+    configuration expects) makes the lookup shape-first, as the engine's is: a tensor is the entry
+    of its tensor id with the expected shape, and only failing that the entry with its sub id."""
     entries = entries if entries is not None else read_directory(path)
     out = {}
     for name, (tid, sub) in MLA_TENSORS.items():
-        e = find(entries, tid, lid, sub)
+        e = find_shape(entries, tid, lid, shapes[name]) if shapes and name in shapes else None
+        if e is None:
+            e = find(entries, tid, lid, sub)
         if e is not None:
             out[name] = load_tensor(path, e)
     if norm_path is not None:

@@ -114,6 +114,62 @@ def test_shapes_against_a_configuration():
         F.check_mla_shapes(w, mla.weight_shapes(bad))
 
 
+def _write_fst(path, n_layers, tensors, theta=10000.0):
+    """A `.fst` file in the reference's layout (scripts/fst_converter.py:173-176, 685-716, 1464-1500):
+    128-byte header, 64-byte directory entries, page-aligned payloads.  tensors: (tid, layer, sub,
+    qtype, ndarray), BF16 payloads as uint16 bits and F32 as float32."""
+    import struct
+    page = lambda x: (x + 4095) & ~4095  # noqa: E731
+    dir_off = page(128)
+    off = page(dir_off + 64 * len(tensors))
+    entries = []
+    with open(path, "wb") as f:
+        for tid, layer, sub, qtype, a in tensors:
+            shape = (tuple(a.shape) + (1, 1, 1))[:3]
+            f.seek(off)
+            f.write(a.tobytes())
+            entries.append(struct.pack("<IHHHHIQQQQQQ", tid, layer, sub, qtype, a.ndim, 0, *shape, off, a.nbytes, 0))
+            off = page(off + a.nbytes)
+        f.seek(dir_off)
+        f.write(b"".join(entries))
+        f.seek(0)
+        f.write(struct.pack("<4sIIIIIIIIIIIQffQQQQQQQQ", b"FST\x00", 2, HIDDEN, n_layers, 0, 8, HEADS, 1, HEAD_DIM, 0, 1, 0,
+                            100, 1e-6, theta, dir_off, len(tensors), off, 0, 0, 0, 0, 0))
+        f.truncate(off)
+
+
+def test_tensors_stored_under_one_sub_id_are_told_apart_by_shape(tmp_path):
+    """One converter path (scripts/fst_converter.py:636-644) writes wq_a and wq_b both as (TID 5, sub 0)
+    and wo_a and wo_b both as (TID 8, sub 0); the engine finds each by its shape
+    (src/fst_engine.cpp:1553-1558, 1610-1615), takes the compress ratios from TID 40 (1559-1590) and
+    the RoPE base from the header (1505).  Given the expected shapes the reader does the same; without
+    them it falls back to sub ids and, for such a file, finds no wq_b."""
+    rng = np.random.default_rng(5)
+    bits = lambda *s: trunc_bits(rng.standard_normal(s).astype(np.float32))  # noqa: E731
+    t = {"wq_a": bits(Q_LORA, HIDDEN), "wq_b": bits(HEADS * HEAD_DIM, Q_LORA), "wkv_a": bits(KV, HIDDEN),
+         "wo_a": bits(O_LOW, HEADS * HEAD_DIM // 2), "wo_b": bits(HIDDEN, O_LOW)}
+    tensors = []
+    for l in range(3):
+        tensors += [(5, l, 0, F.QTYPE_BF16, t["wq_b"] + l), (5, l, 0, F.QTYPE_BF16, t["wq_a"] + l),
+                    (6, l, 0, F.QTYPE_BF16, t["wkv_a"] + l),
+                    (8, l, 0, F.QTYPE_BF16, t["wo_b"] + l), (8, l, 0, F.QTYPE_BF16, t["wo_a"] + l)]
+    tensors.append((F.TID_COMPRESS_RATIOS, F.GLOBAL_LAYER, 0, F.QTYPE_F32, np.array([0.0, 0.0, 4.0], np.float32)))
+    path = str(tmp_path / "sub0.fst")
+    _write_fst(path, 3, tensors, theta=50000.0)
+    shapes = {k: v.shape for k, v in t.items()}
+    for l in range(3):
+        w = F.load_mla_layer(path, l, shapes=shapes)
+        for k in t:
+            assert np.array_equal(w[k], t[k] + l), (l, k)
+    plain = F.load_mla_layer(path, 1)
+    assert "wq_b" not in plain and "wo_b" not in plain      # (TID, sub 1) does not exist in this form
+    assert F.compress_ratios(path, 3) == [0, 0, 4]
+    assert F.read_header(path).rope_freq_base == 50000.0
+    # a file without TID 40: the engine's default pattern
+    assert F.compress_ratios(MAIN, 6) == [0, 0, 4, 128, 4, 128]
+    assert F.compress_ratios(MAIN, 43)[40:] == [4, 0, 0]
+
+
 def test_malformed_files_are_errors(tmp_path):
     p = tmp_path / "bad.fst"
     p.write_bytes(b"nope" + bytes(200))
