@@ -21,11 +21,21 @@ PRESET_BASELINE = 0
 PRESET_FASTAR_V4 = 1
 
 
+def reference_tree() -> str | None:
+    """The FaStar source tree: $FST_REFERENCE, else a folder `reference` beside this repository;
+    None when neither holds the engine source."""
+    for d in (os.environ.get("FST_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if d and os.path.exists(os.path.join(d, "src", "fst_engine.cpp")):
+            return d
+    return None
+
+
 def build(with_ref: bool = True) -> None:
     """Compile the oracle (and the reference snippets when the reference tree is there)."""
     subprocess.run(["make", "-C", _HERE, "-s"], check=True)
-    if with_ref and os.path.exists("/root/reference/src/fst_engine.cpp"):
-        subprocess.run(["make", "-C", _HERE, "-s", "ref"], check=True)
+    ref = reference_tree() if with_ref else None
+    if ref:
+        subprocess.run(["make", "-C", _HERE, "-s", "ref", f"REF={ref}"], check=True)
 
 
 class OracleCfg(C.Structure):

@@ -3,8 +3,8 @@ primitives (scripts/fst_converter.py: _pack_header, _quant_shared, align_up, SHA
 TID_* / QTYPE_* constants), following the writer loop of convert_full_model_v4
 (scripts/fst_converter.py:1464-1500): header page, directory page, page-aligned payloads.
 
-Run in a container that has the FaStar tree (default /root/reference, or FST_REFERENCE):
-    python tests/golden/make_fst_fixture.py
+Run where the FaStar tree is:
+    FST_REFERENCE=/path/to/FaStar python tests/golden/make_fst_fixture.py
 The tensors are tiny (hidden 64, 4 heads) and seeded, so the test can rebuild the float values and
 check what the reader returns against them; shapes are free in the format.
 """
@@ -14,7 +14,9 @@ import sys
 
 import numpy as np
 
-REF = os.environ.get("FST_REFERENCE", "/root/reference")
+REF = os.environ.get("FST_REFERENCE")
+if not REF:
+    sys.exit("set FST_REFERENCE to the FaStar source tree")
 sys.path.insert(0, os.path.join(REF, "scripts"))
 sys.argv = sys.argv[:1]
 import fst_converter as F  # noqa: E402

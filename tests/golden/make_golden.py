@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Regenerates tests/golden/ref_vectors.npz from the reference's own code.
 
-Run in a container that has the FaStar tree (default /root/reference):
+Run where the FaStar tree is (FST_REFERENCE=/path/to/FaStar):
     make -C oracle ref && python tests/golden/make_golden.py
 
 Two sources, both executed unmodified:
@@ -24,7 +24,9 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("FST_REFERENCE", "/root/reference")
+REF = os.environ.get("FST_REFERENCE")
+if not REF:
+    sys.exit("set FST_REFERENCE to the FaStar source tree")
 
 
 def load_functions(path, names, namespace):
