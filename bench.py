@@ -63,6 +63,8 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the strong-scaling and long-context measurements")
     ap.add_argument("--merge-kernel", action="store_true", help="every token through its partial and the merge kernel")
+    ap.add_argument("--token-schedule", action="store_true",
+                    help="multi-token calls keep the token-by-token split-KV schedule (no groups of lanes sharing pages)")
     ap.add_argument("--min-timed-s", type=float, default=0.25)
     ap.add_argument("--sequential-pages", action="store_true",
                     help="leave the page pool in order (block tables ascend) instead of scrambling it")
@@ -346,6 +348,8 @@ def measure_batch(a, torch, dist, timer, rank, world, local, sharding, with_e2e,
     ctx = wl.ctx
     if a.merge_kernel:
         ctx.set_fused_merge(False)
+    if a.token_schedule:
+        ctx.set_block_schedule(False)
     T = wl.T
     h_host = torch.from_numpy(wl.h_bits.view(np.int16)).pin_memory()
     out_host = torch.empty_like(h_host).pin_memory()

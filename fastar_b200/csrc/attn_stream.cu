@@ -92,6 +92,7 @@ struct StreamParams {
   const float* sinks;       // [64] or null
   const float* lut;         // [T, rope] (cos, sin): inverse RoPE of the output tail of heads 0 .. inv_rope-1
   int rope, inv_rope;
+  int tiles_shared;  // other blocks read the same tiles at about the same time: normal L2 priority
 };
 
 
@@ -326,8 +327,9 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
       cur.init(p.segs, seg0, seg1);
       bool ok = true;
       // cache tiles are read once and are more than L2 holds: they leave L2 first, so that the
-      // partials written here are still there when the merge reads them
-      const uint64_t stream_policy = tc::l2_policy_evict_first();
+      // partials written here are still there when the merge reads them -- unless the schedule
+      // has the lanes of a group read the same tiles side by side (blocks of query tokens)
+      const uint64_t stream_policy = p.tiles_shared ? tc::l2_policy_evict_normal() : tc::l2_policy_evict_first();
       // the chunks of slot g that this producer copies, from rows row0 .. row0+63 of `map`
       auto fill = [&](int g, const CUtensorMap* map, int row0) -> bool {
         const int c0 = (r + 3 - (g * NCH) % 3) % 3;
@@ -680,6 +682,7 @@ cudaError_t launch_attn_stream(const AttnArgs& a, cudaStream_t st) {
   p.direct = a.direct_single ? 1 : 0;
   p.tok_part = a.tok_part; p.o_lat = a.o_lat; p.sinks = a.sinks; p.lut = a.lut;
   p.rope = a.rope; p.inv_rope = a.inv_rope;
+  p.tiles_shared = a.tiles_shared ? 1 : 0;
   if (a.d_qk == 576) {
     if (p.direct) return launch_pdl(k_attn_stream<9, true>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(9), st, 1, tmKV, tmQ, p);
     return launch_pdl(k_attn_stream<9, false>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(9), st, 1, tmKV, tmQ, p);

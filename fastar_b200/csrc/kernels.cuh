@@ -154,6 +154,9 @@ struct AttnArgs {
   long long q_rows;         // rows of q_eff (new tokens * H)
   long long pool_rows;      // n_pages * page_tokens
   float scale;
+  // the schedule makes several thread blocks read the same cache tiles at about the same time
+  // (blocks of query tokens): tiles then keep the normal L2 priority instead of leaving first
+  bool tiles_shared = false;
   // tcgen05 kernel only: a token whose whole context is ONE segment of the schedule (one partial)
   // is normalised and written to o_lat by the attention kernel itself and leaves no partial; the
   // merge kernel that follows is told to skip such tokens (MergeArgs::skip_single).

@@ -85,6 +85,7 @@ struct Sched {
   int n_segs = 0, n_parts = 0, n_ctas = 0;
   long long kv_rows = 0;
   int max_tok_parts = 0, min_tok_parts = 0, n_single_part = 0;
+  bool by_blocks = false;  // cut_block_schedule made it: the lanes of a group read the same pages side by side
   // what the compressor kernel of this class reads (classes 1, 2)
   CompressTok* d_ctoks = nullptr;
   CompressStep* d_csteps = nullptr;
@@ -123,6 +124,7 @@ struct FstMlaCtx {
   float *d_part_m = nullptr, *d_part_l = nullptr, *d_part_o = nullptr;
   int max_parts = 0;
   bool fused_merge = true;       // the attention kernel finishes single-partial tokens itself
+  bool block_schedule = true;    // calls with G >= 4 new tokens per sequence: thread blocks in groups of G lanes
   Sched sched[N_CLASSES];        // the current plan's schedule per layer class
   int info_class = 0;            // class of the layer that ran last (plan_info reports its schedule)
   bool has_cmp = false;          // some layer has a KV compressor
@@ -419,6 +421,7 @@ AttnArgs attn_args(FstMlaCtx* c, int lid, const bf16* q_eff, bool may_fuse = fal
   a.pool_rows = (long long)c->cfg.n_pages * c->cfg.page_tokens;
   a.q_rows = (long long)c->T * c->d.H;
   a.scale = c->cfg.softmax_scale;
+  a.tiles_shared = S.by_blocks;
   if (may_fuse && c->fused_merge && S.n_single_part > 0) {
     a.direct_single = true;
     a.tok_part = S.d_tok_part;
@@ -1295,7 +1298,8 @@ struct TileStream {
 // pays for its Q_eff block (one ring slot), refilling the pipeline and writing its partial
 // (measured inside the pipelined layer: about three 64-token tiles of the streaming kernel).
 void cut_schedule(const FstMlaCtx* c, const std::vector<TileStream>& streams, int T, std::vector<AttnSeg>* segs_out,
-                  std::vector<int32_t>* cta_seg_out, std::vector<int32_t>* tok_part_out, long long* kv_rows_out) {
+                  std::vector<int32_t>* cta_seg_out, std::vector<int32_t>* tok_part_out, long long* kv_rows_out,
+                  int max_ctas = 0) {
   const int unit = c->cfg.page_tokens == 64 ? 64 : ATTN_TILE;
   const long long SEG_COST2 = unit == 64 ? 6 : 5;
   const int n_streams = (int)streams.size();
@@ -1308,7 +1312,7 @@ void cut_schedule(const FstMlaCtx* c, const std::vector<TileStream>& streams, in
     kv_rows += streams[i].hi - streams[i].lo;
     n_nonempty += streams[i].hi > 0;
   }
-  const int n_ctas = (int)std::min<long long>(c->n_sm, std::max<long long>(total_tiles, 1));
+  const int n_ctas = (int)std::min<long long>(max_ctas > 0 ? max_ctas : c->n_sm, std::max<long long>(total_tiles, 1));
   std::vector<AttnSeg>& segs = *segs_out;
   std::vector<int32_t>& cta_seg = *cta_seg_out;
   std::vector<int32_t> parts_of(T, 0);
@@ -1363,6 +1367,75 @@ void cut_schedule(const FstMlaCtx* c, const std::vector<TileStream>& streams, in
   *kv_rows_out = kv_rows;
 }
 
+// The schedule for BLOCKS of query tokens (speculative verify, prefill chunks over a long context:
+// every sequence of the call brings the same number G >= 4 of new tokens, which all attend to the
+// same rows but for the causal edge).  Cutting token after token would let the G tokens of a
+// sequence walk its pages at G different times, and each page would come from HBM G times (measured:
+// 13 x the cache bytes for 16-token blocks, L2 hit rate 29 %).  Here the thread blocks form
+// n_sm / G GROUPS of G lanes; the sequences' page columns are cut into one run per group exactly as
+// the token schedule cuts tiles; lane i of a group walks its group's run for token i of each
+// sequence, so the G lanes read the same page at about the same time and it crosses the HBM
+// interface once.  Returns false (nothing written) when the call is not of that shape.
+bool cut_block_schedule(const FstMlaCtx* c, int T, std::vector<AttnSeg>* segs_out, std::vector<int32_t>* cta_seg_out,
+                        std::vector<int32_t>* tok_part_out, long long* kv_rows_out) {
+  const int unit = 64;
+  if (c->cfg.page_tokens != unit) return false;
+  int G = 0, n_seq = 0;
+  for (const FstMlaSeqStep& st : c->pl_steps) {
+    if (st.q_len == 0) continue;
+    if (G && st.q_len != G) return false;
+    G = st.q_len;
+    ++n_seq;
+  }
+  if (G < 4 || G > c->n_sm) return false;
+  for (int t = 0; t < T; ++t)
+    if (c->pl_kvlo[t] != 0) return false;  // sliding windows keep the token schedule
+  const int n_groups = c->n_sm / G;
+  // one stream per sequence: the rows its last token sees (the tokens of a step are adjacent)
+  std::vector<TileStream> cols;
+  long long kv_rows = 0, n_cols = 0;
+  for (int t0 = 0; t0 < T; t0 += G) {
+    int hi = 0;
+    for (int i = 0; i < G; ++i) {
+      hi = std::max(hi, c->pl_kvlen[t0 + i]);
+      kv_rows += c->pl_kvlen[t0 + i];
+    }
+    cols.push_back(TileStream{t0, c->pl_tok_table[t0], 0, hi});
+    n_cols += (hi + unit - 1) / unit;
+  }
+  if (n_cols < 2ll * n_groups) return false;  // too little work per group to cut it this way
+  std::vector<AttnSeg> gsegs;
+  std::vector<int32_t> g_seg, unused;
+  long long unused_rows = 0;
+  cut_schedule(c, cols, T, &gsegs, &g_seg, &unused, &unused_rows, n_groups);
+  const int groups = (int)g_seg.size() - 1;
+  std::vector<AttnSeg>& segs = *segs_out;
+  segs.clear();
+  cta_seg_out->assign((size_t)groups * G + 1, 0);
+  std::vector<int32_t> parts_of(T, 0);
+  for (int g = 0; g < groups; ++g)
+    for (int i = 0; i < G; ++i) {
+      (*cta_seg_out)[g * G + i] = (int)segs.size();
+      for (int k = g_seg[g]; k < g_seg[g + 1]; ++k) {
+        const int t = gsegs[k].tok + i;
+        AttnSeg sg = gsegs[k];
+        sg.tok = t;
+        sg.table = c->pl_tok_table[t];
+        sg.kv_end = std::min(sg.kv_end, c->pl_kvlen[t]);
+        if (sg.kv_end <= sg.kv_begin) continue;  // the causal edge: this token does not reach the run
+        sg.part = parts_of[t]++;                   // for now the index among the token's parts
+        segs.push_back(sg);
+      }
+    }
+  (*cta_seg_out)[(size_t)groups * G] = (int)segs.size();
+  tok_part_out->assign(T + 1, 0);
+  for (int t = 0; t < T; ++t) (*tok_part_out)[t + 1] = (*tok_part_out)[t] + parts_of[t];
+  // a token's parts ascend with the group index, i.e. with the rows they cover
+  for (AttnSeg& sg : segs) sg.part += (*tok_part_out)[sg.tok];
+  *kv_rows_out = kv_rows;
+  return true;
+}
+
 // The second part: schedules (one per layer class in use) and block tables.  on_copy_stream:
 // upload it beside the kernels that already run on the context's stream (which then waits for
 // it); else one copy of the whole blob (or of the second part, if the first went ahead) on the
@@ -1409,7 +1482,8 @@ int plan_schedule_part(FstMlaCtx* c, bool on_copy_stream) {
       }
     }
     long long kv_rows = 0;
-    cut_schedule(c, streams, T, &segs, &cta_seg, &tok_part, &kv_rows);
+    S.by_blocks = k == 0 && c->block_schedule && cut_block_schedule(c, T, &segs, &cta_seg, &tok_part, &kv_rows);
+    if (!S.by_blocks) cut_schedule(c, streams, T, &segs, &cta_seg, &tok_part, &kv_rows);
     if ((int)segs.size() > c->segs_cap || (int)segs.size() > c->max_parts)
       return fail(FST_MLA_ERR_CAPACITY, "split schedule overflow");
     S.d_tok_part = reinterpret_cast<int32_t*>(put(tok_part.data(), (size_t)(T + 1) * sizeof(int32_t)));
@@ -1464,6 +1538,13 @@ int fst_cuda_mla_plan(FstMlaCtx* c, const FstMlaSeqStep* steps, int32_t n_seqs, 
 int fst_cuda_mla_set_plan_reuse(FstMlaCtx* c, int32_t on) {
   if (!c) return fail(FST_MLA_ERR_ARG, "null context");
   c->plan_reuse = on != 0;
+  return FST_MLA_OK;
+}
+
+int fst_cuda_mla_set_block_schedule(FstMlaCtx* c, int32_t on) {
+  if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  if (c->block_schedule != (on != 0)) c->planned = false;  // the next call builds its plan anew
+  c->block_schedule = on != 0;
   return FST_MLA_OK;
 }
 

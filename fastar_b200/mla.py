@@ -120,6 +120,7 @@ def load_library() -> C.CDLL:
     L.fst_cuda_mla_set_plan_reuse.argtypes = [vp, i32]
     L.fst_cuda_mla_set_window.argtypes = [vp, i32]
     L.fst_cuda_mla_set_fused_merge.argtypes = [vp, i32]
+    L.fst_cuda_mla_set_block_schedule.argtypes = [vp, i32]
     L.fst_cuda_mla_plan_counts.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
     L.fst_cuda_mla_set_layer_rope.argtypes = [vp, C.c_int, i32]
     L.fst_cuda_mla_set_rope_theta.argtypes = [vp, C.c_float]
@@ -343,6 +344,10 @@ class MlaContext:
     def set_plan_reuse(self, on: bool) -> None:
         """Whether a plan request equal to the valid plan keeps it (default) or rebuilds it."""
         self._check(self.lib.fst_cuda_mla_set_plan_reuse(self._h, 1 if on else 0))
+
+    def set_block_schedule(self, on: bool) -> None:
+        """Calls with G >= 4 new tokens per sequence: thread blocks in groups of G lanes that share pages."""
+        self._check(self.lib.fst_cuda_mla_set_block_schedule(self._h, 1 if on else 0))
 
     def set_fused_merge(self, on: bool) -> None:
         """Let the attention kernel finish tokens that have a single partial itself (default)."""

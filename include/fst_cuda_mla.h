@@ -242,6 +242,15 @@ int fst_cuda_mla_set_plan_reuse(FstMlaCtx* ctx, int32_t on);
  * such a token: verify blocks and prefill chunks mostly are).  on = 0: every token goes through
  * its partial and the merge kernel.  Both give the same bits.  Default: on. */
 int fst_cuda_mla_set_fused_merge(FstMlaCtx* ctx, int32_t on);
+/* Calls in which every sequence brings the same number G >= 4 of new tokens (speculative-verify
+ * blocks, prefill chunks over a long context; the engine's M_PAD = 16 rows per call,
+ * src/fst_engine.cpp:2959, 3573-3589) are scheduled by BLOCKS: the thread blocks form n_sm / G
+ * groups of G lanes, the page columns of the sequences are cut into one run per group, and lane i
+ * walks its group's run for token i -- so the G tokens of a sequence read each cache page at the
+ * same time and it comes from HBM once, not G times.  on = 0: the token-by-token schedule of
+ * decode for every call.  Results do not depend on it beyond the order of a token's parts.
+ * Default: on. */
+int fst_cuda_mla_set_block_schedule(FstMlaCtx* ctx, int32_t on);
 /* Sliding window that fst_cuda_mla_forward applies to every sequence of its calls (0: none). */
 int fst_cuda_mla_set_window(FstMlaCtx* ctx, int32_t window);
 /* Plans built and plan requests answered by the valid plan, since the context was created. */

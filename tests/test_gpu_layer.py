@@ -104,6 +104,48 @@ def test_verify_block_causal(impl):
     run_layer(mla.PRESET_BASELINE, impl, [200, 64], 16, True, seed=2)
 
 
+@pytest.mark.parametrize("preset", [mla.PRESET_BASELINE, mla.PRESET_FASTAR_V4], ids=["baseline", "v4"])
+@pytest.mark.parametrize("q_len,causal", [(16, True), (5, False)], ids=["verify-16", "dense-5"])
+def test_blocks_of_tokens_scheduled_by_groups_of_lanes(preset, q_len, causal):
+    """Calls with G >= 4 new tokens per sequence and enough pages are cut by BLOCKS (n_sm / G groups of
+    G thread blocks, lane i of a group takes token i of each sequence over the group's run of page
+    columns).  Lengths around page boundaries make the causal edge bite: with 255 cached rows token 0
+    of a 16-token block ends in page 3 and the others reach page 4; with 1023 the block ends
+    exactly at a boundary.  Against the oracle stage by stage, two consecutive calls."""
+    run_layer(preset, IMPLS[1], [255, 256, 1023, 64 * 30 + 3, 700, 0, 4000], q_len, causal, seed=7, steps=2, ulps=2)
+
+
+def test_block_schedule_against_the_token_schedule():
+    """The same 16-token verify call under both schedules: the block schedule uses whole groups of 16
+    thread blocks and leaves most tokens in one part; outputs agree to the rounding of a bf16 step
+    (the parts are cut at other rows, so the fp32 sums differ in their last bits)."""
+    lens, q = [3000, 1500, 2047, 900, 4100, 64], 16
+    B = len(lens)
+    cfg = mla.make_config(mla.PRESET_BASELINE, n_pages=sum((L + q + 63) // 64 for L in lens) + 4, max_tokens=B * q, max_seqs=B)
+    bits, _ = weights_for(mla.PRESET_BASELINE)
+    with mla.MlaContext(cfg) as ctx:
+        ctx.set_layer_weights(0, bits)
+        seqs = []
+        for b, L in enumerate(lens):
+            s = ctx.seq_alloc()
+            ctx.cache_write(0, s, 0, synth.to_bf16_bits(synth.cache_rows_f32(cfg, 12, b, L)))
+            seqs.append(s)
+        h = synth.to_bf16_bits(synth.hidden_f32(cfg, 12, B * q))
+        res = {}
+        for key, on in (("blocks", True), ("tokens", False), ("blocks again", True)):
+            ctx.set_block_schedule(on)
+            out = ctx.forward(0, h, seqs, lens, [q] * B, causal=True)
+            res[key] = (out.copy(), ctx.plan_info())
+            for s, L in zip(seqs, lens):
+                ctx.seq_truncate(s, L)
+        n_sm = res["tokens"][1]["n_ctas"]
+        assert res["blocks"][1]["n_ctas"] == n_sm // q * q
+        assert res["blocks"][1]["kv_rows"] == res["tokens"][1]["kv_rows"] == sum(L + i + 1 for L in lens for i in range(q))
+        assert res["blocks"][1]["n_partials"] < res["tokens"][1]["n_partials"]
+        assert np.array_equal(res["blocks"][0], res["blocks again"][0])
+        check_close(res["blocks"][0], synth.from_bf16_bits(res["tokens"][0]), "block schedule vs token schedule", ulps=1)
+
+
 @pytest.mark.parametrize("impl", IMPLS, ids=[i[0] for i in IMPLS])
 def test_prefill_from_empty(impl):
     # the reference's own regime: 16-token chunks from position 0 (prefill_tiled, 2957-2984)
