@@ -100,7 +100,8 @@ struct StreamMisc {
   uint64_t full_t[4][3]; // chunks 3i .. 3i+2 of tile g have landed: barrier [g & 3][i]
   uint64_t o_done[4];    // the SV MMAs of tile g have retired (its ring slots are free): barrier g & 3
   uint64_t q_ready;      // Q_eff of a segment written to tensor memory by the softmax threads
-  uint64_t s_full[2];    // both score partials of tile g are complete: barrier g & 1 (two commits)
+  uint64_t s_full[3];    // both score partials of tile n are complete: barrier n & 1 (two commits); WHOLE: the
+                         // scores of tile n, barrier n % 3 -- one per buffer, as the QK MMAs may run three tiles ahead
   uint64_t s_free[3];    // the softmax threads have read the partial in this score buffer
   uint64_t p_full[3];    // the probabilities of tile n are written: barrier n % 3
   uint32_t tmem_slot;
@@ -279,7 +280,13 @@ __device__ __forceinline__ bool qk_chunks(StreamMisc* mi, int g, uint32_t d, uin
 // DIRECT: tokens with a single partial are finished here (finish_token); the variant without it is
 // the one batched decode runs, where every token is split (the mere presence of that code in the
 // kernel costs 2-3 us of 85 there, measured).
-template <int NCH, bool DIRECT>
+// WHOLE: each QK issuer takes whole tiles (alternating) into one score buffer per tile, instead of
+// half of every tile's chunks into a buffer of its own.  A tile's scores then take longer to
+// complete, but three buffers hold three tiles, so the QK MMAs run ahead of the softmax instead of
+// waiting for it to free a buffer -- the better trade when tiles come from L2 (blocks of query
+// tokens: the kernel is bound by its own pipeline there; attention of the 32 x 16 x 16384 verify block
+// 1.69 -> 1.55 ms), the worse one when the life of a frame bounds the kernel (decode: 86 -> 88 us).
+template <int NCH, bool DIRECT, bool WHOLE>
 __global__ void __launch_bounds__(ST_THREADS, 1)
 k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ CUtensorMap tmQ, StreamParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -297,7 +304,7 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
       tc::mbar_init(&mi->o_done[i], 1);
     }
     tc::mbar_init(&mi->q_ready, 256);
-    for (int i = 0; i < 2; ++i) tc::mbar_init(&mi->s_full[i], 2);
+    for (int i = 0; i < 3; ++i) tc::mbar_init(&mi->s_full[i], WHOLE ? 1 : 2);
     for (int i = 0; i < 3; ++i) tc::mbar_init(&mi->s_free[i], 256);
     for (int i = 0; i < 3; ++i) tc::mbar_init(&mi->p_full[i], 256);
     mi->abort_flag = 0;
@@ -374,16 +381,21 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
           ok = tc::mbar_wait(&mi->q_ready, cur.sidx & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
           if (ok && part == 0) tc::mbar_arrive(&mi->o_done[cur.gq & 3]);
         }
-        const int k = 2 * n + part, buf = k % 3, use = k / 3;
+        if (WHOLE && (n & 1) != part) {  // the other issuer's tile
+          cur.next(p.segs);
+          continue;
+        }
+        const int k = WHOLE ? n : 2 * n + part, buf = k % 3, use = k / 3;
         // the softmax threads have read the previous partial in this buffer
         if (ok && use >= 1) ok = tc::mbar_wait(&mi->s_free[buf], (use - 1) & 1, abort_flag, p.d_status, ST_MMA_TIMEOUT);
         if (!ok) break;
         const uint32_t d = tmem + COL_S + buf * TILE;  // same lanes as the TMEM-resident A
         const uint32_t frame16 = ring16 + (g % 3) * NCH * (CHUNK / 16);
-        if (part == 0) ok = qk_chunks<0, 5>(mi, g, d, tmem, frame16, abort_flag, p.d_status);
+        if (WHOLE) ok = qk_chunks<0, NCH>(mi, g, d, tmem, frame16, abort_flag, p.d_status);
+        else if (part == 0) ok = qk_chunks<0, 5>(mi, g, d, tmem, frame16, abort_flag, p.d_status);
         else ok = qk_chunks<5, NCH>(mi, g, d, tmem, frame16, abort_flag, p.d_status);
         if (!ok) break;
-        tc::umma_commit(&mi->s_full[n & 1]);
+        tc::umma_commit(&mi->s_full[WHOLE ? n % 3 : n & 1]);
         cur.next(p.segs);
       }
     }
@@ -485,17 +497,22 @@ k_attn_stream(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ 
       for (int t = 0; t < n_tiles && ok; ++t, cur.next(p.segs)) {
         g = cur.g;
         const int n = cur.n;
-        ok = tc::mbar_wait(&mi->s_full[n & 1], (n >> 1) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
+        ok = tc::mbar_wait(&mi->s_full[WHOLE ? n % 3 : n & 1], (WHOLE ? n / 3 : n >> 1) & 1, abort_flag, p.d_status, ST_SOFTMAX_TIMEOUT);
         tc::tc_fence_after();
         // this thread's first token, relative to the first visible row; visible: [0, span)
         const int rel0 = (sg.kv_begin & ~(TILE - 1)) - sg.kv_begin + t * TILE + half * 32 + sub * 16;
         float sc[16], sc2[16];
-        const int b0 = (2 * n) % 3, b1 = (2 * n + 1) % 3;
+        const int b0 = WHOLE ? n % 3 : (2 * n) % 3, b1 = (2 * n + 1) % 3;
         tmem_ld16x32(lane_addr + COL_S + b0 * TILE + half * 32, sc);
-        tmem_ld16x32(lane_addr + COL_S + b1 * TILE + half * 32, sc2);
+        if (WHOLE) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sc2[j] = 0.0f;
+        } else {
+          tmem_ld16x32(lane_addr + COL_S + b1 * TILE + half * 32, sc2);
+        }
         tc::tc_fence_before();
         tc::mbar_arrive(&mi->s_free[b0]);
-        tc::mbar_arrive(&mi->s_free[b1]);
+        if (!WHOLE) tc::mbar_arrive(&mi->s_free[b1]);
         float mx = -INFINITY;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -683,12 +700,16 @@ cudaError_t launch_attn_stream(const AttnArgs& a, cudaStream_t st) {
   p.tok_part = a.tok_part; p.o_lat = a.o_lat; p.sinks = a.sinks; p.lut = a.lut;
   p.rope = a.rope; p.inv_rope = a.inv_rope;
   p.tiles_shared = a.tiles_shared ? 1 : 0;
+  const bool whole = a.tiles_shared;
+#define FST_ATTN_LAUNCH(NCHV, DIR, WH) \
+  launch_pdl(k_attn_stream<NCHV, DIR, WH>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(NCHV), st, 1, tmKV, tmQ, p)
   if (a.d_qk == 576) {
-    if (p.direct) return launch_pdl(k_attn_stream<9, true>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(9), st, 1, tmKV, tmQ, p);
-    return launch_pdl(k_attn_stream<9, false>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(9), st, 1, tmKV, tmQ, p);
+    if (whole) return p.direct ? FST_ATTN_LAUNCH(9, true, true) : FST_ATTN_LAUNCH(9, false, true);
+    return p.direct ? FST_ATTN_LAUNCH(9, true, false) : FST_ATTN_LAUNCH(9, false, false);
   }
-  if (p.direct) return launch_pdl(k_attn_stream<8, true>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(8), st, 1, tmKV, tmQ, p);
-  return launch_pdl(k_attn_stream<8, false>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(8), st, 1, tmKV, tmQ, p);
+  if (whole) return p.direct ? FST_ATTN_LAUNCH(8, true, true) : FST_ATTN_LAUNCH(8, false, true);
+  return p.direct ? FST_ATTN_LAUNCH(8, true, false) : FST_ATTN_LAUNCH(8, false, false);
+#undef FST_ATTN_LAUNCH
 }
 
 }  // namespace fst

@@ -155,7 +155,8 @@ struct AttnArgs {
   long long pool_rows;      // n_pages * page_tokens
   float scale;
   // the schedule makes several thread blocks read the same cache tiles at about the same time
-  // (blocks of query tokens): tiles then keep the normal L2 priority instead of leaving first
+  // (blocks of query tokens): tiles then keep the normal L2 priority instead of leaving first, and
+  // the tcgen05 kernel lets each QK issuer take whole tiles (k_attn_stream, WHOLE)
   bool tiles_shared = false;
   // tcgen05 kernel only: a token whose whole context is ONE segment of the schedule (one partial)
   // is normalised and written to o_lat by the attention kernel itself and leaves no partial; the

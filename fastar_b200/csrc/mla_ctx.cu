@@ -2029,6 +2029,51 @@ int fst_cuda_mla_debug_attr_first_use(uint64_t kernel_key, int32_t device, int64
                                           value) ? 1 : 0;
 }
 
+int fst_cuda_mla_debug_schedule(int32_t n_sm, const int32_t* pos0, const int32_t* q_lens, int32_t n_seqs, int32_t causal,
+                                int32_t by_blocks, int32_t* segs_out, int32_t cap, int32_t* n_segs_out, int32_t* n_ctas_out,
+                                int32_t* cut_by_blocks_out) {
+  if (!pos0 || !q_lens || !segs_out || !n_segs_out || !n_ctas_out || n_sm < 1 || n_seqs < 0 || cap < 0)
+    return fail(FST_MLA_ERR_ARG, "bad argument");
+  // a context that never touches a device: only what the two cutting functions read
+  FstMlaCtx c;
+  memset(&c.cfg, 0, sizeof(c.cfg));
+  c.cfg.page_tokens = 64;
+  c.n_sm = n_sm;
+  c.pl_causal = causal;
+  int T = 0;
+  for (int b = 0; b < n_seqs; ++b) {
+    if (pos0[b] < 0 || q_lens[b] < 0) return fail(FST_MLA_ERR_ARG, "negative position or length");
+    c.pl_steps.push_back(FstMlaSeqStep{b, pos0[b], q_lens[b], -1, 1, 0});
+    for (int i = 0; i < q_lens[b]; ++i, ++T) {
+      c.pl_tok_table.push_back(b);  // stands for the offset of the sequence's block table
+      c.pl_kvlen.push_back(causal ? pos0[b] + i + 1 : pos0[b] + q_lens[b]);
+      c.pl_kvlo.push_back(0);
+    }
+  }
+  std::vector<AttnSeg> segs;
+  std::vector<int32_t> cta_seg, tok_part;
+  long long kv_rows = 0;
+  bool blocks = by_blocks && cut_block_schedule(&c, T, &segs, &cta_seg, &tok_part, &kv_rows);
+  if (!blocks) {
+    std::vector<TileStream> streams;
+    for (int t = 0; t < T; ++t) streams.push_back(TileStream{t, c.pl_tok_table[t], 0, c.pl_kvlen[t]});
+    cut_schedule(&c, streams, T, &segs, &cta_seg, &tok_part, &kv_rows);
+  }
+  if ((int)segs.size() > cap) return fail(FST_MLA_ERR_CAPACITY, "%d segments, room for %d", (int)segs.size(), cap);
+  const int n_ctas = (int)cta_seg.size() - 1;
+  for (int k = 0; k < n_ctas; ++k)
+    for (int i = cta_seg[k]; i < cta_seg[k + 1]; ++i) {
+      int32_t* o = segs_out + 5 * (size_t)i;
+      o[0] = segs[i].tok; o[1] = segs[i].kv_begin; o[2] = segs[i].kv_end; o[3] = segs[i].part; o[4] = k;
+      if (segs[i].part < tok_part[segs[i].tok] || segs[i].part >= tok_part[segs[i].tok + 1])
+        return fail(FST_MLA_ERR_STATE, "segment %d: part %d outside its token's range", i, segs[i].part);
+    }
+  *n_segs_out = (int)segs.size();
+  *n_ctas_out = n_ctas;
+  if (cut_by_blocks_out) *cut_by_blocks_out = blocks ? 1 : 0;
+  return FST_MLA_OK;
+}
+
 int fst_cuda_mla_debug_set_status(FstMlaCtx* c, int32_t code) {
   if (!c) return fail(FST_MLA_ERR_ARG, "null context");
   CU(cudaSetDevice(c->cfg.device));

@@ -121,6 +121,7 @@ def load_library() -> C.CDLL:
     L.fst_cuda_mla_set_window.argtypes = [vp, i32]
     L.fst_cuda_mla_set_fused_merge.argtypes = [vp, i32]
     L.fst_cuda_mla_set_block_schedule.argtypes = [vp, i32]
+    L.fst_cuda_mla_debug_schedule.argtypes = [i32, i32p, i32p, i32, i32, i32, i32p, i32, i32p, i32p, i32p]
     L.fst_cuda_mla_plan_counts.argtypes = [vp, C.POINTER(i64), C.POINTER(i64)]
     L.fst_cuda_mla_set_layer_rope.argtypes = [vp, C.c_int, i32]
     L.fst_cuda_mla_set_rope_theta.argtypes = [vp, C.c_float]
@@ -173,6 +174,24 @@ def weight_shapes(cfg: Config) -> dict:
     else:
         sh["wkv_b"] = (H * (cfg.qk_nope + cfg.v_head), cfg.kv_lora)
     return sh
+
+
+def debug_schedule(n_sm: int, pos0, q_lens, causal: bool, by_blocks: bool = True):
+    """The split-KV schedule of a call as the library cuts it, on the host alone (no device needed):
+    (segments [n, 5] = token, first row, end row, partial slot, thread block; number of thread blocks;
+    whether the block schedule cut it)."""
+    L = load_library()
+    p0 = np.ascontiguousarray(pos0, np.int32)
+    ql = np.ascontiguousarray(q_lens, np.int32)
+    cap = int(ql.sum()) + n_sm + 8
+    segs = np.zeros((cap, 5), np.int32)
+    n, k, b = C.c_int32(0), C.c_int32(0), C.c_int32(0)
+    i32p = C.POINTER(C.c_int32)
+    rc = L.fst_cuda_mla_debug_schedule(n_sm, p0.ctypes.data_as(i32p), ql.ctypes.data_as(i32p), len(p0), int(causal),
+                                       int(by_blocks), segs.ctypes.data_as(i32p), cap, C.byref(n), C.byref(k), C.byref(b))
+    if rc:
+        raise MlaError(rc, L.fst_cuda_mla_last_error().decode())
+    return segs[:n.value].copy(), k.value, bool(b.value)
 
 
 class MlaContext:

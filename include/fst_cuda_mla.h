@@ -348,6 +348,15 @@ int fst_cuda_mla_family_counts(FstMlaCtx* ctx, int64_t* tensor_out, int64_t* sim
  * tensor memory) waits on a barrier that nothing arrives at, with a limit of `polls` polls
  * (1 .. 65536), gives up and records its status.  Enqueued on the context's stream. */
 int fst_cuda_mla_selftest_wait_expiry(FstMlaCtx* ctx, int32_t polls);
+/* The split-KV schedule of a call, cut on the host without any device (for tests of the cutting
+ * rules): sequences b = 0 .. n_seqs-1 bring q_lens[b] new rows at pos0[b]; a row sees [0, pos0 + i + 1)
+ * when causal, [0, pos0 + q_len) otherwise; n_sm thread blocks; by_blocks allows the block schedule
+ * (fst_cuda_mla_set_block_schedule).  segs_out receives five values per segment, in the order the
+ * thread blocks walk them: token, first row, end row, partial slot, thread block.
+ * *cut_by_blocks_out tells which rule cut it. */
+int fst_cuda_mla_debug_schedule(int32_t n_sm, const int32_t* pos0, const int32_t* q_lens, int32_t n_seqs, int32_t causal,
+                                int32_t by_blocks, int32_t* segs_out, int32_t cap, int32_t* n_segs_out,
+                                int32_t* n_ctas_out, int32_t* cut_by_blocks_out);
 /* Test hook: writes `code` into the device status word, as a kernel that failed a check would. */
 int fst_cuda_mla_debug_set_status(FstMlaCtx* ctx, int32_t code);
 /* Test hook, host only (no CUDA call): the library sets function attributes (the dynamic
