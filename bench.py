@@ -141,6 +141,15 @@ def ncu_traffic():
         return None
 
 
+def verify_traffic():
+    """DRAM bytes per row of a SEQUENCE for the attention kernel on blocks of 16 query tokens, from
+    the committed ncu capture at 8 sequences (profiles/verify_traffic.json)."""
+    try:
+        return json.load(open(os.path.join(ROOT, "profiles", "verify_traffic.json")))
+    except Exception:
+        return None
+
+
 def config_dict(a, desc, batch, q_len, lo, hi):
     """What both arms print as `config`: the workload, nothing that differs between the arms."""
     return {"workload": desc, "batch": batch, "q_len": q_len, "ctx": [lo, hi], "page_tokens": 64, "preset": "baseline",
@@ -519,6 +528,22 @@ def main():
                                         "peak_TFLOPs": tensor_peak,
                                         "frac": flops / (attn_ms * 1e-3) / 1e12 / tensor_peak if attn_ms else None}},
                 "kernel_ms": kt, "clocks": main_res["clocks"]}
+        if q_len > 1:
+            # blocks of query tokens: the tensor cores bound the path (139 264 flop per visible row and
+            # token); under the block schedule a cache page is read once per SEQUENCE, so the cache
+            # bytes of a launch are those of the sequences' rows, not of every token's
+            seq_rows = sum(int(r) + q_len for r in wl.rows)
+            v8 = verify_traffic()
+            tfl = flops / (attn_ms * 1e-3) / 1e12 if attn_ms else None
+            line["roofline"] = {"bound": "tensor", "kernel": "k_attn_stream (M = 64 MMAs: half the dense rate)",
+                                "achieved": tfl, "peak": tensor_peak, "peak_kind": peak_kind + ", sustained bf16 GEMM",
+                                "unit": "TFLOP/s", "frac": tfl / tensor_peak if tfl else None,
+                                "flops_per_launch": flops, "launch_ms": attn_ms,
+                                "cache_bytes_per_launch": ROW_BYTES * seq_rows,
+                                "cache_bytes_if_every_token_read_its_own": kv_bytes,
+                                "traffic": v8["dram_bytes_per_sequence_row"] * seq_rows if v8 else None,
+                                "cache_GBs": ROW_BYTES * seq_rows / (attn_ms * 1e-3) / 1e9 if attn_ms else None,
+                                "schedule": "tokens" if a.token_schedule else "blocks"}
         line.update(extras)
         if world == 1 and not a.no_cpu_baseline:
             par, cw = parity_of(a, wl, main_res["out_bits"])
