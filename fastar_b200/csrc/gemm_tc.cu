@@ -173,11 +173,17 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
   } else {
     // epilogue warps: TMEM lane quadrant = warp % 4; thread = one weight row n
     pdl_wait();
-    if (p.rope_src && blockIdx.x == 0 && blockIdx.y == 0) {
-      // side job while the accumulator is being built: RoPE of head z's rope pairs, all tokens
+    // side job while the accumulator is being built: RoPE of head z's rope pairs.  Few tokens: the
+    // head's first block takes them all (spreading them bought nothing at 64 tokens); many tokens
+    // (verify blocks, prefill): every block of the head takes a slice, or the one block's 16 rounds
+    // of dependent loads outlast the whole GEMM.
+    const int rope_blocks = p.rope_T > 128 ? (int)(gridDim.x * gridDim.y) : 1;
+    const int rope_id = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+    if (p.rope_src && rope_id < rope_blocks) {
       const int half = p.rope_dims / 2, et = threadIdx.x - 64;  // 128 epilogue threads
-      const int n_items = p.rope_T * half;
-      for (int i0 = et; i0 < n_items; i0 += 8 * (GEMM_THREADS - 64)) {
+      const int t_lo = (int)((long long)p.rope_T * rope_id / rope_blocks), t_hi = (int)((long long)p.rope_T * (rope_id + 1) / rope_blocks);
+      const int n_items = t_hi * half;
+      for (int i0 = t_lo * half + et; i0 < n_items; i0 += 8 * (GEMM_THREADS - 64)) {
         // eight items per thread and round, all loads before the first store
         __nv_bfloat162 x[8];
         float2 cs[8];
@@ -208,7 +214,53 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     tc::tc_fence_after();
     const int row = quad * 32 + lane;
     const int n = n0 + row;
-    if (ok) {
+    // whether this block's output rows can go out as 8-byte stores (four weight rows per store)
+    const bool wide_out = p.splits == 1 && (p.ldc % 4) == 0 && (p.c_bs % 4) == 0 && (n0 % 4) == 0 && n0 + W_TILE <= p.N &&
+                          (reinterpret_cast<uintptr_t>(p.C) & 7) == 0;
+    if (wide_out) {
+      // the four epilogue warps take the staged path together or not at all (a wait that one of
+      // them gave up must not leave the others at the barriers below)
+      uint32_t all_ok;
+      asm volatile(
+          "{\n\t.reg .pred q, r;\n\t"
+          "setp.ne.u32 q, %1, 0;\n\t"
+          "bar.red.and.pred r, 1, 128, q;\n\t"
+          "selp.u32 %0, 1, 0, r;\n\t}"
+          : "=r"(all_ok)
+          : "r"((uint32_t)ok)
+          : "memory");
+      ok = all_ok != 0;
+    }
+    if (ok && wide_out) {
+      // No K split: the tile leaves through shared memory (the ring is idle once acc_bar fired), 32
+      // tokens at a time, so that a warp writes 256 contiguous bytes of one token's row instead of
+      // every thread two bytes per token.
+      float* red = reinterpret_cast<float*>(smem);  // [32][128]
+      const int e = threadIdx.x - 64;
+      for (int c0 = 0; c0 < NT; c0 += 32) {
+        if (m0 + c0 >= p.M) break;
+        float v[32];
+        if (n_kc > 0) {
+          tc::tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + c0, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < NT - c0) red[j * W_TILE + row] = v[j];
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int n_tok = min(min(32, NT - c0), p.M - m0 - c0);
+        for (int idx = e; idx < n_tok * (W_TILE / 4); idx += GEMM_THREADS - 64) {
+          const int tok = idx / (W_TILE / 4), r4 = (idx % (W_TILE / 4)) * 4;
+          const float4 f = *reinterpret_cast<const float4*>(red + tok * W_TILE + r4);
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(f.x, f.y), hi = __floats2bfloat162_rn(f.z, f.w);
+          *reinterpret_cast<uint2*>(p.C + z * p.c_bs + (long long)(m0 + c0 + tok) * p.ldc + n0 + r4) =
+              make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    } else if (ok) {
       float* red = reinterpret_cast<float*>(smem);  // [NT][128]: the ring is idle once acc_bar fired
       for (int c0 = 0; c0 < NT; c0 += 32) {
         if (p.splits == 1 && m0 + c0 >= p.M) break;
