@@ -105,6 +105,15 @@ def test_causal_verify_block(preset, impl):
     run_case(preset[1], impl[1], [100, 128, 250], q_len=16, causal=True, seed=3, ulps=1)
 
 
+@pytest.mark.parametrize("preset", PRESETS, ids=[p[0] for p in PRESETS])
+def test_blocks_of_tokens_with_a_sharp_softmax(preset):
+    # 16-token causal blocks over enough pages for the block schedule (groups of 16 lanes, whole-tile
+    # QK issue running ahead of the softmax), with a large query norm: the reference maximum moves
+    # often, also in the middle of a sequence, so the rescaling of O between the SV MMAs of
+    # consecutive tiles is exercised; lengths on and beside page boundaries
+    run_case(preset[1], mla.IMPL_TENSOR, [1500, 1023, 2048, 640, 3001], q_len=16, causal=True, seed=8, q_std=6.0, ulps=1)
+
+
 def test_empty_batch_and_zero_context():
     cfg, ctx = setup_ctx(mla.PRESET_BASELINE, mla.IMPL_AUTO, 8, 4)
     try:
