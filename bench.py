@@ -347,6 +347,32 @@ def measure_longctx(a, torch, dist, timer, rank, world, local):
     return res
 
 
+def measure_noalloc(torch, rows=65536, calls=10):
+    """fst_cuda_mla_attention_noalloc (decode attention without a context or any allocation, CUDA-core
+    kernels, at most 31 splits: its scratch is a fixed 4 MiB array) at its largest size: us per call."""
+    from fastar_b200 import mla
+    g = torch.Generator(device="cuda").manual_seed(0)
+    cache = torch.randn((rows, 576), generator=g, device="cuda").to(torch.bfloat16)
+    q = torch.randn((64, 576), generator=g, device="cuda").to(torch.bfloat16)
+    out = torch.zeros((64, 512), dtype=torch.bfloat16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    call = lambda: mla.attention_noalloc(q.data_ptr(), cache.data_ptr(), rows, 64, 576, 512, 1.0 / math.sqrt(192.0),  # noqa: E731
+                                         out.data_ptr(), st)
+    for _ in range(2):
+        if call():
+            return {"error": mla.load_library().fst_cuda_mla_last_error().decode()}
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    ev0.record()
+    for _ in range(calls):
+        call()
+    ev1.record()
+    torch.cuda.synchronize()
+    us = 1e3 * ev0.elapsed_time(ev1) / calls
+    return {"what": "fst_cuda_mla_attention_noalloc, one query token over 65536 contiguous rows", "rows": rows,
+            "us_per_call": us, "cache_GBs": rows * ROW_BYTES / (us * 1e-6) / 1e9, "finite": bool(torch.isfinite(out.float()).all())}
+
+
 def measure_batch(a, torch, dist, timer, rank, world, local, sharding, with_e2e, with_clocks):
     """Batched workloads (batched / single / verify), replicated per rank or one batch sharded."""
     from fastar_b200 import mla, workloads
@@ -494,6 +520,8 @@ def main():
                             "imbalance": st["rows_max"] * world / max(st["rows_all"], 1.0),
                             "attn_us_rank0": 1e3 * st["kernel_ms"]["attn"] if st["kernel_ms"]["attn"] else None}
         extras["longctx"] = measure_longctx(a, torch, dist, timer, rank, world, local)
+        if world == 1:
+            extras["noalloc"] = measure_noalloc(torch)
 
     if rank == 0:
         kt, info = main_res["kernel_ms"], main_res["info"]

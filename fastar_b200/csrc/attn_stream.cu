@@ -702,7 +702,7 @@ cudaError_t launch_attn_stream(const AttnArgs& a, cudaStream_t st) {
   p.tiles_shared = a.tiles_shared ? 1 : 0;
   const bool whole = a.tiles_shared;
 #define FST_ATTN_LAUNCH(NCHV, DIR, WH) \
-  launch_pdl(k_attn_stream<NCHV, DIR, WH>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(NCHV), st, 1, tmKV, tmQ, p)
+  launch_k(a.dependent_launch, k_attn_stream<NCHV, DIR, WH>, dim3(a.n_ctas), dim3(ST_THREADS), smem_total(NCHV), st, 1, tmKV, tmQ, p)
   if (a.d_qk == 576) {
     if (whole) return p.direct ? FST_ATTN_LAUNCH(9, true, true) : FST_ATTN_LAUNCH(9, false, true);
     return p.direct ? FST_ATTN_LAUNCH(9, true, false) : FST_ATTN_LAUNCH(9, false, false);

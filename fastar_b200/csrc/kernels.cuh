@@ -54,8 +54,8 @@ inline void prefer_max_shared(const void* kernel) {
 
 // Launch with programmatic stream serialisation (and an optional cluster along y).
 template <class... KArgs, class... Args>
-inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
-                              int cluster_y, Args&&... args) {
+inline cudaError_t launch_k(bool dependent, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                            int cluster_y, Args&&... args) {
   prefer_max_shared(reinterpret_cast<const void*>(kernel));
   cudaError_t e_attr = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
   if (e_attr != cudaSuccess) return e_attr;
@@ -66,9 +66,11 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
   int n = 0;
-  attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[n].val.programmaticStreamSerializationAllowed = 1;
-  ++n;
+  if (dependent) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
   if (cluster_y > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
     attr[n].val.clusterDim.x = 1;
@@ -79,6 +81,13 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cfg.attrs = attr;
   cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+// Programmatic dependent launch: the kernel may start while its predecessor in the stream drains
+// and orders itself behind it with griddepcontrol.wait.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              int cluster_y, Args&&... args) {
+  return launch_k(true, kernel, grid, block, smem, st, cluster_y, static_cast<Args&&>(args)...);
 }
 
 // Strided-batched C[z][m, n] = sum_k A[z][m, k] * B[z][n, k]  (b_kn: B[z][k, n]).
@@ -154,6 +163,10 @@ struct AttnArgs {
   long long q_rows;         // rows of q_eff (new tokens * H)
   long long pool_rows;      // n_pages * page_tokens
   float scale;
+  // tcgen05 kernel: launch as a programmatic dependent of the kernel before it in the stream.  Off
+  // for callers whose schedule arrays (segs, cta_seg, tables) are WRITTEN by that kernel: the
+  // attention kernel reads its block's segment range before it waits for its predecessor.
+  bool dependent_launch = true;
   // the schedule makes several thread blocks read the same cache tiles at about the same time
   // (blocks of query tokens): tiles then keep the normal L2 priority instead of leaving first, and
   // the tcgen05 kernel lets each QK issuer take whole tiles (k_attn_stream, WHOLE)

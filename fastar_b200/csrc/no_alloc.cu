@@ -34,7 +34,8 @@ constexpr size_t SZ_PART_ML = (size_t)NA_MAX_SPLITS * NA_MAX_HEADS * sizeof(floa
 constexpr size_t OFF_PART_L = OFF_PART_M + SZ_PART_ML;
 constexpr size_t OFF_SEGS = OFF_PART_L + SZ_PART_ML;
 constexpr size_t OFF_TABLE = OFF_SEGS + 1024;                                   // 32 segments x 20 bytes, padded
-constexpr size_t OFF_TOK = OFF_TABLE + (NA_MAX_ROWS / NA_PAGE) * sizeof(int32_t);  // tok_table[1], tok_part[2]
+constexpr size_t OFF_TOK = OFF_TABLE + (NA_MAX_ROWS / NA_PAGE) * sizeof(int32_t);  // tok_table[1], tok_part[2]; from
+                                                                                // int 16: cta_seg[33]; int 60: status
 constexpr size_t OFF_LUT = OFF_TOK + 256;                                       // unused RoPE table slot
 constexpr size_t SCRATCH_BYTES = OFF_LUT + 256;
 
@@ -48,28 +49,32 @@ unsigned char* g_na_ptr[64] = {nullptr};
 
 // Rewrites every piece of bookkeeping the attention and merge kernels read from the scratch:
 // an identity block table (the cache is contiguous), the split schedule, the one-token maps.
-__global__ void k_na_setup(unsigned char* scratch, int n_rows, int n_splits) {
+// unit: rows per schedule tile -- 32 for the CUDA-core kernel, 64 (a page) for the tcgen05 one,
+// whose thread block k walks segment k (cta_seg) and reports a wait that ran out in the status word.
+__global__ void k_na_setup(unsigned char* scratch, int n_rows, int n_splits, int unit) {
   AttnSeg* segs = reinterpret_cast<AttnSeg*>(scratch + OFF_SEGS);
   int32_t* table = reinterpret_cast<int32_t*>(scratch + OFF_TABLE);
   int32_t* tok = reinterpret_cast<int32_t*>(scratch + OFF_TOK);
   const int n_pages = (n_rows + NA_PAGE - 1) / NA_PAGE;
   for (int i = threadIdx.x; i < n_pages; i += blockDim.x) table[i] = i;
   if (threadIdx.x < n_splits) {
-    // equal runs of 32-row tiles; the last split takes the ragged end
-    const int tiles = (n_rows + 31) / 32;
+    // equal runs of tiles; the last split takes the ragged end
+    const int tiles = (n_rows + unit - 1) / unit;
     const int s = threadIdx.x;
     AttnSeg sg;
     sg.tok = 0;
-    sg.kv_begin = (int)((long long)tiles * s / n_splits) * 32;
-    sg.kv_end = min(n_rows, (int)((long long)tiles * (s + 1) / n_splits) * 32);
+    sg.kv_begin = (int)((long long)tiles * s / n_splits) * unit;
+    sg.kv_end = min(n_rows, (int)((long long)tiles * (s + 1) / n_splits) * unit);
     sg.part = s;
     sg.table = 0;  // the identity block table starts at entry 0
     segs[s] = sg;
   }
+  if (threadIdx.x <= n_splits) tok[16 + threadIdx.x] = threadIdx.x;  // cta_seg: block k takes segment k
   if (threadIdx.x == 0) {
     tok[0] = 0;         // tok_table[0]: the token's block table starts at entry 0
     tok[1] = 0;         // tok_part[0]
     tok[2] = n_splits;  // tok_part[1]
+    tok[60] = 0;        // status word of the bounded waits
   }
 }
 
@@ -118,22 +123,16 @@ extern "C" int fst_cuda_mla_attention_noalloc(const void* d_q_eff, const void* d
   }
   unsigned char* sc = g_na_ptr[dev];
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
-  const int n_splits = std::max(1, std::min(NA_MAX_SPLITS, (n_rows + 127) / 128));
-
-  k_na_setup<<<1, 256, 0, st>>>(sc, n_rows, n_splits);
-
   AttnArgs a;
   a.q_eff = static_cast<const bf16*>(d_q_eff);
   a.pool = static_cast<const bf16*>(d_cache);
   a.tables = reinterpret_cast<const int32_t*>(sc + OFF_TABLE);
   a.segs = reinterpret_cast<const AttnSeg*>(sc + OFF_SEGS);
-  a.cta_seg = nullptr;
+  a.cta_seg = reinterpret_cast<const int32_t*>(sc + OFF_TOK) + 16;
   a.part_m = reinterpret_cast<float*>(sc + OFF_PART_M);
   a.part_l = reinterpret_cast<float*>(sc + OFF_PART_L);
   a.part_o = reinterpret_cast<float*>(sc + OFF_PART_O);
-  a.d_status = nullptr;
-  a.n_segs = n_splits;
-  a.n_ctas = n_splits;
+  a.d_status = reinterpret_cast<int*>(sc + OFF_TOK) + 60;
   a.H = n_heads;
   a.d_qk = d_qk;
   a.d_v = d_v;
@@ -142,7 +141,24 @@ extern "C" int fst_cuda_mla_attention_noalloc(const void* d_q_eff, const void* d
   a.q_rows = n_heads;
   a.pool_rows = n_rows;
   a.scale = softmax_scale;
-  launch_attn_simt(a, st);
+  // The full MLA shape (64 heads, 576- or 512-wide rows, 512 value columns) goes to the tcgen05
+  // streaming kernel, one thread block per split over whole 64-row pages; every other shape to the
+  // CUDA-core kernel (so do caches of less than one page).  Either way at most 32 splits: that is
+  // what the scratch holds.
+  const bool stream = n_rows >= NA_PAGE && attn_stream_supported(a);
+  const int unit = stream ? NA_PAGE : 32;
+  const int n_splits = std::max(1, std::min(NA_MAX_SPLITS, stream ? (n_rows + NA_PAGE - 1) / NA_PAGE : (n_rows + 127) / 128));
+  a.n_segs = n_splits;
+  a.n_ctas = n_splits;
+  k_na_setup<<<1, 256, 0, st>>>(sc, n_rows, n_splits, unit);
+  if (stream) {
+    // (not as a programmatic dependent: the schedule it reads on entry was written by k_na_setup)
+    a.dependent_launch = false;
+    cudaError_t es = launch_attn_stream(a, st);
+    if (es != cudaSuccess) return na_fail(FST_MLA_ERR_CUDA, cudaGetErrorString(es));
+  } else {
+    launch_attn_simt(a, st);
+  }
 
   MergeArgs m;
   m.part_m = a.part_m;
@@ -160,6 +176,7 @@ extern "C" int fst_cuda_mla_attention_noalloc(const void* d_q_eff, const void* d
   m.inv_rope = 0;
   m.mode = 0;
   m.threads = 256;
+  m.wide = 1;  // one query token: a block per (head row, 128 columns) where the shape allows
   launch_merge(m, st);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return na_fail(FST_MLA_ERR_CUDA, cudaGetErrorString(e));

@@ -36,7 +36,9 @@ def test_matches_the_regular_entry_point_twice_in_a_row():
     scale = 1.0 / math.sqrt(192.0)
     rng = np.random.default_rng(12)
     cfg = mla.make_config()
-    for call, L in enumerate((5000, 777)):  # the second, smaller call reuses the array's stale contents
+    # (the second, smaller call reuses the array's stale contents; the third is the largest size, all 32 splits
+    # of the tcgen05 kernel with a ragged last page)
+    for call, L in enumerate((5000, 777, 65536 - 37)):
         rows = synth.to_bf16_bits(synth.cache_rows_f32(cfg, 40 + call, 0, L))
         q = synth.to_bf16_bits(rng.standard_normal((64, 576)).astype(np.float32))
         d_rows = torch.from_numpy(rows.view(np.int16)).cuda()
