@@ -63,6 +63,9 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the strong-scaling and long-context measurements")
     ap.add_argument("--merge-kernel", action="store_true", help="every token through its partial and the merge kernel")
+    ap.add_argument("--preset", default="baseline", choices=["baseline", "v4"],
+                    help="v4: the live engine's layer form (512-wide rows, head norm, sink, inverse RoPE, grouped wo_a, "
+                         "214 MB of weights); GPU figures only (its parity is the tests'), no CPU legs")
     ap.add_argument("--token-schedule", action="store_true",
                     help="multi-token calls keep the token-by-token split-KV schedule (no groups of lanes sharing pages)")
     ap.add_argument("--min-timed-s", type=float, default=0.25)
@@ -152,7 +155,7 @@ def verify_traffic():
 
 def config_dict(a, desc, batch, q_len, lo, hi):
     """What both arms print as `config`: the workload, nothing that differs between the arms."""
-    return {"workload": desc, "batch": batch, "q_len": q_len, "ctx": [lo, hi], "page_tokens": 64, "preset": "baseline",
+    return {"workload": desc, "batch": batch, "q_len": q_len, "ctx": [lo, hi], "page_tokens": 64, "preset": a.preset,
             "seed": a.seed}
 
 
@@ -379,7 +382,8 @@ def measure_batch(a, torch, dist, timer, rank, world, local, sharding, with_e2e,
     wl = workloads.build(a.workload if a.workload != "longctx" else "batched", seed=a.seed, rank=rank, world=world,
                          sharding=sharding, device=local, batch=a.batch, ctx_lo=a.ctx_lo, ctx_hi=a.ctx_hi,
                          attn_impl=a.attn_impl, gemm_impl=a.gemm_impl, stream=torch.cuda.current_stream().cuda_stream,
-                         scramble=not a.sequential_pages)
+                         scramble=not a.sequential_pages,
+                         preset=mla.PRESET_FASTAR_V4 if a.preset == "v4" else mla.PRESET_BASELINE)
     ctx = wl.ctx
     if a.merge_kernel:
         ctx.set_fused_merge(False)
@@ -508,7 +512,7 @@ def main():
     main_res = measure_batch(a, torch, dist, timer, rank, world, local, "replica", True, True)
     wl = main_res["wl"]
     extras = {}
-    if not a.no_extras and a.workload == "batched":
+    if not a.no_extras and a.workload == "batched" and a.preset == "baseline":
         if world > 1:
             st = measure_batch(a, torch, dist, timer, rank, world, local, "strong", False, False)
             st["wl"].close()
@@ -525,12 +529,13 @@ def main():
 
     if rank == 0:
         kt, info = main_res["kernel_ms"], main_res["info"]
-        kv_bytes = ROW_BYTES * info["kv_rows"]
+        row_bytes = 1024 if a.preset == "v4" else ROW_BYTES
+        kv_bytes = row_bytes * info["kv_rows"]
         attn_ms, merge_ms = kt["attn"] or 0.0, kt["merge"] or 0.0
         ach_attn = kv_bytes / (attn_ms * 1e-3) / 1e9 if attn_ms else None
         ach_both = kv_bytes / ((attn_ms + merge_ms) * 1e-3) / 1e9 if attn_ms else None
         tr = ncu_traffic()
-        flops = 2.0 * 64 * (576 + 512) * info["kv_rows"]
+        flops = 2.0 * 64 * ((512 if a.preset == "v4" else 576) + 512) * info["kv_rows"]
         cfg = config_dict(a, desc, batch, q_len, lo, hi)
         run = {}
         run.update({"cached_rows_rank0": info["kv_rows"], "attn_ctas": info["n_ctas"], "attn_partials": info["n_partials"],
@@ -573,7 +578,7 @@ def main():
                                 "cache_GBs": ROW_BYTES * seq_rows / (attn_ms * 1e-3) / 1e9 if attn_ms else None,
                                 "schedule": "tokens" if a.token_schedule else "blocks"}
         line.update(extras)
-        if world == 1 and not a.no_cpu_baseline:
+        if world == 1 and not a.no_cpu_baseline and a.preset == "baseline":
             par, cw = parity_of(a, wl, main_res["out_bits"])
             line["parity"] = par
             t0, passes = time.perf_counter(), 0
