@@ -293,8 +293,75 @@ __global__ void __launch_bounds__(256) k_q_rope_token(QPrepArgs a) {
   }
 }
 
+// V4: a warp per (token, head) row, eight rows per block: the row (q_head <= 1024 values) stays in
+// registers, 16 bytes per lane and pass; one shuffle reduction instead of two block barriers and a
+// shared-memory round trip per row.  Same order of operations per element as k_q_prep.
+__global__ void __launch_bounds__(256) k_q_prep_v4_rows(QPrepArgs a) {
+  pdl_launch();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long r = (long long)blockIdx.x * 8 + warp;
+  if (r >= (long long)a.T * a.H) return;
+  const int t = (int)(r / a.H), h = (int)(r % a.H);
+  const uint4* in = reinterpret_cast<const uint4*>(a.q_full + r * a.q_head);
+  uint4* out = reinterpret_cast<uint4*>(a.q_eff + r * a.d_qk);
+  const float* lut = a.lut + (long long)t * a.rope;
+  const int n_u = a.q_head / 8;
+  float x[4][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int u = lane + 32 * i;
+    if (u < n_u) {
+      const uint4 v = in[u];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+        x[i][2 * e] = __low2float(b);
+        x[i][2 * e + 1] = __high2float(b);
+        ss += x[i][2 * e] * x[i][2 * e] + x[i][2 * e + 1] * x[i][2 * e + 1];
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  const float sc = a.head_norm ? 1.0f / sqrtf(ss / (float)a.q_head + a.eps) : 1.0f;
+  const bool rot = h < a.rope_heads;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int u = lane + 32 * i;
+    if (u < n_u) {
+      float y[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = rbf(x[i][e] * sc);
+      const int j0 = 8 * u - a.nope;  // first rope dim of this unit, if not negative
+      if (rot && j0 >= 0) {
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          const float c = lut[j0 + e], sn = lut[j0 + e + 1], x0 = y[e], x1 = y[e + 1];
+          y[e] = x0 * c - x1 * sn;
+          y[e + 1] = x0 * sn + x1 * c;
+        }
+      }
+      uint32_t pk[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(y[2 * e], y[2 * e + 1]);
+        pk[e] = *reinterpret_cast<const uint32_t*>(&b);
+      }
+      out[u] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+  }
+}
+
 void launch_q_prep(const QPrepArgs& a, cudaStream_t st) {
   if (a.T <= 0) return;
+  if (a.v4 && a.q_head % 8 == 0 && a.q_head <= 1024 && a.nope % 8 == 0 && a.d_qk % 8 == 0 && a.rope % 2 == 0 &&
+      a.nope + a.rope == a.q_head && (reinterpret_cast<uintptr_t>(a.q_full) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(a.q_eff) & 15) == 0) {
+    launch_pdl(k_q_prep_v4_rows, dim3((unsigned)(((long long)a.T * a.H + 7) / 8)), dim3(256), 0, st, 1, a);
+    return;
+  }
   // (pair accesses need even offsets: q_head, nope, d_qk and rope are even in both presets)
   if (!a.v4 && a.q_head % 2 == 0 && a.nope % 2 == 0 && a.d_qk % 2 == 0 && a.rope % 2 == 0)
     launch_pdl(k_q_rope_token, dim3(a.T), dim3(256), 0, st, 1, a);
