@@ -406,7 +406,12 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, int* d_status, cudaStream_t st) {
   p.rope_T = g.rope_T; p.rope_H = g.rope_H; p.rope_q_head = g.rope_q_head; p.rope_nope = g.rope_nope;
   p.rope_dims = g.rope_dims; p.rope_d_qk = g.rope_d_qk;
   const int stage_bytes = W_BYTES + NT * BK * 2;
-  p.stages = std::max(2, std::min(8, (96 * 1024) / stage_bytes));
+  // Two blocks share an SM (96 KB of operand ring each) -- unless the grid has no more blocks than
+  // there are SMs: then a block has the SM to itself anyway and takes a ring that holds its whole K
+  // slice, so that every operand tile is requested at once instead of in two or three turns.
+  const bool alone = tiles * splits <= n_sm;
+  const int per_block = (kc_total + splits - 1) / splits;
+  p.stages = std::max(2, std::min(std::min(8, alone ? per_block : 8), ((alone ? 192 : 96) * 1024) / stage_bytes));
   const size_t ring = (size_t)p.stages * stage_bytes, red = splits > 1 ? (size_t)NT * W_TILE * 4 : 0;
   const size_t smem = std::max(ring, red) + 1024 /* alignment */ + 256 /* barriers */;
   dim3 grid(n_tiles, m_tiles * splits, g.batch);
