@@ -373,6 +373,11 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, int* d_status, cudaStream_t st) {
   const long long tiles = (long long)n_tiles * m_tiles * g.batch;
   int splits = 1;
   while (splits < MAX_SPLITS && tiles * splits * 2 <= 2ll * n_sm && kc_total / (splits * 2) >= 2) splits *= 2;
+  // Output tiles that cover half of the SMs or more are not split at all: a block per SM with a ring
+  // of eight stages and no cluster reduction beats two half-size blocks on a third of the SMs
+  // (the q-expand GEMM, 96 tiles: 18.2 -> 16.5 us; cut in three or four it was slower still).
+  // With a handful of tokens the split wins (one token: 14.5 against 16.3 us).
+  if (NT >= 64 && tiles * 2 >= n_sm && tiles <= n_sm) splits = 1;
 
   CUtensorMap tmW, tmA;
   const char* err = nullptr;
