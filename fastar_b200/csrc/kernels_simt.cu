@@ -652,28 +652,43 @@ __global__ void __launch_bounds__(256) k_merge_rows(MergeArgs a) {
     const int p0 = a.tok_part[t], n_parts = a.tok_part[t + 1] - p0;
     if (a.skip_single && n_parts == 1) return;  // finished by the attention kernel
     const bool sk = a.sinks != nullptr;
+    // Lane p holds (max, sum) of part p of a chunk of 32 parts: one round trip for the statistics of
+    // all parts instead of one per part; the parts themselves are walked in order, as before.
     float M = sk ? a.sinks[h] : -INFINITY;
-    for (int p = 0; p < n_parts; ++p) M = fmaxf(M, a.part_m[(long long)(p0 + p) * a.H + h]);
+    float m_l = -INFINITY;
+    for (int base = 0; base < n_parts; base += 32) {
+      m_l = base + lane < n_parts ? a.part_m[(long long)(p0 + base + lane) * a.H + h] : -INFINITY;
+      M = fmaxf(M, warp_max(m_l));
+    }
     float den = sk ? expf(a.sinks[h] - M) : 0.0f;
     float acc[16];
 #pragma unroll
     for (int c = 0; c < 16; ++c) acc[c] = 0.0f;
-    for (int p = 0; p < n_parts; ++p) {
-      const long long i = (long long)(p0 + p) * a.H + h;
-      const float m = a.part_m[i];
-      if (m == -INFINITY) continue;
-      const float w = expf(m - M);
-      den += w * a.part_l[i];
-      const float* o = a.part_o + i * a.d_v;
+    for (int base = 0; base < n_parts; base += 32) {
+      const bool mine = base + lane < n_parts;
+      const long long i_l = (long long)(p0 + base + (mine ? lane : 0)) * a.H + h;
+      if (n_parts > 32) m_l = mine ? a.part_m[i_l] : -INFINITY;  // (one chunk: still in the register)
+      const float l_l = mine ? a.part_l[i_l] : 0.0f;
+      const float w_l = m_l == -INFINITY ? 0.0f : expf(m_l - M);
+      const int cnt = min(32, n_parts - base);
+      for (int p = 0; p < cnt; ++p) {
+        const long long i = (long long)(p0 + base + p) * a.H + h;
+        const float m = __shfl_sync(0xffffffffu, m_l, p);
+        const float w = __shfl_sync(0xffffffffu, w_l, p);
+        const float lp = __shfl_sync(0xffffffffu, l_l, p);
+        if (m == -INFINITY) continue;
+        den += w * lp;
+        const float* o = a.part_o + i * a.d_v;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int col = lane * 4 + 128 * j;
-        if (col < a.d_v) {
-          const float4 v = *reinterpret_cast<const float4*>(o + col);
-          acc[4 * j] = fmaf(w, v.x, acc[4 * j]);
-          acc[4 * j + 1] = fmaf(w, v.y, acc[4 * j + 1]);
-          acc[4 * j + 2] = fmaf(w, v.z, acc[4 * j + 2]);
-          acc[4 * j + 3] = fmaf(w, v.w, acc[4 * j + 3]);
+        for (int j = 0; j < 4; ++j) {
+          const int col = lane * 4 + 128 * j;
+          if (col < a.d_v) {
+            const float4 v = *reinterpret_cast<const float4*>(o + col);
+            acc[4 * j] = fmaf(w, v.x, acc[4 * j]);
+            acc[4 * j + 1] = fmaf(w, v.y, acc[4 * j + 1]);
+            acc[4 * j + 2] = fmaf(w, v.z, acc[4 * j + 2]);
+            acc[4 * j + 3] = fmaf(w, v.w, acc[4 * j + 3]);
+          }
         }
       }
     }
