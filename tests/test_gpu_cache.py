@@ -49,10 +49,20 @@ def test_page_mapping_matches_twin(ctx):
             ctx.seq_free(s)
             assert tw.seq_free(s) == 0
             del live[s]
+        owned = []
         for s, n in live.items():
             assert np.array_equal(ctx.block_table(s), tw.table(s))
             assert ctx.seq_len(s) == n
+            table = [int(x) for x in ctx.block_table(s)]
+            # invariants that do not come from the twin: a sequence holds exactly the pages its
+            # length needs, every page number is in range
+            assert len(table) == (n + 63) // 64
+            assert all(0 <= pg < 40 for pg in table)
+            owned += table
         assert ctx.free_pages() == tw.free_pages()
+        # ... no page is owned twice, and owned + free pages are the whole pool
+        assert len(owned) == len(set(owned))
+        assert len(owned) + ctx.free_pages() == 40
 
 
 def test_rows_land_where_the_table_says(ctx):
