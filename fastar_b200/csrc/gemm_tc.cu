@@ -40,6 +40,8 @@ struct GemmTcParams {
   const float* rope_lut;
   bf16* rope_dst;
   int rope_T, rope_H, rope_q_head, rope_nope, rope_dims, rope_d_qk;
+  const int* status_dev;  // GemmArgs::status_dev / status_host
+  int* status_host;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -327,6 +329,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 
   tc::tc_fence_before();
   __syncthreads();
+  if (p.status_host && threadIdx.x == 0) {
+    // (after this block's own waits: whatever it recorded itself is in the word it reads)
+    const int st = *reinterpret_cast<const volatile int*>(p.status_dev);
+    if (st != 0) *reinterpret_cast<volatile int*>(p.status_host) = st;
+  }
   if (*abort_flag) {
     // a wait was given up: let copies and MMAs in flight settle before TMEM is released
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
@@ -410,6 +417,7 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, int* d_status, cudaStream_t st) {
   p.rope_src = g.rope_src; p.rope_lut = g.rope_lut; p.rope_dst = g.rope_dst;
   p.rope_T = g.rope_T; p.rope_H = g.rope_H; p.rope_q_head = g.rope_q_head; p.rope_nope = g.rope_nope;
   p.rope_dims = g.rope_dims; p.rope_d_qk = g.rope_d_qk;
+  p.status_dev = g.status_host ? g.status_dev : nullptr; p.status_host = g.status_dev ? g.status_host : nullptr;
   const int stage_bytes = W_BYTES + NT * BK * 2;
   // Two blocks share an SM (96 KB of operand ring each) -- unless the grid has no more blocks than
   // there are SMs: then a block has the SM to itself anyway and takes a ring that holds its whole K

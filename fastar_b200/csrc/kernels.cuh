@@ -109,6 +109,12 @@ struct GemmArgs {
   const float* rope_lut = nullptr;  // [T, rope] (cos, sin) pairs
   bf16* rope_dst = nullptr;
   int rope_T = 0, rope_H = 0, rope_q_head = 0, rope_nope = 0, rope_dims = 0, rope_d_qk = 0;
+  // Optional, tcgen05 kernel only (null: off): every block, as its last act, reads the device status
+  // word of the bounded waits and, if it is not zero, stores it to *status_host -- a word in
+  // page-locked host memory that the device can address.  Given to the LAST kernel of a layer call:
+  // the host then has the status when the stream is synchronised, without a copy behind the call.
+  const int* status_dev = nullptr;
+  int* status_host = nullptr;
 };
 void launch_gemm_simt(const GemmArgs& g, cudaStream_t st);
 // tcgen05 path: B in [N, K] layout only, K % 64 == 0, N % 128 == 0, 16-byte aligned rows.

@@ -137,6 +137,8 @@ struct FstMlaCtx {
   const bf16* out_src = nullptr;  // where the last layer call left its output rows
   bool out_zero_copy = true;
   int* h_status = nullptr;  // page-locked copy of the status word, fetched on the stream before a sync
+  int* h_status_dev = nullptr;   // the device's address of h_status (mapped), or null
+  bool status_by_kernel = false; // the last kernel enqueued was an O-proj b that stores the status word to h_status itself
 
   // RoPE kind of every layer: 0 plain (theta = cfg.rope_theta), 1 YaRN (reference
   // build_rope_lut picks per layer, src/fst_engine.cpp:1979-1982)
@@ -375,6 +377,7 @@ bool use_tc_gemm(const FstMlaCtx* c, const GemmArgs& g) {
 }
 
 int run_gemm(FstMlaCtx* c, const GemmArgs& g) {
+  c->status_by_kernel = false;
   if (c->cfg.gemm_impl == FST_MLA_IMPL_TENSOR && !gemm_tc_supported(g))
     return fail(FST_MLA_ERR_ARG, "GEMM %dx%dx%d (b_kn=%d) has no tcgen05 path", g.M, g.N, g.K, g.b_kn);
   if (use_tc_gemm(c, g)) {
@@ -438,6 +441,7 @@ AttnArgs attn_args(FstMlaCtx* c, int lid, const bf16* q_eff, bool may_fuse = fal
 // token that has exactly one partial; the merge that follows skips them.
 int run_attention(FstMlaCtx* c, int lid, const bf16* q_eff, bool* direct = nullptr) {
   if (direct) *direct = false;
+  c->status_by_kernel = false;
   c->info_class = class_of(c, lid);
   if (sched_of(c, lid).n_segs == 0) return FST_MLA_OK;
   AttnArgs a = attn_args(c, lid, q_eff, direct != nullptr);
@@ -565,7 +569,14 @@ int run_back(FstMlaCtx* c, int lid, bf16* h_out) {
   }
   if ((rc = run_gemm(c, g))) return rc;
   prof_mark(c, FST_MLA_K_OPROJ_B);
-  if ((rc = run_gemm(c, plain_gemm(c->d_low, w.wo_b, h_out, T, d.hidden, d.low)))) return rc;
+  GemmArgs gb = plain_gemm(c->d_low, w.wo_b, h_out, T, d.hidden, d.low);
+  const bool by_kernel = c->h_status_dev && use_tc_gemm(c, gb);
+  if (by_kernel) {
+    gb.status_dev = c->d_status;
+    gb.status_host = c->h_status_dev;
+  }
+  if ((rc = run_gemm(c, gb))) return rc;
+  c->status_by_kernel = by_kernel;  // (until anything else is launched: run_gemm clears it)
   prof_mark(c, FST_MLA_K_COUNT);
   return FST_MLA_OK;
 }
@@ -703,9 +714,13 @@ int fst_cuda_mla_create(const FstMlaConfig* cfg, FstMlaCtx** out) {
     rc = fail(FST_MLA_ERR_CUDA, "cudaStreamCreate failed");
   if (!rc) rc = dev_alloc(&x->d_status, 1);
   if (!rc && cudaMemset(x->d_status, 0, sizeof(int)) != cudaSuccess) rc = fail(FST_MLA_ERR_CUDA, "cudaMemset failed");
-  if (!rc && cudaHostAlloc((void**)&x->h_status, sizeof(int), cudaHostAllocDefault) != cudaSuccess)
+  if (!rc && cudaHostAlloc((void**)&x->h_status, sizeof(int), cudaHostAllocMapped) != cudaSuccess)
     rc = fail(FST_MLA_ERR_CUDA, "cudaHostAlloc failed");
   if (!rc) *x->h_status = 0;
+  if (!rc && cudaHostGetDevicePointer((void**)&x->h_status_dev, x->h_status, 0) != cudaSuccess) {
+    cudaGetLastError();
+    x->h_status_dev = nullptr;  // no mapping: the status word is copied behind every call instead
+  }
   if (!rc && cudaHostAlloc((void**)&x->h_pinned, T * d.hidden * sizeof(uint16_t), cudaHostAllocDefault) != cudaSuccess)
     rc = fail(FST_MLA_ERR_CUDA, "cudaHostAlloc failed");
   if (rc) {
@@ -756,11 +771,16 @@ int fst_cuda_mla_set_stream(FstMlaCtx* c, void* s) {
 
 int fst_cuda_mla_sync(FstMlaCtx* c) {
   if (!c) return fail(FST_MLA_ERR_ARG, "null context");
-  // the status word rides the stream (a blocking copy after the synchronisation costs ~10 us more)
-  CU(cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+  // The status word rides the stream (a blocking copy after the synchronisation costs ~10 us more) --
+  // or, behind a whole layer call, was stored to h_status by the last GEMM itself if it was not
+  // zero (GemmArgs::status_host), which saves the copy and its 8 us of completion latency.
+  if (!c->status_by_kernel)
+    CU(cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+  c->status_by_kernel = false;
   CU(cudaStreamSynchronize(c->stream));
-  const int st = *c->h_status;
+  const int st = *reinterpret_cast<volatile int*>(c->h_status);
   if (st != 0) {
+    *c->h_status = 0;
     cudaMemset(c->d_status, 0, sizeof(int));
     return fail(FST_MLA_ERR_DEVICE_CHECK, "a kernel gave up a bounded wait (status %d)", st);
   }
@@ -2018,6 +2038,7 @@ int fst_cuda_mla_selftest_wait_expiry(FstMlaCtx* c, int32_t polls) {
   if (!c) return fail(FST_MLA_ERR_ARG, "null context");
   if (polls < 1 || polls > (1 << 16)) return fail(FST_MLA_ERR_ARG, "poll limit %d outside [1, 65536]", polls);
   CU(cudaSetDevice(c->cfg.device));
+  c->status_by_kernel = false;
   launch_wait_selftest(c->d_status, (uint32_t)polls, c->stream);
   c->launches += 1;
   CU(cudaGetLastError());
@@ -2076,6 +2097,7 @@ int fst_cuda_mla_debug_schedule(int32_t n_sm, const int32_t* pos0, const int32_t
 
 int fst_cuda_mla_debug_set_status(FstMlaCtx* c, int32_t code) {
   if (!c) return fail(FST_MLA_ERR_ARG, "null context");
+  c->status_by_kernel = false;
   CU(cudaSetDevice(c->cfg.device));
   CU(cudaMemcpyAsync(c->d_status, &code, sizeof(int), cudaMemcpyHostToDevice, c->stream));
   CU(cudaStreamSynchronize(c->stream));
